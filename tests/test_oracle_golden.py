@@ -1,0 +1,201 @@
+"""Pins the NumPy oracle against golden vectors produced by the reference's own
+torch-CPU operators (tests/golden/make_golden.py), and against the invariants
+the reference's tests assert."""
+import glob
+import hashlib
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import moe_oracle as O
+
+GOLDEN = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "moe_ref_*.npz")))
+
+
+def sha(a):
+    return hashlib.sha256(np.ascontiguousarray(a).tobytes()).hexdigest()
+
+
+@pytest.mark.parametrize("path", GOLDEN, ids=[os.path.basename(p)[8:-4] for p in GOLDEN])
+def test_gate_matches_reference(path):
+    rec = np.load(path)
+    S, E, M, C = (int(rec[k]) for k in ("S", "E", "M", "C"))
+    assert O.capacity(S, E, 1.0) == C
+    gates_s, idx_loc, cap, elems = O.moe_gate(rec["gate"], np.zeros(E, np.int32), C, M)
+    np.testing.assert_array_equal(idx_loc, rec["idx_loc"])
+    np.testing.assert_array_equal(cap, rec["capused"])
+    np.testing.assert_array_equal(elems.astype(np.int64), rec["elems"])
+    # gates_s: reference sums gate*one_hot (exact: products with 0/1)
+    np.testing.assert_array_equal(gates_s[0], rec["gates_s"])
+
+
+@pytest.mark.parametrize("path", [p for p in GOLDEN if "x" in np.load(p).files],
+                         ids=lambda p: os.path.basename(p)[8:-4])
+def test_data_paths_match_reference(path):
+    rec = np.load(path)
+    S, E, M, C = (int(rec[k]) for k in ("S", "E", "M", "C"))
+    il = rec["idx_loc"]
+    disp = O.moe_encode_fwd(il, rec["x"], E, C, np.zeros(E, np.int32))
+    np.testing.assert_array_equal(disp, rec["disp"])
+    assert sha(disp) == str(rec["sha_disp"])
+    out = O.moe_decode_fwd(rec["eo"], rec["gates_s"], il)
+    np.testing.assert_array_equal(out, rec["out"])
+    np.testing.assert_array_equal(O.moe_encode_dx(il, rec["d_disp"], S), rec["enc_dx"])
+    dg = O.moe_encode_dg(rec["d_gates"], il, E)
+    ref_dg = np.zeros((S, E), np.float32)
+    ref_dg[tuple(rec["enc_dg_nnz"])] = rec["enc_dg_val"]
+    np.testing.assert_array_equal(dg, ref_dg)
+    np.testing.assert_array_equal(O.moe_decode_dx(rec["gates_s"], il, rec["d_out"], E, C), rec["dec_dx"])
+    np.testing.assert_allclose(O.moe_decode_dg(il, rec["d_out"], rec["eo"])[0], rec["dec_dg"], rtol=1e-5, atol=1e-5)
+
+
+def test_c1_hashes_from_seed():
+    """Config 1 (S=2048, E=8, M=512, softmax gate, seed 0): regenerate the token
+    matrix from the seed and check the dispatched buffer and the combined output
+    against the reference's hashes."""
+    rec = np.load([p for p in GOLDEN if "c1_" in p][0])
+    S, E, M, C = (int(rec[k]) for k in ("S", "E", "M", "C"))
+    g = torch.Generator().manual_seed(int(rec["seed"]))
+    gate = torch.softmax(torch.randn(S, E, generator=g), dim=1).numpy()
+    x = torch.randn(S, M, generator=g).numpy()
+    if sha(x) != str(rec["sha_x"]) or not np.array_equal(gate, rec["gate"]):
+        pytest.skip("torch CPU generator stream differs from the one that made the fixture")
+    gs, il, cap, elems, disp = O.moe_encode(x, gate, np.zeros(E, np.int32), 1.0)
+    assert sha(disp) == str(rec["sha_disp"])
+    assert (il[0] < 0).sum() == 45
+
+
+def test_loop_port_equals_vectorised():
+    rng = np.random.default_rng(5)
+    for k in (1, 2):
+        S, E, M = 96, 4, 8
+        gate = rng.random((S, E), dtype=np.float32)
+        x = rng.standard_normal((S, M)).astype(np.float32)
+        C = O.capacity(S, E, 1.0, k)
+        cap0 = np.array([0, 3, 0, 10], np.int32)
+        a = O.loops_encode(x, gate, cap0, C, k)
+        gs, il, cap, el = O.moe_gate(gate, cap0, C, M, k)
+        d = O.moe_encode_fwd(il, x, E, C, cap0)
+        for u, v in zip(a, (gs, il, cap, el, d)):
+            np.testing.assert_array_equal(u, v)
+        eo = rng.standard_normal((E, C, M)).astype(np.float32)
+        np.testing.assert_allclose(O.loops_decode(eo, gs, il), O.moe_decode_fwd(eo, gs, il), rtol=1e-6, atol=1e-6)
+
+
+@pytest.mark.parametrize("S,E", [(1024, 32), (2048, 64), (1000, 7)])
+def test_invariants(S, E):
+    """Invariants of tests/python/op/cuda/test_cuda_moe.py:119-137, :377-381."""
+    rng = np.random.default_rng(S + E)
+    M = 8
+    for k in (1, 2):
+        gate = rng.random((S, E), dtype=np.float32)
+        x = rng.standard_normal((S, M)).astype(np.float32)
+        cap0 = rng.integers(0, 3, E).astype(np.int32)
+        C = O.capacity(S, E, 1.0, k)
+        gs, il, cap, el = O.moe_gate(gate, cap0, C, M, k)
+        kept_rows = set()
+        for j in range(k):
+            idx, loc = il[2 * j], il[2 * j + 1]
+            ok = idx >= 0
+            assert np.all(loc[ok] < C - cap0[idx[ok]])
+            for e, l in zip(idx[ok], loc[ok]):
+                assert (e, l) not in kept_rows
+                kept_rows.add((e, l))
+        for e in range(E):
+            locs = sorted(l for (ee, l) in kept_rows if ee == e)
+            assert locs == list(range(len(locs)))
+            assert len(locs) == cap[e] - cap0[e]
+            assert el[e] == (cap[e] - cap0[e]) * M
+        disp = O.moe_encode_fwd(il, x, E, C, cap0)
+        out = O.moe_decode_fwd(disp, gs, il)
+        want = np.zeros_like(x)
+        for j in range(k):
+            ok = il[2 * j] >= 0
+            want[ok] += gs[j][ok][:, None] * x[ok]
+        np.testing.assert_allclose(out, want, rtol=1e-6, atol=1e-6)
+
+
+@pytest.mark.parametrize("n", [2, 4])
+def test_partitioned_encode_merge_equals_unpartitioned(n):
+    """tests/python/op/cuda/test_cuda_moe.py:387-471: chained moe_encode(cf*n) +
+    merge_masks + redispatch == one moe_encode(cf) after masking."""
+    rng = np.random.default_rng(n)
+    S, M, E = 1024, 16, 2
+    x = rng.standard_normal((S, M)).astype(np.float32)
+    gate = (x @ rng.standard_normal((M, E)).astype(np.float32)).astype(np.float32)
+    rg, ril, rcap, _, rd = O.moe_encode(x, gate, np.zeros(E, np.int32), 1.0)
+    cap = np.zeros(E, np.int32)
+    ils, ds, gss = [], [], []
+    for i in range(n):
+        sl = slice(i * S // n, (i + 1) * S // n)
+        g, il, cap, _, d = O.moe_encode(x[sl], gate[sl], cap, float(n))
+        ils.append(il); ds.append(d); gss.append(g[0])
+    mil = O.moe_merge_masks(ils, E)
+    md = O.moe_redispatch(ds, ils)
+    ril = ril.copy()
+    ril[1][ril[0] < 0] = -1
+    np.testing.assert_array_equal(mil, ril)
+    for e in range(E):
+        kept = int((ril[0] == e).sum())
+        np.testing.assert_array_equal(md[e, :kept], rd[e, :kept])
+    np.testing.assert_array_equal(np.concatenate(gss), rg[0])
+
+
+def test_bpr_matches_embedded_reference_oracle():
+    """Restates the loop oracle of tests/python/op/cuda/test_cuda_moe.py:184-222
+    (its per-expert counters) and compares the vectorised version with it."""
+    rng = np.random.default_rng(0)
+    S_orig, E, M, n = 512, 8, 4, 2
+    gate = rng.random((S_orig, E), dtype=np.float32)
+    x = rng.standard_normal((S_orig, M)).astype(np.float32)
+    for pid in range(n):
+        C = O.bpr_capacity(S_orig, E, n, float(n))
+        gs, il, cap, el, d = O.moe_encode_bpr(x, gate, n, pid, float(n))
+        idx = np.argmax(gate, axis=1)
+        g = gate[np.arange(S_orig), idx]
+        order = np.argsort(-g, kind="stable")
+        cnt = {}
+        dropped = np.zeros(S_orig, bool)
+        for s in order:
+            if cnt.get(idx[s], 0) < C:
+                cnt[idx[s]] = cnt.get(idx[s], 0) + 1
+            else:
+                dropped[s] = True
+        S = S_orig // n
+        cnt2 = {}
+        for i in range(S):
+            s = pid * S + i
+            if dropped[s]:
+                assert il[0, i] == -1 and il[1, i] == -1
+            else:
+                assert il[0, i] == idx[s] and il[1, i] == cnt2.get(idx[s], 0)
+                cnt2[idx[s]] = cnt2.get(idx[s], 0) + 1
+                np.testing.assert_array_equal(d[idx[s], il[1, i]], x[s])
+        for e in range(E):
+            assert cap[e] == cnt2.get(e, 0) and el[e] == cnt2.get(e, 0) * M
+
+
+def test_all_to_all_pattern():
+    """tests/python/distributed/test_alltoall.py:51-58 and :105-122."""
+    W = 4
+    bufs = [np.full((W, 4), r + 1, np.float32) for r in range(W)]
+    outs = O.all_to_all(bufs)
+    for r in range(W):
+        np.testing.assert_array_equal(outs[r], np.arange(1, W + 1, dtype=np.float32)[:, None] * np.ones((1, 4)))
+    back = O.all_to_all(O.all_to_all([np.arange(W * 6, dtype=np.float32).reshape(W, 6) + 100 * r for r in range(W)]))
+    for r in range(W):
+        np.testing.assert_array_equal(back[r], np.arange(W * 6, dtype=np.float32).reshape(W, 6) + 100 * r)
+    nch = 2
+    bufs = [np.arange(W * nch * 5, dtype=np.float32).reshape(W, nch * 5) + 1000 * r for r in range(W)]
+    sc = [np.array([(i + j + r) % 4 + 1 for i in range(W) for j in range(nch)], np.uint64) for r in range(W)]
+    outs, rcs = O.all_to_allv(bufs, sc, nch)
+    for r in range(W):
+        o = outs[r].reshape(W, nch, 5)
+        for i in range(W):
+            for j in range(nch):
+                c = int(sc[i][r * nch + j])
+                assert rcs[r][i * nch + j] == c
+                np.testing.assert_array_equal(o[i, j, :c], bufs[i].reshape(W, nch, 5)[r, j, :c])
+                assert np.all(o[i, j, c:] == 0)
