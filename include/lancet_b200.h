@@ -1,0 +1,133 @@
+/*
+ * lancet_b200.h - C ABI of the B200-native MoE data-parallel hot path.
+ *
+ * Every entry point is `extern "C"`, takes plain device pointers and sizes, returns an int
+ * status (0 = ok) and only enqueues work on the stream it is given: nothing here allocates
+ * device memory or synchronises the device.  Outputs and workspaces are owned by the
+ * caller (in RAF: by the executor, see include/raf/op.h:55-91 and src/requests.h:17-52 of
+ * the reference).  Arguments are validated before anything is launched; an invalid call
+ * launches nothing and `lancet_last_error()` describes the reason.
+ *
+ * Each declaration cites the reference interface it replaces (path inside the reference
+ * project : line).
+ *
+ * Conventions: S tokens, E experts, M model dim, C capacity rows per expert, k choices per
+ * token (1 or 2).  `idx_loc` is int32 [2k, S]: rows (2j, 2j+1) are the expert index (-1 when
+ * dropped) and the location of choice j; for k = 1 this is the reference's
+ * `indices_locations[2, S]`.  `gates_s` is [k, S].
+ */
+#ifndef LANCET_B200_H_
+#define LANCET_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* lancet_stream_t; /* a cudaStream_t */
+typedef void* lancet_comm_t;   /* an opaque communicator made by lancet_comm_init_rank */
+
+enum { LANCET_F32 = 0, LANCET_F16 = 1, LANCET_BF16 = 2 };
+
+enum {
+  LANCET_OK = 0,
+  LANCET_ERR_INVALID = 1,     /* bad shape, dtype, size, alignment or flag */
+  LANCET_ERR_NULL = 2,        /* a required pointer is null */
+  LANCET_ERR_CUDA = 3,        /* a CUDA runtime call or launch failed */
+  LANCET_ERR_TIMEOUT = 4,     /* a bounded device-side wait ran out (peer never arrived) */
+  LANCET_ERR_COMM = 5,        /* NCCL missing or an NCCL call failed */
+  LANCET_ERR_UNSUPPORTED = 6
+};
+
+/* flags of lancet_moe_encode_fwd / lancet_moe_encode */
+enum {
+  LANCET_ENCODE_GLOBAL_LOC = 1, /* write row in_capused[e] + loc (one shared buffer for chained chunks) */
+  LANCET_ENCODE_NO_ZERO = 2     /* do not zero rows that no token owns */
+};
+
+const char* lancet_last_error(void);      /* thread-local text of the last failure */
+const char* lancet_version(void);
+int lancet_abi_version(void);
+
+/* C = (int)(cf * ((k*S + E - 1) / E)).  Replaces the inline formula of
+ * src/op/declare/moe.cc:46 and src/op/dialect/cuda/moe.cc:110 (k = 1). */
+int lancet_moe_capacity(int S, int E, float capacity_factor, int k);
+
+/* ---- gating with capacity slot assignment -------------------------------------------------
+ * Replaces the three TVM helper kernels of MoeEncode (src/op/dialect/cuda/moe.cc:177-250,
+ * :366-371: argmax, one_hot, sum(gate*mask)) and launch_gen_location
+ * (src/op/dialect/cuda/kernels/kernel_util.cuh:59, tutel_moe_dispatch.cu:164-212, :548-553).
+ * gate [S,E] in gate_dtype; in_capused [E] may be null (= zeros).  Outputs: gates_s [k,S] in
+ * gates_dtype, idx_loc [2k,S], out_capused [E], out_elems [E] (elements sent per expert).
+ * ws: lancet_moe_gate_workspace_bytes(S,E,k) bytes of scratch, 16-byte aligned. */
+size_t lancet_moe_gate_workspace_bytes(int S, int E, int k);
+int lancet_moe_gate(const void* gate, int gate_dtype, int S, int E, int k, const int32_t* in_capused,
+                    int C, int M, void* out_gates_s, int gates_dtype, int32_t* out_idx_loc,
+                    int32_t* out_capused, uint64_t* out_elems, void* ws, size_t ws_bytes,
+                    lancet_stream_t stream);
+
+/* ---- dispatch: scatter token rows into the [E,C,M] expert buffer ---------------------------
+ * Replaces launch_encode_forward (kernel_util.cuh:36-39; tutel_moe_dispatch.cu:61-86, :461-484).
+ * rows_hi/rows_lo (both nullable, int32 [E]): when rows_hi is given, expert e owns rows
+ * [0, rows_hi[e] - rows_lo[e]) and only the rows past that are zeroed (no full-buffer memset);
+ * when null the whole buffer is zeroed first, as the reference does. */
+int lancet_moe_encode_fwd(const int32_t* idx_loc, int k, const int32_t* in_capused, const int32_t* rows_hi,
+                          const int32_t* rows_lo, const void* x, void* dispatched, int S, int M, int C, int E,
+                          int dtype, int flags, lancet_stream_t stream);
+
+/* Zero rows [used[e], C) of every expert (finishes a LANCET_ENCODE_GLOBAL_LOC chain). */
+int lancet_moe_zero_tail(void* dispatched, const int32_t* used, int M, int C, int E, int dtype,
+                         lancet_stream_t stream);
+
+/* The whole `raf.op.cuda.moe_encode` op (src/op/dialect/cuda/moe.cc:351-396; outputs as
+ * src/op/declare/moe.cc:48-57): gating, then dispatch.  C is computed from capacity_factor. */
+int lancet_moe_encode(const void* x, const void* gate, int gate_dtype, const int32_t* in_capused,
+                      float capacity_factor, int S, int M, int E, int k, int dtype, void* out_gates_s,
+                      int gates_dtype, int32_t* out_idx_loc, int32_t* out_capused, uint64_t* out_elems,
+                      void* dispatched, void* ws, size_t ws_bytes, int flags, lancet_stream_t stream);
+
+/* ---- combine and the four gradient ops -----------------------------------------------------
+ * launch_decode_forward (kernel_util.cuh:44-45; tutel_moe_dispatch.cu:110-116, :511-518). */
+int lancet_moe_decode_fwd(const void* gates_s, int gates_dtype, const int32_t* idx_loc, int k,
+                          const void* expert_out, void* out, int S, int M, int C, int E, int dtype,
+                          lancet_stream_t stream);
+/* launch_encode_backward_data (kernel_util.cuh:40-41; tutel_moe_dispatch.cu:88-94, :486-493). */
+int lancet_moe_encode_bwd_data(const int32_t* idx_loc, int k, const void* dy_dispatched, void* dx, int S,
+                               int M, int C, int E, int dtype, lancet_stream_t stream);
+/* launch_encode_backward_gate (kernel_util.cuh:42-43; tutel_moe_dispatch.cu:96-108, :498-506).
+ * gate is read only for k = 2 (Jacobian of the normalisation). */
+int lancet_moe_encode_bwd_gate(const void* dy_gates_s, int gates_dtype, const int32_t* idx_loc, int k,
+                               const void* gate, int gate_dtype, void* dgate, int S, int E,
+                               lancet_stream_t stream);
+/* launch_decode_backward_data (kernel_util.cuh:46-47; tutel_moe_dispatch.cu:118-124, :523-531).
+ * rows_used nullable: as rows_hi above. */
+int lancet_moe_decode_bwd_data(const void* gates_s, int gates_dtype, const int32_t* idx_loc, int k,
+                               const void* dy, void* d_expert, const int32_t* rows_used, int S, int M, int C,
+                               int E, int dtype, lancet_stream_t stream);
+/* launch_decode_backward_gate (kernel_util.cuh:48-49; tutel_moe_dispatch.cu:126-160, :536-543). */
+int lancet_moe_decode_bwd_gate(const int32_t* idx_loc, int k, const void* dy, const void* expert_out,
+                               void* dgates_s, int gates_dtype, int S, int M, int C, int E, int dtype,
+                               lancet_stream_t stream);
+
+/* ---- LANS optimizer ---------------------------------------------------------------------------
+ * Replaces multi_tensor_lans_cuda (kernel_util.cuh:26-34; multi_tensor_lans.cu:401-450) and the
+ * host side of LansImpl::Execute (src/op/dialect/cuda/lans.cc:92-148).  g/p/m/v are HOST arrays of
+ * n_tensors device pointers (float32 tensors, updated in place except g), numels a host array.
+ * `step` is the 1-based step count as a host integer (the reference reads it back from the
+ * device, lans.cc:102-107); bias corrections are computed from it on the host (lans.cc:108-117).
+ * ws: lancet_lans_workspace_bytes() bytes, 16-byte aligned, kept by the caller between steps.
+ * With LANCET_LANS_TABLES_READY the tensor table uploaded by an earlier call with the same
+ * pointers, sizes and workspace is reused and the call is launch-only. */
+enum { LANCET_LANS_TABLES_READY = 1 };
+size_t lancet_lans_workspace_bytes(int n_tensors, const int64_t* numels);
+int lancet_lans(void* ws, size_t ws_bytes, int n_tensors, const int64_t* numels, void* const* g, void* const* p,
+                void* const* m, void* const* v, int dtype, int step, float lr, float beta1, float beta2, float eps,
+                int bias_correction, float weight_decay, int grad_averaging, int mode, int normalize_grad, int flags,
+                lancet_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LANCET_B200_H_ */

@@ -1,0 +1,95 @@
+"""ctypes binding of the C ABI declared in include/lancet_b200.h.
+
+The library is the product: there is no Python or CPU fallback.  `lib()` raises if the
+shared object has not been built (run `python -m lancet_b200.build` or `__graft_entry__.build()`).
+"""
+import ctypes
+import os
+import re
+
+from . import build as _build
+
+_LIB = None
+
+c_void_p = ctypes.c_void_p
+c_int = ctypes.c_int
+c_float = ctypes.c_float
+c_size_t = ctypes.c_size_t
+c_i64 = ctypes.c_int64
+
+HEADER = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "include", "lancet_b200.h")
+
+# name -> (restype, argtypes).  Kept next to the header; tests check that both list the same names.
+SIGNATURES = {
+    "lancet_last_error": (ctypes.c_char_p, []),
+    "lancet_version": (ctypes.c_char_p, []),
+    "lancet_abi_version": (c_int, []),
+    "lancet_moe_capacity": (c_int, [c_int, c_int, c_float, c_int]),
+    "lancet_moe_gate_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "lancet_moe_gate": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int,
+                                c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "lancet_moe_encode_fwd": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                      c_int, c_int, c_int, c_int, c_void_p]),
+    "lancet_moe_zero_tail": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
+    "lancet_moe_encode": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int,
+                                  c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_int,
+                                  c_void_p]),
+    "lancet_moe_decode_fwd": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                      c_int, c_void_p]),
+    "lancet_moe_encode_bwd_data": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                           c_void_p]),
+    "lancet_moe_encode_bwd_gate": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int,
+                                           c_void_p]),
+    "lancet_moe_decode_bwd_data": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                           c_int, c_int, c_int, c_void_p]),
+    "lancet_moe_decode_bwd_gate": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                           c_int, c_int, c_void_p]),
+    "lancet_lans_workspace_bytes": (c_size_t, [c_int, ctypes.POINTER(c_i64)]),
+    "lancet_lans": (c_int, [c_void_p, c_size_t, c_int, ctypes.POINTER(c_i64), ctypes.POINTER(c_void_p),
+                            ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), c_int, c_int,
+                            c_float, c_float, c_float, c_float, c_int, c_float, c_int, c_int, c_int, c_int, c_void_p]),
+}
+
+F32, F16, BF16 = 0, 1, 2
+OK = 0
+ENCODE_GLOBAL_LOC, ENCODE_NO_ZERO = 1, 2
+LANS_TABLES_READY = 1
+
+
+class LancetError(RuntimeError):
+    def __init__(self, code, text):
+        super().__init__("lancet_b200 error %d: %s" % (code, text))
+        self.code = code
+
+
+def header_symbols():
+    """Names of all functions declared in include/lancet_b200.h."""
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(lancet_[a-z0-9_]+)\s*\(", text)))
+
+
+def lib_path():
+    return _build.LIB_PATH
+
+
+def lib():
+    global _LIB
+    if _LIB is None:
+        path = lib_path()
+        if not os.path.exists(path):
+            raise ImportError(
+                "lancet_b200: %s is missing. Build it with `python -m lancet_b200.build`; there is no fallback path."
+                % path)
+        handle = ctypes.CDLL(path, mode=ctypes.RTLD_GLOBAL)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype = res
+            fn.argtypes = args
+        _LIB = handle
+    return _LIB
+
+
+def check(status):
+    if status != OK:
+        raise LancetError(status, lib().lancet_last_error().decode("utf-8", "replace"))

@@ -1,0 +1,242 @@
+"""Host-side mirror of the reference's operator surface for the MoE hot path.
+
+Function names, argument order and meaning follow the RAF op schemas
+(scripts/src_codegen/def_schema.py:642-716 and :726-742 of the reference):
+`moe_encode(data, gate, used_capacity, capacity_factor)`, `moe_decode(data, gate,
+indices_locations)`, `moe_encode_dx(dy, indices_locations)`, `moe_encode_dg(dy,
+indices_locations, n_experts)`, `moe_decode_dx(dy, gate, indices_locations, n_experts,
+capacity)`, `moe_decode_dg(dy, data, indices_locations)`, `lans(tensor_list, step, ...)`.
+torch supplies device memory and the current stream only; all arithmetic runs in the CUDA
+library behind the C ABI.  Extra keyword arguments (k, gates dtype) extend the surface to the
+top-2 gate; their defaults reproduce the reference ops.
+"""
+import ctypes
+
+import torch
+
+from . import _capi
+from ._capi import check
+
+_DT = {torch.float32: _capi.F32, torch.float16: _capi.F16, torch.bfloat16: _capi.BF16}
+_workspaces = {}
+
+
+def _dt(t):
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise TypeError("lancet_b200: unsupported dtype %s (float32, float16, bfloat16)" % t.dtype)
+
+
+def _ptr(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else None
+
+
+def _stream(t):
+    return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def _require_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise ValueError("lancet_b200 ops need CUDA tensors (there is no CPU path)")
+        if t is not None and not t.is_contiguous():
+            raise ValueError("lancet_b200 ops need contiguous tensors")
+
+
+def workspace(device, nbytes, tag="default"):
+    """A cached, 256-byte aligned scratch tensor per (device, tag), grown on demand."""
+    key = (device, tag)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def moe_capacity(S, E, capacity_factor=1.0, k=1):
+    return _capi.lib().lancet_moe_capacity(S, E, capacity_factor, k)
+
+
+def moe_gate(gate, used_capacity, capacity, M, k=1, gates_dtype=torch.float32):
+    """Gating only: returns (gates_s [k,S], indices_locations [2k,S], capused [E], elements [E] uint64)."""
+    _require_cuda(gate, used_capacity)
+    S, E = gate.shape
+    dev = gate.device
+    gates_s = torch.empty((k, S), dtype=gates_dtype, device=dev)
+    idx_loc = torch.empty((2 * k, S), dtype=torch.int32, device=dev)
+    capused = torch.empty((E,), dtype=torch.int32, device=dev)
+    elems = torch.empty((E,), dtype=torch.uint64, device=dev)
+    L = _capi.lib()
+    nws = L.lancet_moe_gate_workspace_bytes(S, E, k)
+    ws = workspace(dev, nws, "gate")
+    check(L.lancet_moe_gate(_ptr(gate), _dt(gate), S, E, k, _ptr(used_capacity), capacity, M, _ptr(gates_s),
+                            _DT[gates_dtype], _ptr(idx_loc), _ptr(capused), _ptr(elems), _ptr(ws), ws.numel(),
+                            _stream(gate)))
+    return gates_s, idx_loc, capused, elems
+
+
+def moe_encode(data, gate, used_capacity, capacity_factor=1.0, k=1, gates_dtype=None, out=None, flags=0):
+    """`raf.op.moe_encode`: returns (gates_s, indices_locations, used_capacity, elements_per_expert,
+    dispatched [E,C,M]).  For k=1 gates_s has shape [S] and indices_locations [2,S] as in the reference."""
+    _require_cuda(data, gate, used_capacity)
+    S, M = data.shape
+    E = gate.shape[1]
+    if gate.shape[0] != S:
+        raise ValueError("Input data and gate should have matching shape in dim 0.")
+    dev = data.device
+    gates_dtype = gates_dtype or torch.float32
+    L = _capi.lib()
+    C = L.lancet_moe_capacity(S, E, capacity_factor, k)
+    gates_s = torch.empty((k, S), dtype=gates_dtype, device=dev)
+    idx_loc = torch.empty((2 * k, S), dtype=torch.int32, device=dev)
+    capused = torch.empty((E,), dtype=torch.int32, device=dev)
+    elems = torch.empty((E,), dtype=torch.uint64, device=dev)
+    disp = out if out is not None else torch.empty((E, C, M), dtype=data.dtype, device=dev)
+    nws = L.lancet_moe_gate_workspace_bytes(S, E, k)
+    ws = workspace(dev, nws, "gate")
+    check(L.lancet_moe_encode(_ptr(data), _ptr(gate), _dt(gate), _ptr(used_capacity), capacity_factor, S, M, E, k,
+                              _dt(data), _ptr(gates_s), _DT[gates_dtype], _ptr(idx_loc), _ptr(capused), _ptr(elems),
+                              _ptr(disp), _ptr(ws), ws.numel(), flags, _stream(data)))
+    if k == 1:
+        gates_s = gates_s[0]
+    return gates_s, idx_loc, capused, elems, disp
+
+
+def moe_encode_fwd(indices_locations, data, n_experts, capacity, used_capacity=None, rows_hi=None, rows_lo=None,
+                   out=None, flags=0):
+    """Dispatch only (launch_encode_forward of the reference)."""
+    _require_cuda(indices_locations, data)
+    S, M = data.shape
+    k = indices_locations.shape[0] // 2
+    disp = out if out is not None else torch.empty((n_experts, capacity, M), dtype=data.dtype, device=data.device)
+    check(_capi.lib().lancet_moe_encode_fwd(_ptr(indices_locations), k, _ptr(used_capacity), _ptr(rows_hi),
+                                            _ptr(rows_lo), _ptr(data), _ptr(disp), S, M, capacity, n_experts,
+                                            _dt(data), flags, _stream(data)))
+    return disp
+
+
+def moe_zero_tail(dispatched, used):
+    E, C, M = dispatched.shape
+    check(_capi.lib().lancet_moe_zero_tail(_ptr(dispatched), _ptr(used), M, C, E, _dt(dispatched), _stream(dispatched)))
+    return dispatched
+
+
+def _k_of(indices_locations):
+    return indices_locations.shape[0] // 2
+
+
+def moe_decode(data, gate, indices_locations, out=None):
+    """`raf.op.moe_decode`: data [E,C,M] expert output, gate = gates_s, returns [S,M]."""
+    _require_cuda(data, gate, indices_locations)
+    E, C, M = data.shape
+    S = indices_locations.shape[1]
+    k = _k_of(indices_locations)
+    res = out if out is not None else torch.empty((S, M), dtype=data.dtype, device=data.device)
+    check(_capi.lib().lancet_moe_decode_fwd(_ptr(gate), _dt(gate), _ptr(indices_locations), k, _ptr(data), _ptr(res),
+                                            S, M, C, E, _dt(data), _stream(data)))
+    return res
+
+
+def moe_encode_dx(dy, indices_locations):
+    """`raf.op.moe_encode_dx`: dy [E,C,M] -> dx [S,M]."""
+    _require_cuda(dy, indices_locations)
+    E, C, M = dy.shape
+    S = indices_locations.shape[1]
+    dx = torch.empty((S, M), dtype=dy.dtype, device=dy.device)
+    check(_capi.lib().lancet_moe_encode_bwd_data(_ptr(indices_locations), _k_of(indices_locations), _ptr(dy), _ptr(dx),
+                                                 S, M, C, E, _dt(dy), _stream(dy)))
+    return dx
+
+
+def moe_encode_dg(dy, indices_locations, n_experts, gate=None):
+    """`raf.op.moe_encode_dg`: dy = gradient of gates_s -> dgate [S,E] in dy's dtype (k=1).
+    For k=2 the gate matrix is needed (Jacobian of the normalisation); dgate has gate's dtype."""
+    _require_cuda(dy, indices_locations, gate)
+    S = indices_locations.shape[1]
+    k = _k_of(indices_locations)
+    if k == 2 and gate is None:
+        raise ValueError("moe_encode_dg with k=2 needs the gate matrix")
+    out_dtype = gate.dtype if gate is not None else dy.dtype
+    dgate = torch.empty((S, n_experts), dtype=out_dtype, device=dy.device)
+    check(_capi.lib().lancet_moe_encode_bwd_gate(_ptr(dy), _dt(dy), _ptr(indices_locations), k, _ptr(gate),
+                                                 _DT[out_dtype], _ptr(dgate), S, n_experts, _stream(dy)))
+    return dgate
+
+
+def moe_decode_dx(dy, gate, indices_locations, n_experts, capacity, rows_used=None):
+    """`raf.op.moe_decode_dx`: dy [S,M], gate = gates_s -> d_expert [E,C,M]."""
+    _require_cuda(dy, gate, indices_locations, rows_used)
+    S, M = dy.shape
+    out = torch.empty((n_experts, capacity, M), dtype=dy.dtype, device=dy.device)
+    check(_capi.lib().lancet_moe_decode_bwd_data(_ptr(gate), _dt(gate), _ptr(indices_locations), _k_of(indices_locations),
+                                                 _ptr(dy), _ptr(out), _ptr(rows_used), S, M, capacity, n_experts,
+                                                 _dt(dy), _stream(dy)))
+    return out
+
+
+def moe_decode_dg(dy, data, indices_locations, gates_dtype=None):
+    """`raf.op.moe_decode_dg`: dy [S,M], data [E,C,M] -> dgates_s [S] (k=1) or [k,S]."""
+    _require_cuda(dy, data, indices_locations)
+    E, C, M = data.shape
+    S = dy.shape[0]
+    k = _k_of(indices_locations)
+    gates_dtype = gates_dtype or torch.float32
+    out = torch.empty((k, S), dtype=gates_dtype, device=dy.device)
+    check(_capi.lib().lancet_moe_decode_bwd_gate(_ptr(indices_locations), k, _ptr(dy), _ptr(data), _ptr(out),
+                                                 _DT[gates_dtype], S, M, C, E, _dt(dy), _stream(dy)))
+    return out[0] if k == 1 else out
+
+
+class LansState:
+    """Host tables of one LANS parameter group (built once, reused every step)."""
+
+    def __init__(self, grads, params, exp_avg, exp_avg_sq):
+        n = len(params)
+        if not (len(grads) == len(exp_avg) == len(exp_avg_sq) == n):
+            raise ValueError("lans: the four tensor lists must have the same length")
+        _require_cuda(*grads, *params, *exp_avg, *exp_avg_sq)
+        for t in list(grads) + list(params) + list(exp_avg) + list(exp_avg_sq):
+            if t.dtype != torch.float32:
+                raise TypeError("lans: only float32 tensors are supported")
+        self.n = n
+        self.device = params[0].device if n else torch.device("cuda")
+        self.numels = (ctypes.c_int64 * max(n, 1))(*[p.numel() for p in params])
+        mk = lambda ts: (ctypes.c_void_p * max(n, 1))(*[t.data_ptr() for t in ts])
+        self.g, self.p, self.m, self.v = mk(grads), mk(params), mk(exp_avg), mk(exp_avg_sq)
+        self.key = tuple(t.data_ptr() for t in list(grads) + list(params) + list(exp_avg) + list(exp_avg_sq))
+        L = _capi.lib()
+        self.ws_bytes = L.lancet_lans_workspace_bytes(n, self.numels) if n else 0
+        self.ws = torch.empty(max(self.ws_bytes, 256), dtype=torch.uint8, device=self.device)
+        self.ready = False
+
+
+_lans_states = {}
+
+
+def lans(tensor_list, step, learning_rate=1e-3, beta1=0.9, beta2=0.999, eps=1e-6, bias_correction=1,
+         weight_decay=0.01, grad_averaging=1, mode=1, normalize_grad=True, state=None):
+    """`raf.op.lans`: tensor_list = g_list + x_list + m_list + v_list (python/raf/optim/lans.py:265 of the
+    reference); parameters, m and v are updated in place and the list is returned.  `step` is a host
+    integer or float (1-based)."""
+    n4 = len(tensor_list)
+    if n4 % 4 != 0:
+        raise ValueError("lans: tensor_list must hold 4 lists of equal length")
+    n = n4 // 4
+    if n == 0:
+        return tensor_list
+    g, p, m, v = (tensor_list[i * n:(i + 1) * n] for i in range(4))
+    if state is None:
+        key = tuple(t.data_ptr() for t in tensor_list)
+        state = _lans_states.get(key)
+        if state is None:
+            state = LansState(g, p, m, v)
+            _lans_states.clear()
+            _lans_states[key] = state
+    flags = _capi.LANS_TABLES_READY if state.ready else 0
+    check(_capi.lib().lancet_lans(_ptr(state.ws), state.ws.numel(), state.n, state.numels, state.g, state.p, state.m,
+                                  state.v, _capi.F32, int(step), learning_rate, beta1, beta2, eps, int(bias_correction),
+                                  weight_decay, int(grad_averaging), int(mode), int(bool(normalize_grad)), flags,
+                                  _stream(p[0])))
+    state.ready = True
+    return tensor_list

@@ -1,0 +1,236 @@
+"""Parity of the CUDA MoE path (through the C ABI) with the CPU oracle and the golden vectors
+made by the reference's own operators.  Integer outputs and fp32 data moves must be bit-exact."""
+import glob
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import lancet_b200 as LB
+from oracle import moe_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+GOLDEN = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "moe_ref_*.npz")))
+TDT = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}
+
+
+def cu(a, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
+    return t.to(dtype) if dtype is not None else t
+
+
+def host(t):
+    if t.dtype == torch.bfloat16:
+        return t.float().cpu().numpy()
+    if t.dtype == torch.uint64:
+        return t.cpu().view(torch.int64).numpy().astype(np.uint64)
+    return t.cpu().numpy()
+
+
+@pytest.mark.parametrize("path", GOLDEN, ids=[os.path.basename(p)[8:-4] for p in GOLDEN])
+def test_golden_reference_vectors(path):
+    rec = np.load(path)
+    S, E, M, C = (int(rec[k]) for k in ("S", "E", "M", "C"))
+    gate = cu(rec["gate"])
+    cap0 = torch.zeros(E, dtype=torch.int32, device=DEV)
+    gs, il, cap, elems = LB.moe_gate(gate, cap0, C, M)
+    np.testing.assert_array_equal(host(il), rec["idx_loc"])
+    np.testing.assert_array_equal(host(cap), rec["capused"])
+    np.testing.assert_array_equal(host(elems).astype(np.int64), rec["elems"])
+    np.testing.assert_array_equal(host(gs)[0], rec["gates_s"])
+    if "x" not in rec.files:
+        return
+    x = cu(rec["x"])
+    g1, il1, cap1, el1, disp = LB.moe_encode(x, gate, cap0, 1.0)
+    np.testing.assert_array_equal(host(il1), rec["idx_loc"])
+    np.testing.assert_array_equal(host(disp), rec["disp"])
+    out = LB.moe_decode(cu(rec["eo"]), g1, il1)
+    np.testing.assert_array_equal(host(out), rec["out"])
+    np.testing.assert_array_equal(host(LB.moe_encode_dx(cu(rec["d_disp"]), il1)), rec["enc_dx"])
+    dg = host(LB.moe_encode_dg(cu(rec["d_gates"]), il1, E))
+    ref_dg = np.zeros((S, E), np.float32)
+    ref_dg[tuple(rec["enc_dg_nnz"])] = rec["enc_dg_val"]
+    np.testing.assert_array_equal(dg, ref_dg)
+    np.testing.assert_array_equal(host(LB.moe_decode_dx(cu(rec["d_out"]), g1, il1, E, C)), rec["dec_dx"])
+    rows_used = cap1
+    np.testing.assert_array_equal(host(LB.moe_decode_dx(cu(rec["d_out"]), g1, il1, E, C, rows_used=rows_used)),
+                                  rec["dec_dx"])
+    np.testing.assert_allclose(host(LB.moe_decode_dg(cu(rec["d_out"]), cu(rec["eo"]), il1)), rec["dec_dg"],
+                               rtol=1e-5, atol=1e-5)
+
+
+def test_config1_from_seed():
+    """S=2048, E=8, M=512 fp32, softmax gate, seed 0 (the reference's CPU-runnable configuration)."""
+    g = torch.Generator().manual_seed(0)
+    gate = torch.softmax(torch.randn(2048, 8, generator=g), dim=1)
+    x = torch.randn(2048, 512, generator=g)
+    want = O.moe_encode(x.numpy(), gate.numpy(), np.zeros(8, np.int32), 1.0)
+    got = LB.moe_encode(x.to(DEV), gate.to(DEV), torch.zeros(8, dtype=torch.int32, device=DEV), 1.0)
+    np.testing.assert_array_equal(host(got[0]), want[0][0])
+    for a, b in zip(got[1:], want[1:]):
+        np.testing.assert_array_equal(host(a), b)
+    out = LB.moe_decode(got[4], got[0], got[1])
+    np.testing.assert_array_equal(host(out), O.moe_decode_fwd(want[4], want[0], want[1]))
+
+
+CASES = [
+    # S, E, M, k, dtype, gate dtype, capacity factor
+    (1024, 32, 128, 1, "f32", "f32", 1.0),
+    (2048, 64, 128, 1, "f32", "f32", 1.0),
+    (1000, 7, 36, 1, "f32", "f32", 1.0),      # ragged: S % E != 0, 16-byte rows
+    (513, 3, 5, 1, "f32", "f32", 2.0),        # rows not a multiple of 16 bytes
+    (300, 5, 7, 2, "f16", "f32", 1.25),       # 2-byte access path
+    (300, 5, 6, 2, "bf16", "f32", 1.25),      # 4-byte access path
+    (4096, 16, 256, 2, "f16", "f32", 1.25),
+    (4096, 2, 64, 2, "f16", "f16", 1.25),     # E = 2: heavy contention; fp16 gate
+    (4096, 16, 256, 2, "bf16", "bf16", 1.0),
+    (1, 4, 8, 1, "f32", "f32", 1.0),
+    (31, 2, 8, 2, "f32", "f32", 1.0),
+    (70000, 8, 8, 1, "f32", "f32", 1.0),      # more than 256 tiles: tile-scan pass
+    (70000, 6, 8, 2, "f16", "f32", 0.5),
+]
+
+
+@pytest.mark.parametrize("S,E,M,k,dt,gdt,cf", CASES)
+def test_encode_decode_and_grads_match_oracle(S, E, M, k, dt, gdt, cf):
+    rng = np.random.default_rng(S * 131 + E * 7 + k)
+    tdt, tgdt = TDT[dt], TDT[gdt]
+    gate_t = torch.softmax(torch.from_numpy(rng.standard_normal((S, E)).astype(np.float32)), dim=1).to(tgdt)
+    x_t = torch.from_numpy(rng.standard_normal((S, M)).astype(np.float32)).to(tdt)
+    cap0 = rng.integers(0, 4, E).astype(np.int32)
+    gate_np = gate_t.float().numpy()           # exact widening of the 16-bit gate
+    x_np = x_t.float().numpy() if dt == "bf16" else x_t.numpy()
+    C = O.capacity(S, E, cf, k)
+    w_gs, w_il, w_cap, w_el = O.moe_gate(gate_np, cap0, C, M, k)
+    w_disp = O.moe_encode_fwd(w_il, x_np, E, C, cap0)
+    gs, il, cap, el, disp = LB.moe_encode(x_t.to(DEV), gate_t.to(DEV), cu(cap0), cf, k=k)
+    assert disp.shape == (E, C, M)
+    np.testing.assert_array_equal(host(il), w_il)
+    np.testing.assert_array_equal(host(cap), w_cap)
+    np.testing.assert_array_equal(host(el), w_el)
+    np.testing.assert_array_equal(host(gs).reshape(k, S), w_gs)      # fp32 gates: bit-exact, k=2 included
+    np.testing.assert_array_equal(host(disp), w_disp)                # data move: bit-exact, padding rows zero
+    # Oracle results are float32 values computed from the widened inputs; rounding them once to the
+    # data dtype (round-to-nearest-even, as the kernels do) must reproduce the device bit for bit.
+    def rnd(a):
+        return torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(tdt).float().numpy()
+
+    def f32(t):
+        return host(t).astype(np.float32)
+
+    # combine on a random expert output
+    eo_t = torch.from_numpy(rng.standard_normal((E, C, M)).astype(np.float32)).to(tdt)
+    eo_np = eo_t.float().numpy()
+    out = LB.moe_decode(eo_t.to(DEV), gs, il)
+    np.testing.assert_array_equal(f32(out), rnd(O.moe_decode_fwd(eo_np, w_gs, w_il)))
+    # gradients
+    dy_t = torch.from_numpy(rng.standard_normal((E, C, M)).astype(np.float32)).to(tdt)
+    dx = LB.moe_encode_dx(dy_t.to(DEV), il)
+    np.testing.assert_array_equal(f32(dx), rnd(O.moe_encode_dx(w_il, dy_t.float().numpy(), S)))
+    do_t = torch.from_numpy(rng.standard_normal((S, M)).astype(np.float32)).to(tdt)
+    do_np = do_t.float().numpy()
+    ddx = LB.moe_decode_dx(do_t.to(DEV), gs, il, E, C)
+    np.testing.assert_array_equal(f32(ddx), rnd(O.moe_decode_dx(w_gs, w_il, do_np, E, C)))
+    rows_used = cu((w_cap - cap0).astype(np.int32))
+    ddx2 = LB.moe_decode_dx(do_t.to(DEV), gs, il, E, C, rows_used=rows_used)
+    np.testing.assert_array_equal(f32(ddx2), f32(ddx))
+    ddg = LB.moe_decode_dg(do_t.to(DEV), eo_t.to(DEV), il)
+    w_ddg = O.moe_decode_dg(w_il, do_np, eo_np)
+    # fp32 accumulation of M products: rel 1e-5 of the sum of magnitudes
+    np.testing.assert_allclose(host(ddg).reshape(k, S), w_ddg, rtol=1e-5, atol=1e-5 * M)
+    dgs = rng.standard_normal((k, S)).astype(np.float32)
+    if k == 1:
+        edg = LB.moe_encode_dg(cu(dgs[0]), il, E)
+        np.testing.assert_array_equal(host(edg), O.moe_encode_dg(dgs, w_il, E))
+    else:
+        edg = LB.moe_encode_dg(cu(dgs), il, E, gate=gate_t.to(DEV))
+        w_edg = O.moe_encode_dg_top2(dgs, w_il, gate_np, E)
+        np.testing.assert_allclose(host(edg).astype(np.float32), w_edg.astype(np.float32),
+                                   rtol=1e-5 if gdt == "f32" else 1e-2, atol=1e-6 if gdt == "f32" else 1e-2)
+
+
+def test_empty_inputs():
+    E, M = 4, 8
+    x = torch.zeros((0, M), device=DEV)
+    gate = torch.zeros((0, E), device=DEV)
+    cap0 = torch.tensor([1, 0, 2, 0], dtype=torch.int32, device=DEV)
+    gs, il, cap, el, disp = LB.moe_encode(x, gate, cap0, 1.0)
+    assert disp.shape == (E, 0, M) and il.shape == (2, 0)
+    np.testing.assert_array_equal(host(cap), [0, 0, 0, 0])   # min(in + 0, C = 0)
+    out = LB.moe_decode(torch.zeros((E, 0, M), device=DEV), gs, il)
+    assert out.shape == (0, M)
+
+
+def test_all_tokens_to_one_expert_and_drops():
+    S, E, M = 512, 4, 16
+    gate = torch.zeros((S, E)); gate[:, 2] = 1.0
+    x = torch.randn(S, M)
+    gs, il, cap, el, disp = LB.moe_encode(x.to(DEV), gate.to(DEV), torch.zeros(E, dtype=torch.int32, device=DEV), 1.0)
+    C = S // E
+    ilh = host(il)
+    assert (ilh[0][:C] == 2).all() and (ilh[0][C:] == -1).all()
+    np.testing.assert_array_equal(ilh[1], np.arange(S))
+    np.testing.assert_array_equal(host(cap), [0, 0, C, 0])
+    np.testing.assert_array_equal(host(disp)[2], x[:C].numpy())
+    assert host(disp)[[0, 1, 3]].sum() == 0
+
+
+def test_ties_pick_first_maximum():
+    gate = torch.tensor([[0.5, 0.5, 0.0], [0.1, 0.4, 0.4], [0.3, 0.3, 0.3]], dtype=torch.float32)
+    for k in (1, 2):
+        C = 4
+        want = O.moe_gate(gate.numpy(), np.zeros(3, np.int32), C, 1, k)
+        got = LB.moe_gate(gate.to(DEV), torch.zeros(3, dtype=torch.int32, device=DEV), C, 1, k=k)
+        np.testing.assert_array_equal(host(got[1]), want[1])
+    assert host(got[1])[0].tolist() == [0, 1, 0] and host(got[1])[2].tolist() == [1, 2, 1]
+
+
+@pytest.mark.parametrize("n,k", [(2, 1), (4, 1), (4, 2)])
+def test_chained_partitions_share_one_buffer(n, k):
+    """n chained moe_encode calls with capacity factor cf*n (reference PartitionMoEEncode,
+    src/pass/dist_optimization/partition_exprs.cc:1709-1795): per-call outputs match the oracle, and
+    the shared-buffer mode (row = used_capacity + location) reproduces merge+redispatch."""
+    rng = np.random.default_rng(n * 10 + k)
+    S, M, E, cf = 2048, 32, 4, 1.0
+    x = rng.standard_normal((S, M)).astype(np.float32)
+    gate = rng.random((S, E), dtype=np.float32)
+    Sp = S // n
+    C = O.capacity(Sp, E, cf * n, k)
+    shared = torch.full((E, C, M), 7.0, device=DEV)
+    cap = np.zeros(E, np.int32)
+    cap_t = torch.zeros(E, dtype=torch.int32, device=DEV)
+    ils, disps = [], []
+    for i in range(n):
+        sl = slice(i * Sp, (i + 1) * Sp)
+        w = O.moe_encode(x[sl], gate[sl], cap, cf * n, k)
+        got = LB.moe_encode(cu(x[sl]), cu(gate[sl]), cap_t, cf * n, k=k)
+        np.testing.assert_array_equal(host(got[1]), w[1])
+        np.testing.assert_array_equal(host(got[2]), w[2])
+        np.testing.assert_array_equal(host(got[3]), w[3])
+        np.testing.assert_array_equal(host(got[4]), w[4])
+        LB.moe_encode_fwd(got[1], cu(x[sl]), E, C, used_capacity=cap_t, out=shared,
+                          flags=LB._capi.ENCODE_GLOBAL_LOC | LB._capi.ENCODE_NO_ZERO)
+        ils.append(w[1]); disps.append(w[4])
+        cap, cap_t = w[2], got[2]
+    LB.moe_zero_tail(shared, cap_t)
+    if k == 1:
+        np.testing.assert_array_equal(host(shared), O.moe_redispatch(disps, ils))
+    want = np.zeros((E, C, M), np.float32)
+    base = np.zeros(E, np.int64)
+    for d, il in zip(disps, ils):
+        for e in range(E):
+            cnt = sum(int(((il[2 * j] == e)).sum()) for j in range(k))
+            want[e, base[e]:base[e] + cnt] = d[e, :cnt]
+            base[e] += cnt
+    np.testing.assert_array_equal(host(shared), want)
+
+
+def test_errors_are_reported_not_launched():
+    x = torch.zeros((8, 4), device=DEV)
+    gate = torch.zeros((8, 1), device=DEV)
+    with pytest.raises(LB.LancetError) as ei:
+        LB.moe_encode(x, gate, torch.zeros(1, dtype=torch.int32, device=DEV), 1.0, k=2)   # E < k
+    assert ei.value.code == 1
+    torch.cuda.synchronize()
