@@ -1,0 +1,383 @@
+"""Benchmark of the MoE data-parallel hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload moe|lans]
+
+Workload "moe" (default, the configuration the headline metric is quoted on): per GPU S=16384
+tokens, M=2048, fp16 tokens, fp32 gate probabilities, E=2*N experts, top-2, capacity factor 1.25,
+dispatch in 4 chained chunks + exchange + combine.  A step is one pass over one batch of seeded
+synthetic tokens.  One JSON line is printed by rank 0.
+"""
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+
+S_TOKENS, M_DIM, TOP_K, CAP_FACTOR, N_CHUNKS = 16384, 2048, 2, 1.25, 4
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return d, "measured"
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the benchmark runs."""
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.tmp = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(gpu_index), "--query-gpu=" + self.FIELDS + ",timestamp",
+                 "--format=csv,noheader,nounits", "-lms", "100"], stdout=self.tmp, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        self.tmp.flush()
+        self.tmp.seek(0)
+        rows = [r.strip().split(", ") for r in self.tmp.read().splitlines() if r.strip()]
+        self.tmp.close()
+        os.unlink(self.tmp.name)
+        return rows
+
+    @staticmethod
+    def summarise(rows):
+        sm, mx, reasons = [], [], set()
+        for r in rows:
+            try:
+                clk, cmax = float(r[1]), float(r[2])
+            except (ValueError, IndexError):
+                continue
+            sm.append(clk)
+            mx.append(cmax)
+            for name, col in (("hw_slowdown", 5), ("hw_thermal_slowdown", 6), ("sw_thermal_slowdown", 7),
+                              ("sw_power_cap", 8)):
+                if len(r) > col and r[col].strip().lower() == "active":
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        # under load = the upper half of the samples (idle samples before/after the region are low)
+        hi = sorted(sm)[len(sm) // 2:]
+        return {"sm_mhz": statistics.median(hi), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def synth_inputs(rank, world, S, M, dtype, device=None, sets=2):
+    """Seeded synthetic tokens ~N(0,1) and softmax(N(0,1) logits) gate probabilities, seed 1000+rank."""
+    E = 2 * world
+    xs, gates = [], []
+    for i in range(sets):
+        g = torch.Generator().manual_seed(1000 + rank + 7919 * i)
+        logits = torch.randn(S, E, generator=g)
+        gates.append(torch.softmax(logits, dim=1))
+        xs.append(torch.randn(S, M, generator=g).to(dtype))
+    return xs, gates
+
+
+def cpu_reference_sample(max_seconds, world=1, tokens=None):
+    """Times the restatement of the reference's torch-CPU operators (per-token loops) on a sample
+    of the workload; returns (tokens_per_s, cores, description, seconds)."""
+    from oracle import moe_oracle as O
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    E = 2 * world
+    # probe speed on 256 tokens, then size the sample
+    def run(S):
+        xs, gates = synth_inputs(0, world, S, M_DIM, torch.float16, sets=1)
+        x, gate = xs[0].numpy(), gates[0].numpy()
+        C = O.capacity(S, E, CAP_FACTOR, TOP_K)
+        t0 = time.perf_counter()
+        gs, il, cap, el, disp = O.loops_encode(x, gate, np.zeros(E, np.int32), C, TOP_K)
+        out = O.loops_decode(disp, gs, il)
+        dt = time.perf_counter() - t0
+        return dt, float(np.abs(out.astype(np.float32)).sum())
+    if tokens is None:
+        dt, _ = run(256)
+        tokens = int(min(S_TOKENS, max(256, 256 * (max_seconds / max(dt, 1e-6)))))
+        tokens = max(256, tokens // 256 * 256)
+    dt, _ = run(tokens)
+    return tokens / dt, cores, "%d of %d tokens/GPU, M=%d, E=%d, top-%d, encode+decode with per-token loops" % (
+        tokens, S_TOKENS, M_DIM, E, TOP_K), dt, tokens
+
+
+def run_reference_arm(args):
+    """--impl reference: the reference's CPU implementation of the path (restated port; the reference
+    itself has no CPU operator that builds without TVM) on the host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    world = args.gpus
+    budget = 100.0 / max(1, args.steps + args.warmup)
+    rate, cores, sample, dt, tokens = cpu_reference_sample(min(20.0, budget), world)
+    for _ in range(max(0, args.warmup - 1)):
+        cpu_reference_sample(0, world, tokens)
+    times = []
+    for _ in range(args.steps):
+        r = cpu_reference_sample(0, world, tokens)
+        times.append(r[3])
+    ms = 1e3 * sum(times) / len(times)
+    value = tokens / (ms / 1e3)
+    line = {
+        "impl": "reference", "metric": "moe_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": moe_config(world),
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def moe_config(world):
+    return {"workload": "moe_dispatch_a2a_combine: S=%d tokens/GPU, M=%d fp16, E=%d, top-%d, cf=%.2f, %d chunks" % (
+        S_TOKENS, M_DIM, 2 * world, TOP_K, CAP_FACTOR, N_CHUNKS),
+        "tokens_per_gpu": S_TOKENS, "model_dim": M_DIM, "experts": 2 * world, "top_k": TOP_K,
+        "capacity_factor": CAP_FACTOR, "chunks": N_CHUNKS,
+        "l2": "inputs rotate over 2 sets; 288 MiB touched per step exceeds the 126 MB L2"}
+
+
+def run_moe(args):
+    import lancet_b200 as LB
+    from lancet_b200 import _capi
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit("bench.py: --gpus %d but WORLD_SIZE=%d (launch with torch.distributed.run for N>1)" % (
+            args.gpus, world))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    L = _capi.lib()
+    E = 2 * world
+    xs_h, gates_h = synth_inputs(rank, world, S_TOKENS, M_DIM, torch.float16)
+    xs = [x.to(dev) for x in xs_h]
+    gates = [g.to(dev) for g in gates_h]
+    if world == 1:
+        plan = LB.ChunkedMoE(S_TOKENS, M_DIM, E, TOP_K, CAP_FACTOR, N_CHUNKS, torch.float16, device=dev)
+    else:
+        plan = LB.DistChunkedMoE(S_TOKENS, M_DIM, TOP_K, CAP_FACTOR, N_CHUNKS, torch.float16, device=dev)
+
+    def step(i):
+        plan.dispatch(xs[i % 2], gates[i % 2])
+        plan.exchange_forward() if world > 1 else None
+        plan.exchange_backward() if world > 1 else None
+        return plan.combine()
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    sync_all()
+    # ---- timed region: K steps, device resident inputs ------------------------------------------
+    kname = b"dispatch_rows_kernel"
+    L.lancet_profile_begin(kname)
+    launches0 = L.lancet_launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for i in range(args.steps):
+        step(i)
+    ev1.record()
+    sync_all()
+    ms_total = ev0.elapsed_time(ev1)
+    launches = L.lancet_launch_count() - launches0
+    k_ms, k_n = ctypes.c_double(0), ctypes.c_longlong(0)
+    _capi.check(L.lancet_profile_end(ctypes.byref(k_ms), ctypes.byref(k_n)))
+    if world > 1:
+        import torch.distributed as dist
+        t = torch.tensor([ms_total], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    ms_step = ms_total / args.steps
+    value = S_TOKENS * world / (ms_step / 1e3)
+
+    # ---- end to end: pinned host inputs in, combined output back, every step ---------------------
+    e2e_steps = max(3, min(args.steps, 50))
+    x_pin = [x.pin_memory() for x in xs_h]
+    g_pin = [g.pin_memory() for g in gates_h]
+    out_pin = torch.empty((S_TOKENS, M_DIM), dtype=torch.float16).pin_memory()
+    x_dev, g_dev = torch.empty_like(xs[0]), torch.empty_like(gates[0])
+
+    def e2e_step(i):
+        x_dev.copy_(x_pin[i % 2], non_blocking=True)
+        g_dev.copy_(g_pin[i % 2], non_blocking=True)
+        plan.dispatch(x_dev, g_dev)
+        if world > 1:
+            plan.exchange_forward()
+            plan.exchange_backward()
+        out_pin.copy_(plan.combine(), non_blocking=True)
+
+    for i in range(3):
+        e2e_step(i)
+    sync_all()
+    ev0.record()
+    for i in range(e2e_steps):
+        e2e_step(i)
+    ev1.record()
+    sync_all()
+    e2e_ms = ev0.elapsed_time(ev1)
+    if world > 1:
+        import torch.distributed as dist
+        t = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_value = S_TOKENS * world / (e2e_ms / e2e_steps / 1e3)
+    clocks = ClockSampler.summarise(sampler.stop()) if sampler else None
+    if rank != 0:
+        return
+    # ---- roofline of the dominant kernel (dispatch scatter) ---------------------------------------
+    peaks, peak_kind = load_peaks()
+    hbm_peak = float(peaks.get("hbm_gbs", FALLBACK_PEAKS["hbm_gbs"]))
+    cap = plan.capused.cpu().numpy()
+    kept_rows = int(cap[-1].sum())                      # rows written by the 4 dispatch launches of a step
+    row_bytes = M_DIM * 2
+    # algorithmic bytes of the dispatch launch (all chunks in one launch): token rows read once, the
+    # whole padded [E,C,M] buffer written once (kept rows + zero rows)
+    bytes_per_launch = S_TOKENS * row_bytes + E * plan.C * row_bytes
+    roof = None
+    if k_n.value > 0:
+        avg_s = k_ms.value / k_n.value / 1e3
+        achieved = bytes_per_launch / avg_s / 1e9
+        roof = {"bound": "hbm", "kernel": kname.decode(), "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
+                "frac": achieved / hbm_peak, "peak_kind": peak_kind, "traffic": None,
+                "bytes_per_launch": bytes_per_launch, "avg_launch_us": avg_s * 1e6, "launches_timed": k_n.value}
+        tr = os.path.join(ROOT, "profiles", "traffic.json")
+        if os.path.exists(tr):
+            with open(tr) as f:
+                roof["traffic"] = json.load(f).get(kname.decode())
+    line = {
+        "metric": "moe_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16", "data": "synthetic", "config": moe_config(world),
+        "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": S_TOKENS * row_bytes + S_TOKENS * E * 4,
+                "d2h_bytes_per_step": S_TOKENS * row_bytes, "steps": e2e_steps},
+        "gpu_launches": int(launches), "clocks": clocks, "roofline": roof,
+        "step_bytes": {"dispatch_read": S_TOKENS * row_bytes, "dispatch_write": E * plan.C * row_bytes,
+                       "combine_read": kept_rows * row_bytes, "combine_write": S_TOKENS * row_bytes},
+    }
+    step_bytes = sum(line["step_bytes"].values())
+    line["step_hbm_frac"] = step_bytes / (ms_step / 1e3) / 1e9 / hbm_peak
+    if world == 1 and not args.no_cpu:
+        rate, cores, sample, _, _ = cpu_reference_sample(15.0, 1)
+        line["cpu_baseline"] = {"value": rate, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample}
+    print(json.dumps(line), flush=True)
+
+
+def lans_shapes():
+    """196 fp32 tensors, 354.6 M elements: GPT-2-medium-like (24 layers x 8 tensors + embeddings + final norm)."""
+    shapes = [(50257, 1024), (1024, 1024)]
+    for _ in range(24):
+        shapes += [(1024, 1024), (1024, 1024), (1024, 1024), (1024, 1024), (4096, 1024), (1024, 4096), (1024,), (1024,)]
+    shapes += [(1024,), (1024,)]
+    return shapes
+
+
+def run_lans(args):
+    import lancet_b200 as LB
+    from lancet_b200 import _capi
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    L = _capi.lib()
+    shapes = lans_shapes()
+    g = torch.Generator(device=dev).manual_seed(0)
+    P = [torch.randn(s, device=dev, generator=g) * 0.02 for s in shapes]
+    G = [torch.randn(s, device=dev, generator=g) * 1e-3 for s in shapes]
+    Mo = [torch.randn(s, device=dev, generator=g) * 1e-4 for s in shapes]
+    V = [torch.rand(s, device=dev, generator=g) * 1e-6 for s in shapes]
+    tl = G + P + Mo + V
+    n_el = sum(p.numel() for p in P)
+    state = LB.LansState(G, P, Mo, V)
+    sampler = ClockSampler(dev.index)
+    for i in range(max(args.warmup, 3)):
+        LB.lans(tl, 10 + i, state=state)
+    torch.cuda.synchronize()
+    L.lancet_profile_begin(b"lans_phase2_kernel")
+    l0 = L.lancet_launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for i in range(args.steps):
+        LB.lans(tl, 20 + i, state=state)
+    ev1.record()
+    torch.cuda.synchronize()
+    ms = ev0.elapsed_time(ev1) / args.steps
+    launches = L.lancet_launch_count() - l0
+    k_ms, k_n = ctypes.c_double(0), ctypes.c_longlong(0)
+    _capi.check(L.lancet_profile_end(ctypes.byref(k_ms), ctypes.byref(k_n)))
+    clocks = ClockSampler.summarise(sampler.stop())
+    peaks, peak_kind = load_peaks()
+    hbm_peak = float(peaks.get("hbm_gbs", FALLBACK_PEAKS["hbm_gbs"]))
+    avg_s = k_ms.value / max(1, k_n.value) / 1e3
+    achieved = 24.0 * n_el / avg_s / 1e9
+    line = {
+        "metric": "lans_elements_per_s", "value": n_el / (ms / 1e3), "unit": "elements/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "lans_step: %d fp32 tensors, %d elements" % (len(shapes), n_el),
+                   "l2": "5.6 GB of state per step exceeds the 126 MB L2"},
+        "gpu_launches": int(launches), "clocks": clocks,
+        "roofline": {"bound": "hbm", "kernel": "lans_phase2_kernel", "achieved": achieved, "peak": hbm_peak,
+                     "unit": "GB/s", "frac": achieved / hbm_peak, "peak_kind": peak_kind, "traffic": None,
+                     "bytes_per_launch": 24.0 * n_el, "avg_launch_us": avg_s * 1e6},
+        "step_hbm_frac": 52.0 * n_el / (ms / 1e3) / 1e9 / hbm_peak,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="moe", choices=["moe", "lans"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
+    if args.workload == "lans":
+        run_lans(args)
+    else:
+        run_moe(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -41,7 +41,14 @@ enum {
   LANCET_ERR_UNSUPPORTED = 6
 };
 
-/* flags of lancet_moe_encode_fwd / lancet_moe_encode */
+/* flag of lancet_moe_gate: locations are written as in_capused[e] + location, i.e. rows of one
+ * buffer shared by all chunks of a chained, partitioned encode (what the reference obtains later
+ * with moe_merge_masks, src/op/dialect/cuda/kernels/tutel_moe_dispatch.cu:214-255) */
+enum { LANCET_GATE_GLOBAL_LOC = 1 };
+
+/* flags of lancet_moe_encode_fwd / lancet_moe_encode.  With LANCET_ENCODE_GLOBAL_LOC,
+ * lancet_moe_encode gates with LANCET_GATE_GLOBAL_LOC and zeroes nothing (finish the chain with
+ * lancet_moe_zero_tail); lancet_moe_encode_fwd adds in_capused[e] to local locations. */
 enum {
   LANCET_ENCODE_GLOBAL_LOC = 1, /* write row in_capused[e] + loc (one shared buffer for chained chunks) */
   LANCET_ENCODE_NO_ZERO = 2     /* do not zero rows that no token owns */
@@ -50,6 +57,13 @@ enum {
 const char* lancet_last_error(void);      /* thread-local text of the last failure */
 const char* lancet_version(void);
 int lancet_abi_version(void);
+/* Number of kernels this library has launched in this process (all threads). */
+unsigned long long lancet_launch_count(void);
+/* Per-kernel timing for benchmarks: between begin and end every launch of a kernel whose name
+ * contains `kernel_substr` is bracketed by a CUDA event pair on its own stream; end waits for
+ * them and returns the summed duration and the number of launches.  Not for concurrent use. */
+int lancet_profile_begin(const char* kernel_substr);
+int lancet_profile_end(double* total_ms, long long* launches);
 
 /* C = (int)(cf * ((k*S + E - 1) / E)).  Replaces the inline formula of
  * src/op/declare/moe.cc:46 and src/op/dialect/cuda/moe.cc:110 (k = 1). */
@@ -65,8 +79,19 @@ int lancet_moe_capacity(int S, int E, float capacity_factor, int k);
 size_t lancet_moe_gate_workspace_bytes(int S, int E, int k);
 int lancet_moe_gate(const void* gate, int gate_dtype, int S, int E, int k, const int32_t* in_capused,
                     int C, int M, void* out_gates_s, int gates_dtype, int32_t* out_idx_loc,
-                    int32_t* out_capused, uint64_t* out_elems, void* ws, size_t ws_bytes,
+                    int32_t* out_capused, uint64_t* out_elems, void* ws, size_t ws_bytes, int flags,
                     lancet_stream_t stream);
+
+/* Gating of n_chunks chained chunks in one pass (the partitioned moe_encode chain of
+ * src/pass/dist_optimization/partition_exprs.cc:1709-1795): chunk c of Sp = S/n_chunks tokens sees
+ * the capacity used by chunks < c.  Layouts: gate [S,E]; gates_s [n][k][Sp]; idx_loc [n][2k][Sp];
+ * out_capused [n][E] (after each chunk); out_elems [n][E].  Results equal n chained
+ * lancet_moe_gate calls. */
+size_t lancet_moe_gate_chained_workspace_bytes(int S, int E, int k, int n_chunks);
+int lancet_moe_gate_chained(const void* gate, int gate_dtype, int S, int E, int k, int n_chunks,
+                            const int32_t* in_capused, int C, int M, void* out_gates_s, int gates_dtype,
+                            int32_t* out_idx_loc, int32_t* out_capused, uint64_t* out_elems, void* ws,
+                            size_t ws_bytes, int flags, lancet_stream_t stream);
 
 /* ---- dispatch: scatter token rows into the [E,C,M] expert buffer ---------------------------
  * Replaces launch_encode_forward (kernel_util.cuh:36-39; tutel_moe_dispatch.cu:61-86, :461-484).
@@ -110,6 +135,24 @@ int lancet_moe_decode_bwd_data(const void* gates_s, int gates_dtype, const int32
 int lancet_moe_decode_bwd_gate(const int32_t* idx_loc, int k, const void* dy, const void* expert_out,
                                void* dgates_s, int gates_dtype, int S, int M, int C, int E, int dtype,
                                lancet_stream_t stream);
+
+/* ---- chunked dispatch / combine (static form of the reference's partitioned encode) ------------
+ * Replaces the chain moe_encode x n -> moe_merge_masks -> moe_redispatch that the reference's
+ * scheduler emits (src/pass/dist_optimization/partition_exprs.cc:1709-1795, :474-594).  S tokens are
+ * split into n_chunks contiguous chunks of Sp = S/n_chunks; chunk i is gated with capacity factor
+ * capacity_factor*n_chunks and the used capacity of chunks < i, and its rows go straight to their
+ * final place in the single [E,C,M] buffer, C = lancet_moe_capacity(Sp, E, cf*n_chunks, k).
+ * Outputs per chunk: gates_s [n][k][Sp], idx_loc [n][2k][Sp] (locations are rows of the shared
+ * buffer), elems [n][E]; capused_chain [n+1][E] (row 0 is zeroed here, row i+1 = after chunk i). */
+size_t lancet_moe_dispatch_chunked_workspace_bytes(int S, int E, int k, int n_chunks);
+int lancet_moe_dispatch_chunked(const void* x, const void* gate, int gate_dtype, float capacity_factor, int S,
+                                int M, int E, int k, int n_chunks, int dtype, void* gates_s, int gates_dtype,
+                                int32_t* idx_loc, int32_t* capused_chain, uint64_t* elems, void* dispatched,
+                                void* ws, size_t ws_bytes, lancet_stream_t stream);
+/* Combine for outputs of lancet_moe_dispatch_chunked: out [S,M]. */
+int lancet_moe_combine_chunked(const void* expert_out, const void* gates_s, int gates_dtype,
+                               const int32_t* idx_loc, int S, int M, int C, int E, int k, int n_chunks, int dtype,
+                               void* out, lancet_stream_t stream);
 
 /* ---- LANS optimizer ---------------------------------------------------------------------------
  * Replaces multi_tensor_lans_cuda (kernel_util.cuh:26-34; multi_tensor_lans.cu:401-450) and the

@@ -24,10 +24,16 @@ SIGNATURES = {
     "lancet_last_error": (ctypes.c_char_p, []),
     "lancet_version": (ctypes.c_char_p, []),
     "lancet_abi_version": (c_int, []),
+    "lancet_launch_count": (ctypes.c_ulonglong, []),
+    "lancet_profile_begin": (c_int, [ctypes.c_char_p]),
+    "lancet_profile_end": (c_int, [ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_longlong)]),
     "lancet_moe_capacity": (c_int, [c_int, c_int, c_float, c_int]),
     "lancet_moe_gate_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
     "lancet_moe_gate": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int,
-                                c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
+                                c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_int, c_void_p]),
+    "lancet_moe_gate_chained_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
+    "lancet_moe_gate_chained": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p,
+                                        c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_int, c_void_p]),
     "lancet_moe_encode_fwd": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                       c_int, c_int, c_int, c_int, c_void_p]),
     "lancet_moe_zero_tail": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
@@ -44,6 +50,12 @@ SIGNATURES = {
                                            c_int, c_int, c_int, c_void_p]),
     "lancet_moe_decode_bwd_gate": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                            c_int, c_int, c_void_p]),
+    "lancet_moe_dispatch_chunked_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
+    "lancet_moe_dispatch_chunked": (c_int, [c_void_p, c_void_p, c_int, c_float, c_int, c_int, c_int, c_int, c_int, c_int,
+                                            c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t,
+                                            c_void_p]),
+    "lancet_moe_combine_chunked": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                           c_int, c_void_p, c_void_p]),
     "lancet_lans_workspace_bytes": (c_size_t, [c_int, ctypes.POINTER(c_i64)]),
     "lancet_lans": (c_int, [c_void_p, c_size_t, c_int, ctypes.POINTER(c_i64), ctypes.POINTER(c_void_p),
                             ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), c_int, c_int,
@@ -53,6 +65,7 @@ SIGNATURES = {
 F32, F16, BF16 = 0, 1, 2
 OK = 0
 ENCODE_GLOBAL_LOC, ENCODE_NO_ZERO = 1, 2
+GATE_GLOBAL_LOC = 1
 LANS_TABLES_READY = 1
 
 

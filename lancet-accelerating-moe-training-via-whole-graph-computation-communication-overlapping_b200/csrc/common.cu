@@ -1,5 +1,9 @@
 #include "common.cuh"
 
+#include <cstring>
+#include <mutex>
+#include <vector>
+
 namespace lancet {
 
 char* error_buffer() {
@@ -13,6 +17,42 @@ int fail(int code, const char* fmt, ...) {
   vsnprintf(error_buffer(), 512, fmt, ap);
   va_end(ap);
   return code;
+}
+
+static unsigned long long g_launches = 0;
+void count_launch() { __atomic_fetch_add(&g_launches, 1ull, __ATOMIC_RELAXED); }
+unsigned long long launches() { return __atomic_load_n(&g_launches, __ATOMIC_RELAXED); }
+
+namespace {
+struct Profiler {
+  std::mutex mu;
+  bool on = false;
+  char pattern[64] = {0};
+  std::vector<cudaEvent_t> events;  // pairs: before, after
+  size_t used = 0;
+};
+Profiler& prof() {
+  static Profiler p;
+  return p;
+}
+}  // namespace
+
+bool prof_enabled_for(const char* name) {
+  Profiler& p = prof();
+  if (!p.on) return false;
+  return std::strstr(name, p.pattern) != nullptr;
+}
+
+void prof_record(cudaStream_t stream, bool after) {
+  Profiler& p = prof();
+  std::lock_guard<std::mutex> lk(p.mu);
+  if (!after && (p.used & 1)) return;  // unbalanced: ignore
+  if (p.used >= p.events.size()) {
+    cudaEvent_t e;
+    if (cudaEventCreate(&e) != cudaSuccess) return;
+    p.events.push_back(e);
+  }
+  cudaEventRecord(p.events[p.used++], stream);
 }
 
 int sm_count() {
@@ -33,6 +73,38 @@ extern "C" {
 const char* lancet_last_error(void) { return lancet::error_buffer(); }
 const char* lancet_version(void) { return "lancet_b200 0.1 (sm_100a)"; }
 int lancet_abi_version(void) { return 1; }
+unsigned long long lancet_launch_count(void) { return lancet::launches(); }
+
+int lancet_profile_begin(const char* kernel_substr) {
+  if (!kernel_substr || !*kernel_substr) return lancet::fail(LANCET_ERR_NULL, "lancet_profile_begin: empty pattern");
+  lancet::Profiler& p = lancet::prof();
+  std::lock_guard<std::mutex> lk(p.mu);
+  std::strncpy(p.pattern, kernel_substr, sizeof(p.pattern) - 1);
+  p.used = 0;
+  p.on = true;
+  return LANCET_OK;
+}
+
+int lancet_profile_end(double* total_ms, long long* launches) {
+  lancet::Profiler& p = lancet::prof();
+  std::lock_guard<std::mutex> lk(p.mu);
+  p.on = false;
+  double tot = 0;
+  long long n = 0;
+  for (size_t i = 0; i + 1 < p.used; i += 2) {
+    cudaError_t e = cudaEventSynchronize(p.events[i + 1]);
+    if (e != cudaSuccess) return lancet::fail(LANCET_ERR_CUDA, "lancet_profile_end: %s", cudaGetErrorString(e));
+    float ms = 0;
+    e = cudaEventElapsedTime(&ms, p.events[i], p.events[i + 1]);
+    if (e != cudaSuccess) return lancet::fail(LANCET_ERR_CUDA, "lancet_profile_end: %s", cudaGetErrorString(e));
+    tot += ms;
+    ++n;
+  }
+  p.used = 0;
+  if (total_ms) *total_ms = tot;
+  if (launches) *launches = n;
+  return LANCET_OK;
+}
 int lancet_moe_capacity(int S, int E, float capacity_factor, int k) {
   if (S < 0 || E <= 0 || k <= 0) return -1;
   // integer ceil-div, float multiply, truncate: src/op/declare/moe.cc:46 of the reference

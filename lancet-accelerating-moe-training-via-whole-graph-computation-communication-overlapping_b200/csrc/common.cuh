@@ -28,7 +28,26 @@ int fail(int code, const char* fmt, ...);
       return ::lancet::fail(LANCET_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(_e)); \
   } while (0)
 
+void count_launch();
+
+// Optional per-kernel timing with CUDA events on the launching stream (see lancet_profile_begin).
+// A ProfScope placed around a launch records an event pair when the kernel name matches the
+// selected pattern; otherwise it costs one branch.
+bool prof_enabled_for(const char* name);
+void prof_record(cudaStream_t stream, bool after);
+struct ProfScope {
+  cudaStream_t s;
+  bool on;
+  ProfScope(const char* name, cudaStream_t stream) : s(stream), on(prof_enabled_for(name)) {
+    if (on) prof_record(s, false);
+  }
+  ~ProfScope() {
+    if (on) prof_record(s, true);
+  }
+};
+
 inline int launch_status(const char* what) {
+  count_launch();
   cudaError_t e = cudaPeekAtLastError();
   if (e != cudaSuccess) {
     cudaGetLastError();
@@ -76,6 +95,17 @@ __device__ __forceinline__ void store_from_float(void* p, int dtype, size_t i, f
   else
     static_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v);
 }
+
+// launchers shared between translation units
+size_t gate_workspace_bytes(int S, int E, int k, int n_chunks);
+int gate_launch(const void* gate, int gate_dtype, int S, int E, int k, int n_chunks, const int32_t* in_capused, int C,
+                int M, void* out_gates_s, int gates_dtype, int32_t* out_idx_loc, int32_t* out_capused,
+                uint64_t* out_elems, void* ws, int global_loc, cudaStream_t stream);
+int dispatch_launch(const int32_t* idx_loc, int k, const int32_t* in_cap, const int32_t* rows_hi, const int32_t* rows_lo,
+                    const void* x, void* out, int S, int Sp, int M, int C, int E, int dtype, int flags,
+                    cudaStream_t stream);
+int combine_launch(const void* gates, int gates_dtype, const int32_t* idx_loc, int k, const void* src, void* out, int S,
+                   int Sp, int M, int C, int E, int dtype, cudaStream_t stream);
 
 }  // namespace lancet
 

@@ -353,11 +353,20 @@ int lancet_lans(void* ws, size_t ws_bytes, int n_tensors, const int64_t* numels,
   float4* norms = reinterpret_cast<float4*>(base + L.norms_off);
   int* counters = reinterpret_cast<int*>(base + L.counters_off);
   const int grid = (int)L.nchunks;
-  lans_phase1_kernel<<<grid, kLansThreads, 0, stream>>>(d_tensors, n_tensors, part1, norms, counters);
+  {
+    ProfScope prof("lans_phase1_kernel", stream);
+    lans_phase1_kernel<<<grid, kLansThreads, 0, stream>>>(d_tensors, n_tensors, part1, norms, counters);
+  }
   if (int st = launch_status("lans_phase1_kernel")) return st;
-  lans_phase2_kernel<<<grid, kLansThreads, 0, stream>>>(d_tensors, n_tensors, h, part2, norms, counters);
+  {
+    ProfScope prof("lans_phase2_kernel", stream);
+    lans_phase2_kernel<<<grid, kLansThreads, 0, stream>>>(d_tensors, n_tensors, h, part2, norms, counters);
+  }
   if (int st = launch_status("lans_phase2_kernel")) return st;
-  lans_phase3_kernel<<<grid, kLansThreads, 0, stream>>>(d_tensors, n_tensors, h, norms);
+  {
+    ProfScope prof("lans_phase3_kernel", stream);
+    lans_phase3_kernel<<<grid, kLansThreads, 0, stream>>>(d_tensors, n_tensors, h, norms);
+  }
   return launch_status("lans_phase3_kernel");
 }
 }

@@ -18,10 +18,17 @@ struct alignas(sizeof(T) * N) Pack {
   T v[N];
 };
 
+// idx_loc is laid out [n_chunks][2K][Sp] (Sp = S for a single chunk): token s of the batch is token
+// s % Sp of chunk s / Sp.  K2 = 2K rows per chunk.
+__device__ __forceinline__ size_t il_index(int s, int Sp, int K2, int row) {
+  const int c = s / Sp;
+  return ((size_t)c * K2 + row) * Sp + (s - c * Sp);
+}
+
 __device__ __forceinline__ bool kept_choice(const int32_t* __restrict__ idx_loc, const int32_t* __restrict__ in_cap,
-                                            int j, int s, int S, int C, int E, bool global_loc, long long* row) {
-  const int idx = idx_loc[(size_t)(2 * j) * S + s];
-  const int loc = idx_loc[(size_t)(2 * j + 1) * S + s];
+                                            int j, int s, int Sp, int K2, int C, int E, bool global_loc, long long* row) {
+  const int idx = idx_loc[il_index(s, Sp, K2, 2 * j)];
+  const int loc = idx_loc[il_index(s, Sp, K2, 2 * j + 1)];
   if (idx < 0 || idx >= E || loc < 0 || loc >= C) return false;
   int used = 0;
   if (in_cap) {
@@ -40,7 +47,7 @@ template <typename V, int K>
 __global__ void __launch_bounds__(kRowThreads)
 dispatch_rows_kernel(const int32_t* __restrict__ idx_loc, const int32_t* __restrict__ in_cap,
                      const int32_t* __restrict__ rows_hi, const int32_t* __restrict__ rows_lo, const V* __restrict__ x,
-                     V* __restrict__ out, int S, int row_vecs, int C, int E, int global_loc, int zero_tail) {
+                     V* __restrict__ out, int S, int Sp, int row_vecs, int C, int E, int global_loc, int zero_tail) {
   constexpr int U = 8;
   const int lane = threadIdx.x & 31;
   const long long gw = (long long)blockIdx.x * kRowWarps + (threadIdx.x >> 5);
@@ -54,7 +61,7 @@ dispatch_rows_kernel(const int32_t* __restrict__ idx_loc, const int32_t* __restr
       bool any = false;
 #pragma unroll
       for (int j = 0; j < K; ++j) {
-        keep[j] = kept_choice(idx_loc, in_cap, j, s, S, C, E, global_loc != 0, &row[j]);
+        keep[j] = kept_choice(idx_loc, in_cap, j, s, Sp, 2 * K, C, E, global_loc != 0, &row[j]);
         any |= keep[j];
       }
       if (!any) continue;
@@ -97,7 +104,7 @@ dispatch_rows_kernel(const int32_t* __restrict__ idx_loc, const int32_t* __restr
 template <typename T, int N, int K>
 __global__ void __launch_bounds__(kRowThreads)
 combine_rows_kernel(const void* __restrict__ gates, int gates_dtype, const int32_t* __restrict__ idx_loc,
-                    const T* __restrict__ src, T* __restrict__ out, int S, int M, int C, int E) {
+                    const T* __restrict__ src, T* __restrict__ out, int S, int Sp, int M, int C, int E) {
   using P = Pack<T, N>;
   const int lane = threadIdx.x & 31;
   const int row_vecs = M / N;
@@ -109,28 +116,44 @@ combine_rows_kernel(const void* __restrict__ gates, int gates_dtype, const int32
     float g[K];
 #pragma unroll
     for (int j = 0; j < K; ++j) {
-      keep[j] = kept_choice(idx_loc, nullptr, j, (int)s, S, C, E, false, &row[j]);
-      g[j] = gates ? load_as_float(gates, gates_dtype, (size_t)j * S + s) : 1.0f;
+      keep[j] = kept_choice(idx_loc, nullptr, j, (int)s, Sp, 2 * K, C, E, false, &row[j]);
+      g[j] = gates ? load_as_float(gates, gates_dtype, il_index((int)s, Sp, K, j)) : 1.0f;
     }
     P* dst = reinterpret_cast<P*>(out + (size_t)s * M);
-    for (int v = lane; v < row_vecs; v += 32) {
-      float acc[N];
-#pragma unroll
-      for (int i = 0; i < N; ++i) acc[i] = 0.f;
+    constexpr int U = 4;  // independent 16-byte loads in flight per lane and choice
+    for (int base = 0; base < row_vecs; base += 32 * U) {
+      P p[K][U];
 #pragma unroll
       for (int j = 0; j < K; ++j) {
         if (!keep[j]) continue;
-        const P p = reinterpret_cast<const P*>(src + (size_t)row[j] * M)[v];
+        const P* srow = reinterpret_cast<const P*>(src + (size_t)row[j] * M);
 #pragma unroll
-        for (int i = 0; i < N; ++i) {
-          const float prod = __fmul_rn(g[j], Num<T>::to_f(p.v[i]));
-          acc[i] = (j == 0 || !keep[0]) ? prod : __fadd_rn(acc[i], prod);
+        for (int u = 0; u < U; ++u) {
+          const int v = base + u * 32 + lane;
+          if (v < row_vecs) p[j][u] = srow[v];
         }
       }
-      P o;
 #pragma unroll
-      for (int i = 0; i < N; ++i) o.v[i] = Num<T>::from_f(acc[i]);
-      dst[v] = o;
+      for (int u = 0; u < U; ++u) {
+        const int v = base + u * 32 + lane;
+        if (v >= row_vecs) continue;
+        float acc[N];
+#pragma unroll
+        for (int i = 0; i < N; ++i) acc[i] = 0.f;
+#pragma unroll
+        for (int j = 0; j < K; ++j) {
+          if (!keep[j]) continue;
+#pragma unroll
+          for (int i = 0; i < N; ++i) {
+            const float prod = __fmul_rn(g[j], Num<T>::to_f(p[j][u].v[i]));
+            acc[i] = (j == 0 || !keep[0]) ? prod : __fadd_rn(acc[i], prod);
+          }
+        }
+        P o;
+#pragma unroll
+        for (int i = 0; i < N; ++i) o.v[i] = Num<T>::from_f(acc[i]);
+        dst[v] = o;
+      }
     }
   }
 }
@@ -158,7 +181,7 @@ scatter_scaled_rows_kernel(const void* __restrict__ gates, int gates_dtype, cons
       bool any = false;
 #pragma unroll
       for (int j = 0; j < K; ++j) {
-        keep[j] = kept_choice(idx_loc, nullptr, j, s, S, C, E, false, &row[j]);
+        keep[j] = kept_choice(idx_loc, nullptr, j, s, S, 2 * K, C, E, false, &row[j]);
         g[j] = load_as_float(gates, gates_dtype, (size_t)j * S + s);
         any |= keep[j];
       }
@@ -206,7 +229,7 @@ rowdot_kernel(const int32_t* __restrict__ idx_loc, int K, const T* __restrict__ 
     const int s = (int)(task % S);
     long long row;
     float sum = 0.f;
-    if (kept_choice(idx_loc, nullptr, j, s, S, C, E, false, &row)) {
+    if (kept_choice(idx_loc, nullptr, j, s, S, 2 * K, C, E, false, &row)) {
       const P* a = reinterpret_cast<const P*>(eo + (size_t)row * M);
       const P* b = reinterpret_cast<const P*>(dy + (size_t)s * M);
       float part[4] = {0.f, 0.f, 0.f, 0.f};
@@ -272,24 +295,26 @@ static int row_grid(long long tasks) {
 
 template <typename V>
 static int dispatch_launch_v(const int32_t* idx_loc, int k, const int32_t* in_cap, const int32_t* rows_hi,
-                             const int32_t* rows_lo, const void* x, void* out, int S, size_t row_bytes, int C, int E,
-                             int global_loc, int zero_tail, cudaStream_t stream) {
+                             const int32_t* rows_lo, const void* x, void* out, int S, int Sp, size_t row_bytes, int C,
+                             int E, int global_loc, int zero_tail, cudaStream_t stream) {
   const int row_vecs = (int)(row_bytes / sizeof(V));
   const long long tasks = (long long)S + (zero_tail ? (long long)E * C : 0);
   const int grid = row_grid(tasks);
+  ProfScope prof("dispatch_rows_kernel", stream);
   if (k == 1)
     dispatch_rows_kernel<V, 1><<<grid, kRowThreads, 0, stream>>>(idx_loc, in_cap, rows_hi, rows_lo,
                                                                  static_cast<const V*>(x), static_cast<V*>(out), S,
-                                                                 row_vecs, C, E, global_loc, zero_tail);
+                                                                 Sp > 0 ? Sp : 1, row_vecs, C, E, global_loc, zero_tail);
   else
     dispatch_rows_kernel<V, 2><<<grid, kRowThreads, 0, stream>>>(idx_loc, in_cap, rows_hi, rows_lo,
                                                                  static_cast<const V*>(x), static_cast<V*>(out), S,
-                                                                 row_vecs, C, E, global_loc, zero_tail);
+                                                                 Sp > 0 ? Sp : 1, row_vecs, C, E, global_loc, zero_tail);
   return launch_status("dispatch_rows_kernel");
 }
 
 int dispatch_launch(const int32_t* idx_loc, int k, const int32_t* in_cap, const int32_t* rows_hi, const int32_t* rows_lo,
-                    const void* x, void* out, int S, int M, int C, int E, int dtype, int flags, cudaStream_t stream) {
+                    const void* x, void* out, int S, int Sp, int M, int C, int E, int dtype, int flags,
+                    cudaStream_t stream) {
   const size_t row_bytes = (size_t)M * dtype_bytes(dtype);
   const int global_loc = (flags & LANCET_ENCODE_GLOBAL_LOC) ? 1 : 0;
   int zero_tail = 0;
@@ -303,41 +328,42 @@ int dispatch_launch(const int32_t* idx_loc, int k, const int32_t* in_cap, const 
   if (S == 0 && !zero_tail) return LANCET_OK;
   if (row_bytes == 0 || (long long)S + (zero_tail ? (long long)E * C : 0) == 0) return LANCET_OK;
   if (row_bytes % 16 == 0 && aligned(x, 16) && aligned(out, 16))
-    return dispatch_launch_v<uint4>(idx_loc, k, in_cap, rows_hi, rows_lo, x, out, S, row_bytes, C, E, global_loc,
+    return dispatch_launch_v<uint4>(idx_loc, k, in_cap, rows_hi, rows_lo, x, out, S, Sp, row_bytes, C, E, global_loc,
                                     zero_tail, stream);
   if (row_bytes % 4 == 0 && aligned(x, 4) && aligned(out, 4))
-    return dispatch_launch_v<uint32_t>(idx_loc, k, in_cap, rows_hi, rows_lo, x, out, S, row_bytes, C, E, global_loc,
+    return dispatch_launch_v<uint32_t>(idx_loc, k, in_cap, rows_hi, rows_lo, x, out, S, Sp, row_bytes, C, E, global_loc,
                                        zero_tail, stream);
-  return dispatch_launch_v<uint16_t>(idx_loc, k, in_cap, rows_hi, rows_lo, x, out, S, row_bytes, C, E, global_loc,
+  return dispatch_launch_v<uint16_t>(idx_loc, k, in_cap, rows_hi, rows_lo, x, out, S, Sp, row_bytes, C, E, global_loc,
                                      zero_tail, stream);
 }
 
 template <typename T>
 static int combine_launch_t(const void* gates, int gates_dtype, const int32_t* idx_loc, int k, const void* src,
-                            void* out, int S, int M, int C, int E, cudaStream_t stream) {
+                            void* out, int S, int Sp, int M, int C, int E, cudaStream_t stream) {
   constexpr int N = 16 / sizeof(T);
   const bool vec = (M % N == 0) && aligned(src, 16) && aligned(out, 16);
   const int grid = row_grid(S);
   const T* s_ = static_cast<const T*>(src);
   T* o_ = static_cast<T*>(out);
+  ProfScope prof("combine_rows_kernel", stream);
   if (vec) {
     if (k == 1)
-      combine_rows_kernel<T, N, 1><<<grid, kRowThreads, 0, stream>>>(gates, gates_dtype, idx_loc, s_, o_, S, M, C, E);
+      combine_rows_kernel<T, N, 1><<<grid, kRowThreads, 0, stream>>>(gates, gates_dtype, idx_loc, s_, o_, S, Sp, M, C, E);
     else
-      combine_rows_kernel<T, N, 2><<<grid, kRowThreads, 0, stream>>>(gates, gates_dtype, idx_loc, s_, o_, S, M, C, E);
+      combine_rows_kernel<T, N, 2><<<grid, kRowThreads, 0, stream>>>(gates, gates_dtype, idx_loc, s_, o_, S, Sp, M, C, E);
   } else {
     if (k == 1)
-      combine_rows_kernel<T, 1, 1><<<grid, kRowThreads, 0, stream>>>(gates, gates_dtype, idx_loc, s_, o_, S, M, C, E);
+      combine_rows_kernel<T, 1, 1><<<grid, kRowThreads, 0, stream>>>(gates, gates_dtype, idx_loc, s_, o_, S, Sp, M, C, E);
     else
-      combine_rows_kernel<T, 1, 2><<<grid, kRowThreads, 0, stream>>>(gates, gates_dtype, idx_loc, s_, o_, S, M, C, E);
+      combine_rows_kernel<T, 1, 2><<<grid, kRowThreads, 0, stream>>>(gates, gates_dtype, idx_loc, s_, o_, S, Sp, M, C, E);
   }
   return launch_status("combine_rows_kernel");
 }
 
 int combine_launch(const void* gates, int gates_dtype, const int32_t* idx_loc, int k, const void* src, void* out, int S,
-                   int M, int C, int E, int dtype, cudaStream_t stream) {
+                   int Sp, int M, int C, int E, int dtype, cudaStream_t stream) {
   if (S == 0 || M == 0) return LANCET_OK;
-  return LANCET_DISPATCH_DTYPE(dtype, combine_launch_t, gates, gates_dtype, idx_loc, k, src, out, S, M, C, E, stream);
+  return LANCET_DISPATCH_DTYPE(dtype, combine_launch_t, gates, gates_dtype, idx_loc, k, src, out, S, Sp, M, C, E, stream);
 }
 
 template <typename T>
@@ -392,11 +418,6 @@ int rowdot_launch(const int32_t* idx_loc, int k, const void* dy, const void* eo,
   return LANCET_DISPATCH_DTYPE(dtype, rowdot_launch_t, idx_loc, k, dy, eo, dgates, gates_dtype, S, M, C, E, stream);
 }
 
-int gate_launch(const void* gate, int gate_dtype, int S, int E, int k, const int32_t* in_capused, int C, int M,
-                void* out_gates_s, int gates_dtype, int32_t* out_idx_loc, int32_t* out_capused, uint64_t* out_elems,
-                void* ws, cudaStream_t stream);
-size_t gate_workspace_bytes(int S, int E, int k);
-
 }  // namespace lancet
 
 extern "C" {
@@ -421,7 +442,7 @@ int lancet_moe_encode_fwd(const int32_t* idx_loc, int k, const int32_t* in_capus
                  "lancet_moe_encode_fwd: LANCET_ENCODE_GLOBAL_LOC needs in_capused");
   LANCET_REQUIRE(aligned(x, dtype_bytes(dtype)) && aligned(dispatched, dtype_bytes(dtype)), LANCET_ERR_INVALID,
                  "lancet_moe_encode_fwd: data pointers are not aligned to the element size");
-  return dispatch_launch(idx_loc, k, in_capused, rows_hi, rows_lo, x, dispatched, S, M, C, E, dtype, flags,
+  return dispatch_launch(idx_loc, k, in_capused, rows_hi, rows_lo, x, dispatched, S, S, M, C, E, dtype, flags,
                          static_cast<cudaStream_t>(stream));
 }
 
@@ -430,7 +451,7 @@ int lancet_moe_zero_tail(void* dispatched, const int32_t* used, int M, int C, in
   LANCET_REQUIRE(used && ((size_t)E * C * M == 0 || dispatched), LANCET_ERR_NULL, "lancet_moe_zero_tail: null pointer argument");
   if ((size_t)E * C * M == 0) return LANCET_OK;
   // token part is empty (S = 0): only the zero-row tasks run
-  return dispatch_launch(nullptr, 1, nullptr, used, nullptr, nullptr, dispatched, 0, M, C, E, dtype, 0,
+  return dispatch_launch(nullptr, 1, nullptr, used, nullptr, nullptr, dispatched, 0, 1, M, C, E, dtype, 0,
                          static_cast<cudaStream_t>(stream));
 }
 
@@ -441,9 +462,14 @@ int lancet_moe_encode(const void* x, const void* gate, int gate_dtype, const int
   LANCET_REQUIRE(E > 0 && (k == 1 || k == 2) && S >= 0, LANCET_ERR_INVALID, "lancet_moe_encode: bad sizes S=%d E=%d k=%d", S, E, k);
   const int C = lancet_moe_capacity(S, E, capacity_factor, k);
   LANCET_REQUIRE(C >= 0, LANCET_ERR_INVALID, "lancet_moe_encode: capacity %d from factor %f is negative", C, capacity_factor);
+  LANCET_REQUIRE((flags & ~3) == 0, LANCET_ERR_INVALID, "lancet_moe_encode: unknown flag bits 0x%x", flags);
+  const int global_loc = flags & LANCET_ENCODE_GLOBAL_LOC;
   int st = lancet_moe_gate(gate, gate_dtype, S, E, k, in_capused, C, M, out_gates_s, gates_dtype, out_idx_loc,
-                           out_capused, out_elems, ws, ws_bytes, stream);
+                           out_capused, out_elems, ws, ws_bytes, global_loc ? LANCET_GATE_GLOBAL_LOC : 0, stream);
   if (st != LANCET_OK) return st;
+  if (global_loc)  // locations already include the used capacity: rows of earlier chunks stay untouched
+    return lancet_moe_encode_fwd(out_idx_loc, k, nullptr, nullptr, nullptr, x, dispatched, S, M, C, E, dtype,
+                                 LANCET_ENCODE_NO_ZERO, stream);
   return lancet_moe_encode_fwd(out_idx_loc, k, in_capused, out_capused, in_capused, x, dispatched, S, M, C, E, dtype,
                                flags, stream);
 }
@@ -454,7 +480,7 @@ int lancet_moe_decode_fwd(const void* gates_s, int gates_dtype, const int32_t* i
   LANCET_REQUIRE(valid_dtype(gates_dtype), LANCET_ERR_INVALID, "lancet_moe_decode_fwd: unknown gates dtype %d", gates_dtype);
   LANCET_REQUIRE(S == 0 || M == 0 || (gates_s && idx_loc && expert_out && out), LANCET_ERR_NULL,
                  "lancet_moe_decode_fwd: null pointer argument");
-  return combine_launch(gates_s, gates_dtype, idx_loc, k, expert_out, out, S, M, C, E, dtype,
+  return combine_launch(gates_s, gates_dtype, idx_loc, k, expert_out, out, S, S, M, C, E, dtype,
                         static_cast<cudaStream_t>(stream));
 }
 
@@ -463,7 +489,7 @@ int lancet_moe_encode_bwd_data(const int32_t* idx_loc, int k, const void* dy_dis
   CHECK_COMMON("lancet_moe_encode_bwd_data", S, M, C, E, k, dtype);
   LANCET_REQUIRE(S == 0 || M == 0 || (idx_loc && dy_dispatched && dx), LANCET_ERR_NULL,
                  "lancet_moe_encode_bwd_data: null pointer argument");
-  return combine_launch(nullptr, LANCET_F32, idx_loc, k, dy_dispatched, dx, S, M, C, E, dtype,
+  return combine_launch(nullptr, LANCET_F32, idx_loc, k, dy_dispatched, dx, S, S, M, C, E, dtype,
                         static_cast<cudaStream_t>(stream));
 }
 

@@ -58,7 +58,7 @@ def moe_capacity(S, E, capacity_factor=1.0, k=1):
     return _capi.lib().lancet_moe_capacity(S, E, capacity_factor, k)
 
 
-def moe_gate(gate, used_capacity, capacity, M, k=1, gates_dtype=torch.float32):
+def moe_gate(gate, used_capacity, capacity, M, k=1, gates_dtype=torch.float32, flags=0):
     """Gating only: returns (gates_s [k,S], indices_locations [2k,S], capused [E], elements [E] uint64)."""
     _require_cuda(gate, used_capacity)
     S, E = gate.shape
@@ -71,7 +71,7 @@ def moe_gate(gate, used_capacity, capacity, M, k=1, gates_dtype=torch.float32):
     nws = L.lancet_moe_gate_workspace_bytes(S, E, k)
     ws = workspace(dev, nws, "gate")
     check(L.lancet_moe_gate(_ptr(gate), _dt(gate), S, E, k, _ptr(used_capacity), capacity, M, _ptr(gates_s),
-                            _DT[gates_dtype], _ptr(idx_loc), _ptr(capused), _ptr(elems), _ptr(ws), ws.numel(),
+                            _DT[gates_dtype], _ptr(idx_loc), _ptr(capused), _ptr(elems), _ptr(ws), ws.numel(), flags,
                             _stream(gate)))
     return gates_s, idx_loc, capused, elems
 

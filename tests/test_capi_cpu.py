@@ -36,12 +36,12 @@ def test_capacity_formula(L):
 
 def test_invalid_arguments_launch_nothing(L):
     one = ctypes.c_void_p(16)
-    assert L.lancet_moe_gate(one, 0, 8, 4, 3, None, 2, 4, one, 0, one, one, one, one, 1 << 20, None) == 1
+    assert L.lancet_moe_gate(one, 0, 8, 4, 3, None, 2, 4, one, 0, one, one, one, one, 1 << 20, 0, None) == 1
     assert b"k must be 1 or 2" in L.lancet_last_error()
-    assert L.lancet_moe_gate(None, 0, 8, 4, 1, None, 2, 4, one, 0, one, one, one, one, 1 << 20, None) == 2
-    assert L.lancet_moe_gate(one, 0, 8, 4, 1, None, 2, 4, one, 0, one, one, one, one, 8, None) == 1
+    assert L.lancet_moe_gate(None, 0, 8, 4, 1, None, 2, 4, one, 0, one, one, one, one, 1 << 20, 0, None) == 2
+    assert L.lancet_moe_gate(one, 0, 8, 4, 1, None, 2, 4, one, 0, one, one, one, one, 8, 0, None) == 1
     assert b"workspace" in L.lancet_last_error()
-    assert L.lancet_moe_gate(one, 7, 8, 4, 1, None, 2, 4, one, 0, one, one, one, one, 1 << 20, None) == 1
+    assert L.lancet_moe_gate(one, 7, 8, 4, 1, None, 2, 4, one, 0, one, one, one, one, 1 << 20, 0, None) == 1
     assert L.lancet_moe_encode_fwd(one, 1, None, None, None, one, one, 8, 4, 2, 4, 0, 64, None) == 1
     assert L.lancet_moe_encode_fwd(one, 1, None, None, None, one, one, 8, 4, 2, 4, 0, 1, None) == 2  # GLOBAL_LOC w/o capused
     assert L.lancet_moe_decode_fwd(None, 0, one, 1, one, one, 8, 4, 2, 4, 0, None) == 2

@@ -234,3 +234,40 @@ def test_errors_are_reported_not_launched():
         LB.moe_encode(x, gate, torch.zeros(1, dtype=torch.int32, device=DEV), 1.0, k=2)   # E < k
     assert ei.value.code == 1
     torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("S,E,M,k,n,cf", [(4096, 2, 64, 2, 4, 1.25), (2048, 16, 128, 2, 4, 1.25), (1024, 8, 32, 1, 2, 1.0)])
+def test_chunked_plan_matches_chained_oracle(S, E, M, k, n, cf):
+    rng = np.random.default_rng(S + E + n)
+    x = torch.from_numpy(rng.standard_normal((S, M)).astype(np.float32)).half()
+    gate = torch.softmax(torch.from_numpy(rng.standard_normal((S, E)).astype(np.float32)), dim=1)
+    plan = LB.ChunkedMoE(S, M, E, k, cf, n, torch.float16, device=DEV)
+    for _ in range(2):   # second pass checks that buffers are reusable without re-initialisation
+        plan.dispatched.fill_(3.0)
+        disp = plan.dispatch(x.to(DEV), gate.to(DEV))
+        Sp = S // n
+        C = O.capacity(Sp, E, cf * n, k)
+        assert plan.C == C
+        want = np.zeros((E, C, M), np.float16)
+        cap = np.zeros(E, np.int32)
+        outs = []
+        for i in range(n):
+            sl = slice(i * Sp, (i + 1) * Sp)
+            gs, il, cap2, el = O.moe_gate(gate[sl].numpy(), cap, C, M, k)
+            gl = il.copy()
+            # the device adds in_cap[e] of the pre-drop expert choice to every location
+            raw = O.moe_gate(gate[sl].numpy(), np.zeros(E, np.int32), 1 << 30, M, k)[1]
+            for j in range(k):
+                gl[2 * j + 1] = il[2 * j + 1] + cap[raw[2 * j]]
+            np.testing.assert_array_equal(host(plan.idx_loc[i]), gl)
+            np.testing.assert_array_equal(host(plan.gates_s[i]), gs)
+            np.testing.assert_array_equal(host(plan.capused[i + 1]), cap2)
+            np.testing.assert_array_equal(host(plan.elems[i]), el)
+            want += O.moe_encode_fwd(il, x[sl].numpy(), E, C, cap, global_loc=True)
+            outs.append((gs, gl))
+            cap = cap2
+        np.testing.assert_array_equal(host(disp), want)
+        out = plan.combine()
+        ref = np.concatenate([O.moe_decode_fwd(want.astype(np.float32), gs, gl) for gs, gl in outs])
+        np.testing.assert_array_equal(host(out).astype(np.float32),
+                                      torch.from_numpy(ref).half().float().numpy())
