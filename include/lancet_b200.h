@@ -93,6 +93,21 @@ int lancet_moe_gate_chained(const void* gate, int gate_dtype, int S, int E, int 
                             int32_t* out_idx_loc, int32_t* out_capused, uint64_t* out_elems, void* ws,
                             size_t ws_bytes, int flags, lancet_stream_t stream);
 
+/* Gating for callers that can neither pass a workspace nor allocate one: lancet_moe_gate with its
+ * scratch in a fixed 4 MiB array inside the library (lancet_moe_gate_static_max_bytes()), which
+ * every GPU that loads the library holds until the process exits.  It has no counterpart in the
+ * reference, whose executor always supplies workspaces.  It is meant for hosts whose memory pool
+ * already owns the whole device, for operators bound after workspaces were planned, and for step
+ * loops that must not take cudaMalloc's device-wide synchronisation.  Allocates nothing.  Sizes
+ * whose scratch exceeds the array (roughly k*S*4 bytes plus k*E*4 per 256 tokens) are rejected with
+ * LANCET_ERR_INVALID.  The first call on each device looks up the array's device address; make
+ * that call outside any stream capture.  All calls on a device share the array: two calls whose
+ * kernels overlap on the GPU (different streams) race; calls on one stream are safe. */
+size_t lancet_moe_gate_static_max_bytes(void);
+int lancet_moe_gate_static(const void* gate, int gate_dtype, int S, int E, int k, const int32_t* in_capused,
+                           int C, int M, void* out_gates_s, int gates_dtype, int32_t* out_idx_loc,
+                           int32_t* out_capused, uint64_t* out_elems, int flags, lancet_stream_t stream);
+
 /* ---- dispatch: scatter token rows into the [E,C,M] expert buffer ---------------------------
  * Replaces launch_encode_forward (kernel_util.cuh:36-39; tutel_moe_dispatch.cu:61-86, :461-484).
  * rows_hi/rows_lo (both nullable, int32 [E]): when rows_hi is given, expert e owns rows

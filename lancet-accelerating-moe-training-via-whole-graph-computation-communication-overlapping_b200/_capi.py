@@ -34,6 +34,9 @@ SIGNATURES = {
     "lancet_moe_gate_chained_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
     "lancet_moe_gate_chained": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p,
                                         c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_int, c_void_p]),
+    "lancet_moe_gate_static_max_bytes": (c_size_t, []),
+    "lancet_moe_gate_static": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int,
+                                       c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
     "lancet_moe_encode_fwd": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                       c_int, c_int, c_int, c_int, c_void_p]),
     "lancet_moe_zero_tail": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),

@@ -17,6 +17,8 @@
 //
 // The order of tokens inside an expert is the token order, so the result is identical to the
 // serial cumulative sum of the reference.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace lancet {
@@ -359,5 +361,63 @@ int lancet_moe_gate(const void* gate, int gate_dtype, int S, int E, int k, const
                     void* ws, size_t ws_bytes, int flags, lancet_stream_t stream) {
   return lancet_moe_gate_chained(gate, gate_dtype, S, E, k, 1, in_capused, C, M, out_gates_s, gates_dtype, out_idx_loc,
                                  out_capused, out_elems, ws, ws_bytes, flags, stream);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Gating without a caller-supplied workspace.
+//
+// Some hosts of this library cannot hand it scratch memory and cannot let it allocate either: an
+// executor that has already given all device memory to its own pool (a raw cudaMalloc would fail
+// or fragment it), an operator bound after that executor planned its workspaces, or a step loop
+// in which cudaMalloc's device-wide synchronisation would stall work running on other streams.
+// For them the gating scratch lives in a fixed array inside the library image.  Every GPU that
+// loads the library holds these kLancetStaticGateBytes until the process exits.
+// ---------------------------------------------------------------------------------------------
+constexpr size_t kLancetStaticGateBytes = 4u << 20;  // 4 MiB
+static __device__ __align__(256) unsigned char g_static_gate_scratch[kLancetStaticGateBytes];
+
+namespace {
+// Device address of g_static_gate_scratch per device.  In host code the symbol itself is only a
+// stand-in, so the address is looked up once per device (with that device current) and cached.
+void* g_static_gate_ptr[64] = {nullptr};
+std::mutex g_static_gate_mu;
+
+int static_gate_scratch(void** out) {
+  int dev = -1;
+  LANCET_CUDA(cudaGetDevice(&dev));
+  LANCET_REQUIRE(dev >= 0 && dev < 64, LANCET_ERR_UNSUPPORTED, "lancet_moe_gate_static: device index %d out of range", dev);
+  std::lock_guard<std::mutex> lk(g_static_gate_mu);
+  if (g_static_gate_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    LANCET_CUDA(cudaGetSymbolAddress(&p, g_static_gate_scratch));
+    LANCET_REQUIRE(p != nullptr, LANCET_ERR_CUDA, "lancet_moe_gate_static: no device address for the scratch array");
+    g_static_gate_ptr[dev] = p;
+  }
+  *out = g_static_gate_ptr[dev];
+  return LANCET_OK;
+}
+}  // namespace
+
+size_t lancet_moe_gate_static_max_bytes(void) { return kLancetStaticGateBytes; }
+
+int lancet_moe_gate_static(const void* gate, int gate_dtype, int S, int E, int k, const int32_t* in_capused, int C, int M,
+                           void* out_gates_s, int gates_dtype, int32_t* out_idx_loc, int32_t* out_capused,
+                           uint64_t* out_elems, int flags, lancet_stream_t stream) {
+  using namespace lancet;
+  LANCET_REQUIRE(k == 1 || k == 2, LANCET_ERR_INVALID, "lancet_moe_gate_static: k must be 1 or 2, got %d", k);
+  LANCET_REQUIRE(S >= 0 && E >= k && k * E <= 1024, LANCET_ERR_INVALID,
+                 "lancet_moe_gate_static: bad sizes S=%d E=%d k=%d (need S>=0, k<=E, k*E<=1024)", S, E, k);
+  const size_t need = gate_workspace_bytes(S, E, k, 1);
+  LANCET_REQUIRE(need <= kLancetStaticGateBytes, LANCET_ERR_INVALID,
+                 "lancet_moe_gate_static: S=%d E=%d k=%d needs %zu bytes of scratch, the built-in array holds %zu; "
+                 "use lancet_moe_gate with a caller workspace",
+                 S, E, k, need, kLancetStaticGateBytes);
+  void* scratch = nullptr;
+  if (int rc = static_gate_scratch(&scratch)) return rc;
+  // Nothing in the scratch has to start at zero: every word the kernels read (raw gate values,
+  // tile histograms, tile totals) is written earlier in the same call, so stale contents of the
+  // previous call are harmless and no clearing pass is needed.
+  return lancet_moe_gate(gate, gate_dtype, S, E, k, in_capused, C, M, out_gates_s, gates_dtype, out_idx_loc,
+                         out_capused, out_elems, scratch, kLancetStaticGateBytes, flags, stream);
 }
 }
