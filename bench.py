@@ -189,9 +189,9 @@ def run_moe(args):
         plan = LB.DistChunkedMoE(S_TOKENS, M_DIM, TOP_K, CAP_FACTOR, N_CHUNKS, torch.float16, device=dev)
 
     def step(i):
+        # world > 1: the exchange is fused into both kernels (peer stores / peer loads) and the ranks
+        # meet at a flag barrier between them; the experts are the identity for this metric
         plan.dispatch(xs[i % 2], gates[i % 2])
-        plan.exchange_forward() if world > 1 else None
-        plan.exchange_backward() if world > 1 else None
         return plan.combine()
 
     def sync_all():
@@ -206,7 +206,7 @@ def run_moe(args):
         step(i)
     sync_all()
     # ---- timed region: K steps, device resident inputs ------------------------------------------
-    kname = b"dispatch_rows_kernel"
+    kname = b"dispatch_rows_kernel" if world == 1 else b"dispatch_rows_peer_kernel"
     L.lancet_profile_begin(kname)
     launches0 = L.lancet_launch_count()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -238,9 +238,6 @@ def run_moe(args):
         x_dev.copy_(x_pin[i % 2], non_blocking=True)
         g_dev.copy_(g_pin[i % 2], non_blocking=True)
         plan.dispatch(x_dev, g_dev)
-        if world > 1:
-            plan.exchange_forward()
-            plan.exchange_backward()
         out_pin.copy_(plan.combine(), non_blocking=True)
 
     for i in range(3):
@@ -259,12 +256,19 @@ def run_moe(args):
         e2e_ms = float(t.item())
     e2e_value = S_TOKENS * world / (e2e_ms / e2e_steps / 1e3)
     clocks = ClockSampler.summarise(sampler.stop()) if sampler else None
+    if world > 1:
+        plan.check()
+        cap_all = plan.capused.cpu().numpy()
+        import torch.distributed as dist
+        dist.barrier()
+        plan.close()
+        dist.destroy_process_group()
     if rank != 0:
         return
     # ---- roofline of the dominant kernel (dispatch scatter) ---------------------------------------
     peaks, peak_kind = load_peaks()
     hbm_peak = float(peaks.get("hbm_gbs", FALLBACK_PEAKS["hbm_gbs"]))
-    cap = plan.capused.cpu().numpy()
+    cap = plan.capused.cpu().numpy() if world == 1 else cap_all
     kept_rows = int(cap[-1].sum())                      # rows written by the 4 dispatch launches of a step
     row_bytes = M_DIM * 2
     # algorithmic bytes of the dispatch launch (all chunks in one launch): token rows read once, the
@@ -277,6 +281,14 @@ def run_moe(args):
         roof = {"bound": "hbm", "kernel": kname.decode(), "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
                 "frac": achieved / hbm_peak, "peak_kind": peak_kind, "traffic": None,
                 "bytes_per_launch": bytes_per_launch, "avg_launch_us": avg_s * 1e6, "launches_timed": k_n.value}
+        if world > 1:
+            # the fused dispatch is bound by the bytes that leave this GPU over NVLink: (W-1)/W of the
+            # padded expert buffer; peak = the pool's measured peer-copy bandwidth per direction
+            nv_bytes = E * plan.C * row_bytes * (world - 1) / world
+            nv = nv_bytes / avg_s / 1e9
+            roof.update({"bound": "nvlink", "achieved": nv, "peak": 770.0, "frac": nv / 770.0,
+                         "peak_kind": "measured peer copy, per direction", "bytes_per_launch": nv_bytes,
+                         "hbm_achieved": achieved})
         tr = os.path.join(ROOT, "profiles", "traffic.json")
         if os.path.exists(tr):
             with open(tr) as f:

@@ -169,6 +169,44 @@ int lancet_moe_combine_chunked(const void* expert_out, const void* gates_s, int 
                                const int32_t* idx_loc, int S, int M, int C, int E, int k, int n_chunks, int dtype,
                                void* out, lancet_stream_t stream);
 
+/* ---- expert-parallel exchange fused into dispatch / combine over NVLink peer memory ------------
+ * Replaces `moe_encode -> _all_to_all` and `_all_to_all -> moe_decode` of the MoE layer
+ * (NCCLAllToAll::Execute, src/op/dialect/nccl/nccl.cc:199-227; layer wiring in
+ * models/benchmark/pytorch/utils.py:576-634).  Rank r of W owns experts [r*LE, (r+1)*LE).  Every
+ * rank exposes a receive buffer [W][LE][C][M] (what the all-to-all would deliver: block g comes
+ * from rank g); peer_recv / peer_expert_out are HOST arrays of the W device addresses of those
+ * buffers as mapped into this process (own buffer at index `rank`).
+ *
+ * lancet_symm_alloc/open/close/free: device buffers that other processes on the node can map
+ * (set-up time only; these do allocate).  Replaces the communicator bootstrap of
+ * src/distributed/cuda/nccl_communicator.cc:27-60 for the peer-memory path; the 64-byte handle is
+ * exchanged by the caller (any host channel). */
+int lancet_symm_alloc(size_t bytes, void** ptr, unsigned char* handle64);
+int lancet_symm_open(const unsigned char* handle64, void** peer_ptr);
+int lancet_symm_close(void* peer_ptr);
+int lancet_symm_free(void* ptr);
+
+/* Flag barrier between the W ranks on `stream`.  peer_flags[r] = rank r's array of W 32-bit words
+ * (zero-initialised, symmetric memory); epoch must grow by one per barrier on every rank.  A rank
+ * that waits longer than timeout_ns records the missing peer in *status (device int32, zero when
+ * healthy) and returns; lancet_p2p_status() turns a non-zero word into LANCET_ERR_TIMEOUT. */
+int lancet_p2p_barrier(void* const* peer_flags, int W, int rank, unsigned epoch, unsigned long long timeout_ns,
+                       int32_t* status, lancet_stream_t stream);
+int lancet_p2p_status(const int32_t* status, lancet_stream_t stream);
+
+enum { LANCET_P2P_NO_REMOTE_ZERO = 1 }; /* do not zero-fill unowned rows of the peers' buffers */
+/* As lancet_moe_dispatch_chunked with E = LE*W, but rows go straight into the owners' receive
+ * buffers.  gates_s is float32 [n][k][Sp]. */
+int lancet_moe_dispatch_chunked_p2p(const void* x, const void* gate, int gate_dtype, float capacity_factor, int S,
+                                    int M, int LE, int W, int rank, int k, int n_chunks, int dtype, void* gates_s,
+                                    int32_t* idx_loc, int32_t* capused_chain, uint64_t* elems,
+                                    void* const* peer_recv, void* ws, size_t ws_bytes, int flags,
+                                    lancet_stream_t stream);
+/* As lancet_moe_combine_chunked, gathering rows from the owners' expert output buffers. */
+int lancet_moe_combine_chunked_p2p(void* const* peer_expert_out, const void* gates_s, const int32_t* idx_loc, int S,
+                                   int M, int C, int LE, int W, int rank, int k, int n_chunks, int dtype, void* out,
+                                   lancet_stream_t stream);
+
 /* ---- LANS optimizer ---------------------------------------------------------------------------
  * Replaces multi_tensor_lans_cuda (kernel_util.cuh:26-34; multi_tensor_lans.cu:401-450) and the
  * host side of LansImpl::Execute (src/op/dialect/cuda/lans.cc:92-148).  g/p/m/v are HOST arrays of

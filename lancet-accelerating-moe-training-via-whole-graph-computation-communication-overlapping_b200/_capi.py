@@ -59,6 +59,18 @@ SIGNATURES = {
                                             c_void_p]),
     "lancet_moe_combine_chunked": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                            c_int, c_void_p, c_void_p]),
+    "lancet_symm_alloc": (c_int, [c_size_t, ctypes.POINTER(c_void_p), ctypes.c_char_p]),
+    "lancet_symm_open": (c_int, [ctypes.c_char_p, ctypes.POINTER(c_void_p)]),
+    "lancet_symm_close": (c_int, [c_void_p]),
+    "lancet_symm_free": (c_int, [c_void_p]),
+    "lancet_p2p_barrier": (c_int, [ctypes.POINTER(c_void_p), c_int, c_int, ctypes.c_uint, ctypes.c_ulonglong, c_void_p,
+                                   c_void_p]),
+    "lancet_p2p_status": (c_int, [c_void_p, c_void_p]),
+    "lancet_moe_dispatch_chunked_p2p": (c_int, [c_void_p, c_void_p, c_int, c_float, c_int, c_int, c_int, c_int, c_int,
+                                                c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                ctypes.POINTER(c_void_p), c_void_p, c_size_t, c_int, c_void_p]),
+    "lancet_moe_combine_chunked_p2p": (c_int, [ctypes.POINTER(c_void_p), c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                               c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "lancet_lans_workspace_bytes": (c_size_t, [c_int, ctypes.POINTER(c_i64)]),
     "lancet_lans": (c_int, [c_void_p, c_size_t, c_int, ctypes.POINTER(c_i64), ctypes.POINTER(c_void_p),
                             ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), c_int, c_int,
@@ -70,6 +82,8 @@ OK = 0
 ENCODE_GLOBAL_LOC, ENCODE_NO_ZERO = 1, 2
 GATE_GLOBAL_LOC = 1
 LANS_TABLES_READY = 1
+P2P_NO_REMOTE_ZERO = 1
+ERR_TIMEOUT = 4
 
 
 class LancetError(RuntimeError):

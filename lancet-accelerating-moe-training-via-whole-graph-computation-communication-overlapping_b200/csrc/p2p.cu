@@ -1,0 +1,349 @@
+// Expert-parallel exchange fused into dispatch and combine over NVLink peer memory.
+//
+// The reference moves the [E,C,M] expert buffer with an NCCL all-to-all after dispatch and again
+// before combine (NCCLAllToAll::Execute, src/op/dialect/nccl/nccl.cc:199-227; layer in
+// models/benchmark/pytorch/utils.py:576-634): scatter to a local buffer, copy it through NCCL
+// send/recv kernels, read it again on the other side.  Here the scatter itself writes each token
+// row into the receive buffer of the GPU that owns the expert (16-byte peer stores through
+// NVSwitch), and combine gathers rows straight from the owners' output buffers (peer loads), so
+// every row crosses NVLink once and is never staged.  Rank r owns experts [r*LE, (r+1)*LE); its
+// receive buffer is [G=W][LE][C][M] with block g written by rank g - exactly the layout the
+// all-to-all produces.
+//
+// Ranks meet at a flag barrier in peer memory.  Every wait is bounded by a time limit after which
+// the kernel records which peer was missing in a status word and returns.
+#include "common.cuh"
+
+namespace lancet {
+
+constexpr int kMaxPeers = 16;
+struct PeerTable {
+  void* ptr[kMaxPeers];
+};
+
+constexpr int kP2PThreads = 256;
+constexpr int kP2PWarps = kP2PThreads / 32;
+
+__device__ __forceinline__ size_t il_index_p2p(int s, int Sp, int K2, int row) {
+  const int c = s / Sp;
+  return ((size_t)c * K2 + row) * Sp + (s - c * Sp);
+}
+
+// tasks [0,S): token rows; tasks [S, S + E*C): candidate zero rows of my block in every owner's buffer.
+template <typename V, int K>
+__global__ void __launch_bounds__(kP2PThreads)
+dispatch_rows_peer_kernel(const int32_t* __restrict__ idx_loc, const int32_t* __restrict__ rows_used,
+                          const V* __restrict__ x, PeerTable recv, int S, int Sp, int row_vecs, int C, int E, int LE,
+                          int my_rank, int zero_tail) {
+  constexpr int U = 8;
+  const int lane = threadIdx.x & 31;
+  const long long gw = (long long)blockIdx.x * kP2PWarps + (threadIdx.x >> 5);
+  const long long nwarps = (long long)gridDim.x * kP2PWarps;
+  const long long ntasks = (long long)S + (zero_tail ? (long long)E * C : 0);
+  for (long long task = gw; task < ntasks; task += nwarps) {
+    if (task < S) {
+      const int s = (int)task;
+      V* dst[K];
+      bool any = false;
+#pragma unroll
+      for (int j = 0; j < K; ++j) {
+        const int idx = idx_loc[il_index_p2p(s, Sp, 2 * K, 2 * j)];
+        const int loc = idx_loc[il_index_p2p(s, Sp, 2 * K, 2 * j + 1)];
+        dst[j] = nullptr;
+        if (idx >= 0 && idx < E && loc >= 0 && loc < C) {
+          const int owner = idx / LE, le = idx - owner * LE;
+          dst[j] = static_cast<V*>(recv.ptr[owner]) + ((size_t)(my_rank * LE + le) * C + loc) * row_vecs;
+          any = true;
+        }
+      }
+      if (!any) continue;
+      const V* src = x + (size_t)s * row_vecs;
+      for (int base = 0; base < row_vecs; base += 32 * U) {
+        V r[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int v = base + u * 32 + lane;
+          if (v < row_vecs) r[u] = __ldcs(src + v);
+        }
+#pragma unroll
+        for (int j = 0; j < K; ++j) {
+          if (!dst[j]) continue;
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            const int v = base + u * 32 + lane;
+            if (v < row_vecs) dst[j][v] = r[u];
+          }
+        }
+      }
+    } else {
+      const long long r = task - S;
+      const int e = (int)(r / C);
+      const int c = (int)(r % C);
+      if (c < rows_used[e]) continue;
+      const int owner = e / LE, le = e - owner * LE;
+      V* d = static_cast<V*>(recv.ptr[owner]) + ((size_t)(my_rank * LE + le) * C + c) * row_vecs;
+      V z;
+      memset(&z, 0, sizeof(V));
+      for (int v = lane; v < row_vecs; v += 32) d[v] = z;
+    }
+  }
+}
+
+template <typename T, int N>
+struct alignas(sizeof(T) * N) PackP {
+  T v[N];
+};
+
+template <typename T, int N, int K>
+__global__ void __launch_bounds__(kP2PThreads)
+combine_rows_peer_kernel(const float* __restrict__ gates, const int32_t* __restrict__ idx_loc, PeerTable eo,
+                         T* __restrict__ out, int S, int Sp, int M, int C, int E, int LE, int my_rank) {
+  using P = PackP<T, N>;
+  constexpr int U = 4;
+  const int lane = threadIdx.x & 31;
+  const int row_vecs = M / N;
+  const long long gw = (long long)blockIdx.x * kP2PWarps + (threadIdx.x >> 5);
+  const long long nwarps = (long long)gridDim.x * kP2PWarps;
+  for (long long s = gw; s < S; s += nwarps) {
+    const P* srow[K];
+    float g[K];
+#pragma unroll
+    for (int j = 0; j < K; ++j) {
+      const int idx = idx_loc[il_index_p2p((int)s, Sp, 2 * K, 2 * j)];
+      const int loc = idx_loc[il_index_p2p((int)s, Sp, 2 * K, 2 * j + 1)];
+      srow[j] = nullptr;
+      if (idx >= 0 && idx < E && loc >= 0 && loc < C) {
+        const int owner = idx / LE, le = idx - owner * LE;
+        srow[j] = reinterpret_cast<const P*>(static_cast<const T*>(eo.ptr[owner]) +
+                                             ((size_t)(my_rank * LE + le) * C + loc) * M);
+      }
+      g[j] = gates[il_index_p2p((int)s, Sp, K, j)];
+    }
+    P* dst = reinterpret_cast<P*>(out + (size_t)s * M);
+    for (int base = 0; base < row_vecs; base += 32 * U) {
+      P p[K][U];
+#pragma unroll
+      for (int j = 0; j < K; ++j) {
+        if (!srow[j]) continue;
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int v = base + u * 32 + lane;
+          if (v < row_vecs) p[j][u] = srow[j][v];
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int v = base + u * 32 + lane;
+        if (v >= row_vecs) continue;
+        float acc[N];
+#pragma unroll
+        for (int i = 0; i < N; ++i) acc[i] = 0.f;
+#pragma unroll
+        for (int j = 0; j < K; ++j) {
+          if (!srow[j]) continue;
+#pragma unroll
+          for (int i = 0; i < N; ++i) {
+            const float prod = __fmul_rn(g[j], Num<T>::to_f(p[j][u].v[i]));
+            acc[i] = (j == 0 || !srow[0]) ? prod : __fadd_rn(acc[i], prod);
+          }
+        }
+        P o;
+#pragma unroll
+        for (int i = 0; i < N; ++i) o.v[i] = Num<T>::from_f(acc[i]);
+        dst[v] = o;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Thread i tells rank i that this rank has arrived (epoch) and waits until rank i has told us.
+// flags.ptr[r] is rank r's array of W words; word i of it is written by rank i only.
+__global__ void p2p_barrier_kernel(PeerTable flags, int W, int my_rank, unsigned epoch, unsigned long long timeout_ns,
+                                   int* __restrict__ status) {
+  const int i = threadIdx.x;
+  if (i >= W) return;
+  __threadfence_system();
+  unsigned* remote = static_cast<unsigned*>(flags.ptr[i]) + my_rank;
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(epoch) : "memory");
+  const unsigned* local = static_cast<const unsigned*>(flags.ptr[my_rank]) + i;
+  const unsigned long long t0 = globaltimer_ns();
+  while (true) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(local) : "memory");
+    if ((int)(v - epoch) >= 0) break;
+    if (globaltimer_ns() - t0 > timeout_ns) {
+      atomicCAS(status, 0, i + 1);  // remember the first peer that did not arrive
+      break;
+    }
+    __nanosleep(64);
+  }
+  __threadfence_system();
+}
+
+static int p2p_grid(long long tasks) {
+  long long ctas = (tasks + kP2PWarps - 1) / kP2PWarps;
+  const long long cap = (long long)sm_count() * 8;
+  if (ctas > cap) ctas = cap;
+  if (ctas < 1) ctas = 1;
+  return (int)ctas;
+}
+
+template <typename T>
+static int combine_p2p_t(const float* gates, const int32_t* idx_loc, const PeerTable& t, void* out, int S, int Sp, int M,
+                         int C, int E, int LE, int rank, int k, cudaStream_t st) {
+  constexpr int N = 16 / sizeof(T);
+  ProfScope prof("combine_rows_peer_kernel", st);
+  if (k == 1)
+    combine_rows_peer_kernel<T, N, 1><<<p2p_grid(S), kP2PThreads, 0, st>>>(gates, idx_loc, t, static_cast<T*>(out), S, Sp,
+                                                                         M, C, E, LE, rank);
+  else
+    combine_rows_peer_kernel<T, N, 2><<<p2p_grid(S), kP2PThreads, 0, st>>>(gates, idx_loc, t, static_cast<T*>(out), S, Sp,
+                                                                         M, C, E, LE, rank);
+  return launch_status("combine_rows_peer_kernel");
+}
+
+}  // namespace lancet
+
+extern "C" {
+using namespace lancet;
+
+int lancet_symm_alloc(size_t bytes, void** ptr, unsigned char* handle64) {
+  LANCET_REQUIRE(ptr && handle64 && bytes > 0, LANCET_ERR_NULL, "lancet_symm_alloc: null argument or zero size");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+  void* p = nullptr;
+  LANCET_CUDA(cudaMalloc(&p, bytes));
+  cudaError_t e = cudaMemset(p, 0, bytes);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  cudaIpcMemHandle_t h;
+  if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) {
+    cudaFree(p);
+    return fail(LANCET_ERR_CUDA, "lancet_symm_alloc: %s", cudaGetErrorString(e));
+  }
+  memcpy(handle64, &h, 64);
+  *ptr = p;
+  return LANCET_OK;
+}
+
+int lancet_symm_open(const unsigned char* handle64, void** peer_ptr) {
+  LANCET_REQUIRE(handle64 && peer_ptr, LANCET_ERR_NULL, "lancet_symm_open: null argument");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, 64);
+  LANCET_CUDA(cudaIpcOpenMemHandle(peer_ptr, h, cudaIpcMemLazyEnablePeerAccess));
+  return LANCET_OK;
+}
+
+int lancet_symm_close(void* peer_ptr) {
+  if (!peer_ptr) return LANCET_OK;
+  LANCET_CUDA(cudaIpcCloseMemHandle(peer_ptr));
+  return LANCET_OK;
+}
+
+int lancet_symm_free(void* ptr) {
+  if (!ptr) return LANCET_OK;
+  LANCET_CUDA(cudaFree(ptr));
+  return LANCET_OK;
+}
+
+int lancet_p2p_barrier(void* const* peer_flags, int W, int rank, unsigned epoch, unsigned long long timeout_ns,
+                       int32_t* status, lancet_stream_t stream) {
+  LANCET_REQUIRE(W >= 1 && W <= kMaxPeers && rank >= 0 && rank < W, LANCET_ERR_INVALID,
+                 "lancet_p2p_barrier: bad world %d / rank %d (at most %d ranks)", W, rank, kMaxPeers);
+  LANCET_REQUIRE(peer_flags && status, LANCET_ERR_NULL, "lancet_p2p_barrier: null argument");
+  LANCET_REQUIRE(timeout_ns > 0 && timeout_ns <= 60ull * 1000000000ull, LANCET_ERR_INVALID,
+                 "lancet_p2p_barrier: the wait limit must be in (0, 60 s]");
+  PeerTable t;
+  for (int i = 0; i < kMaxPeers; ++i) t.ptr[i] = i < W ? peer_flags[i] : nullptr;
+  for (int i = 0; i < W; ++i) LANCET_REQUIRE(t.ptr[i], LANCET_ERR_NULL, "lancet_p2p_barrier: flag pointer %d is null", i);
+  p2p_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(t, W, rank, epoch, timeout_ns, status);
+  return launch_status("p2p_barrier_kernel");
+}
+
+// Reads the status word written by bounded waits (synchronises the stream).
+int lancet_p2p_status(const int32_t* status, lancet_stream_t stream) {
+  LANCET_REQUIRE(status, LANCET_ERR_NULL, "lancet_p2p_status: null argument");
+  int32_t h = 0;
+  LANCET_CUDA(cudaMemcpyAsync(&h, status, sizeof(h), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream)));
+  LANCET_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+  if (h != 0) return fail(LANCET_ERR_TIMEOUT, "a bounded wait ran out: rank %d did not arrive at the barrier", h - 1);
+  return LANCET_OK;
+}
+
+int lancet_moe_dispatch_chunked_p2p(const void* x, const void* gate, int gate_dtype, float capacity_factor, int S, int M,
+                                    int LE, int W, int rank, int k, int n_chunks, int dtype, void* gates_s,
+                                    int32_t* idx_loc, int32_t* capused_chain, uint64_t* elems, void* const* peer_recv,
+                                    void* ws, size_t ws_bytes, int flags, lancet_stream_t stream) {
+  LANCET_REQUIRE(W >= 1 && W <= kMaxPeers && rank >= 0 && rank < W && LE >= 1, LANCET_ERR_INVALID,
+                 "lancet_moe_dispatch_chunked_p2p: bad world %d / rank %d / local experts %d", W, rank, LE);
+  LANCET_REQUIRE(n_chunks >= 1 && S >= 0 && S % n_chunks == 0, LANCET_ERR_INVALID,
+                 "lancet_moe_dispatch_chunked_p2p: S=%d is not divisible into %d chunks", S, n_chunks);
+  LANCET_REQUIRE((k == 1 || k == 2) && M >= 0 && valid_dtype(dtype) && valid_dtype(gate_dtype), LANCET_ERR_INVALID,
+                 "lancet_moe_dispatch_chunked_p2p: bad k=%d, M=%d or dtype", k, M);
+  LANCET_REQUIRE((flags & ~LANCET_P2P_NO_REMOTE_ZERO) == 0, LANCET_ERR_INVALID,
+                 "lancet_moe_dispatch_chunked_p2p: unknown flag bits 0x%x", flags);
+  LANCET_REQUIRE(peer_recv && capused_chain && elems && ws && (S == 0 || (x && gate && gates_s && idx_loc)),
+                 LANCET_ERR_NULL, "lancet_moe_dispatch_chunked_p2p: null pointer argument");
+  const int E = LE * W;
+  const int Sp = S / n_chunks;
+  const int C = lancet_moe_capacity(Sp, E, capacity_factor * n_chunks, k);
+  LANCET_REQUIRE(C >= 0 && (long long)E * C < (1ll << 31), LANCET_ERR_INVALID,
+                 "lancet_moe_dispatch_chunked_p2p: capacity %d out of range", C);
+  const size_t row_bytes = (size_t)M * dtype_bytes(dtype);
+  LANCET_REQUIRE(row_bytes % 16 == 0 && aligned(x, 16), LANCET_ERR_INVALID,
+                 "lancet_moe_dispatch_chunked_p2p: rows must be a multiple of 16 bytes and 16-byte aligned");
+  PeerTable t;
+  for (int i = 0; i < kMaxPeers; ++i) t.ptr[i] = i < W ? peer_recv[i] : nullptr;
+  for (int i = 0; i < W; ++i)
+    LANCET_REQUIRE(t.ptr[i] && aligned(t.ptr[i], 16), LANCET_ERR_NULL, "lancet_moe_dispatch_chunked_p2p: peer buffer %d is null or unaligned", i);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  LANCET_CUDA(cudaMemsetAsync(capused_chain, 0, (size_t)E * sizeof(int32_t), st));
+  int rc = lancet_moe_gate_chained(gate, gate_dtype, S, E, k, n_chunks, capused_chain, C, M, gates_s, LANCET_F32, idx_loc,
+                                   capused_chain + E, elems, ws, ws_bytes, LANCET_GATE_GLOBAL_LOC, stream);
+  if (rc != LANCET_OK) return rc;
+  if ((size_t)E * C * M == 0) return LANCET_OK;
+  const int zero_tail = (flags & LANCET_P2P_NO_REMOTE_ZERO) ? 0 : 1;
+  const long long tasks = (long long)S + (zero_tail ? (long long)E * C : 0);
+  const int row_vecs = (int)(row_bytes / 16);
+  const int32_t* used = capused_chain + (size_t)n_chunks * E;
+  ProfScope prof("dispatch_rows_peer_kernel", st);
+  if (k == 1)
+    dispatch_rows_peer_kernel<uint4, 1><<<p2p_grid(tasks), kP2PThreads, 0, st>>>(
+        idx_loc, used, static_cast<const uint4*>(x), t, S, Sp > 0 ? Sp : 1, row_vecs, C, E, LE, rank, zero_tail);
+  else
+    dispatch_rows_peer_kernel<uint4, 2><<<p2p_grid(tasks), kP2PThreads, 0, st>>>(
+        idx_loc, used, static_cast<const uint4*>(x), t, S, Sp > 0 ? Sp : 1, row_vecs, C, E, LE, rank, zero_tail);
+  return launch_status("dispatch_rows_peer_kernel");
+}
+
+int lancet_moe_combine_chunked_p2p(void* const* peer_expert_out, const void* gates_s, const int32_t* idx_loc, int S, int M,
+                                   int C, int LE, int W, int rank, int k, int n_chunks, int dtype, void* out,
+                                   lancet_stream_t stream) {
+  LANCET_REQUIRE(W >= 1 && W <= kMaxPeers && rank >= 0 && rank < W && LE >= 1, LANCET_ERR_INVALID,
+                 "lancet_moe_combine_chunked_p2p: bad world %d / rank %d / local experts %d", W, rank, LE);
+  LANCET_REQUIRE(n_chunks >= 1 && S >= 0 && S % n_chunks == 0, LANCET_ERR_INVALID,
+                 "lancet_moe_combine_chunked_p2p: S=%d is not divisible into %d chunks", S, n_chunks);
+  LANCET_REQUIRE((k == 1 || k == 2) && M >= 0 && C >= 0 && valid_dtype(dtype), LANCET_ERR_INVALID,
+                 "lancet_moe_combine_chunked_p2p: bad k=%d, M=%d, C=%d or dtype", k, M, C);
+  if (S == 0 || M == 0) return LANCET_OK;
+  LANCET_REQUIRE(peer_expert_out && gates_s && idx_loc && out, LANCET_ERR_NULL,
+                 "lancet_moe_combine_chunked_p2p: null pointer argument");
+  LANCET_REQUIRE(((size_t)M * dtype_bytes(dtype)) % 16 == 0 && aligned(out, 16), LANCET_ERR_INVALID,
+                 "lancet_moe_combine_chunked_p2p: rows must be a multiple of 16 bytes and 16-byte aligned");
+  PeerTable t;
+  for (int i = 0; i < kMaxPeers; ++i) t.ptr[i] = i < W ? peer_expert_out[i] : nullptr;
+  for (int i = 0; i < W; ++i)
+    LANCET_REQUIRE(t.ptr[i] && aligned(t.ptr[i], 16), LANCET_ERR_NULL, "lancet_moe_combine_chunked_p2p: peer buffer %d is null or unaligned", i);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int E = LE * W, Sp = S / n_chunks;
+  const float* g = static_cast<const float*>(gates_s);
+  if (dtype == LANCET_F32) return combine_p2p_t<float>(g, idx_loc, t, out, S, Sp, M, C, E, LE, rank, k, st);
+  if (dtype == LANCET_F16) return combine_p2p_t<__half>(g, idx_loc, t, out, S, Sp, M, C, E, LE, rank, k, st);
+  return combine_p2p_t<__nv_bfloat16>(g, idx_loc, t, out, S, Sp, M, C, E, LE, rank, k, st);
+}
+}

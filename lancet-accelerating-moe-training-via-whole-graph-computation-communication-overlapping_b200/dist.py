@@ -1,0 +1,195 @@
+"""Expert-parallel MoE layer plan over NVLink peer memory (one process per GPU).
+
+Rank r of W owns experts [r*LE, (r+1)*LE).  Each rank maps every peer's receive buffer
+[W][LE][C][M] once at construction (like RAF's communicator, which is created before the first step:
+src/distributed/cuda/nccl_communicator.cc:27-60); afterwards `dispatch` and `combine` only enqueue
+kernels.  `torch.distributed` is used for the one-time exchange of memory handles.
+"""
+import ctypes
+
+import torch
+
+from . import _capi
+from ._capi import check
+from .ops import _DT, _ptr, _stream
+
+_TYPESTR = {torch.float32: "<f4", torch.float16: "<f2", torch.bfloat16: "<i2", torch.int32: "<i4"}
+
+
+class _RawCuda:
+    def __init__(self, ptr, nelem, typestr):
+        self.__cuda_array_interface__ = {"shape": (nelem,), "typestr": typestr, "data": (ptr, False), "version": 2}
+
+
+def tensor_from_ptr(ptr, shape, dtype, device):
+    """A torch view of device memory owned by the library (no copy)."""
+    n = 1
+    for s in shape:
+        n *= s
+    t = torch.as_tensor(_RawCuda(ptr, n, _TYPESTR[dtype]), device=device)
+    if dtype == torch.bfloat16:
+        t = t.view(torch.bfloat16)
+    return t.view(*shape)
+
+
+def _up(v, a=256):
+    return (v + a - 1) // a * a
+
+
+class ProcessFabric:
+    """Symmetric memory between the ranks of a torch.distributed group on one node (CUDA IPC)."""
+
+    def __init__(self, device, group=None):
+        import torch.distributed as dist
+        self.dist, self.group, self.device = dist, group, device
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.real = True
+        self._owned, self._opened = [], []
+
+    def alloc(self, nbytes):
+        L = _capi.lib()
+        ptr = ctypes.c_void_p()
+        handle = ctypes.create_string_buffer(64)
+        with torch.cuda.device(self.device):
+            check(L.lancet_symm_alloc(nbytes, ctypes.byref(ptr), handle))
+            self._owned.append(ptr.value)
+            handles = [None] * self.world
+            self.dist.all_gather_object(handles, handle.raw, group=self.group)
+            peers = []
+            for r, h in enumerate(handles):
+                if r == self.rank:
+                    peers.append(ptr.value)
+                else:
+                    p = ctypes.c_void_p()
+                    check(L.lancet_symm_open(h, ctypes.byref(p)))
+                    self._opened.append(p.value)
+                    peers.append(p.value)
+        return peers
+
+    def close(self):
+        L = _capi.lib()
+        for p in self._opened:
+            L.lancet_symm_close(ctypes.c_void_p(p))
+        self._opened = []
+        if self.world > 1:
+            self.dist.barrier(group=self.group)
+        for p in self._owned:
+            L.lancet_symm_free(ctypes.c_void_p(p))
+        self._owned = []
+
+
+class LocalFabric:
+    """W virtual ranks inside one process on one GPU (tests): `alloc` returns the same table of W
+    buffers to every rank.  The flag barrier is skipped: the ranks' kernels run one after another
+    on one stream, which already orders them (kernels that wait on one another must never be
+    launched separately on one GPU)."""
+
+    def __init__(self, world, rank, shared):
+        self.world, self.rank, self.shared = world, rank, shared
+        self.real = False
+        self._n = 0
+
+    def alloc(self, nbytes):
+        key = self._n
+        self._n += 1
+        if key not in self.shared:
+            self.shared[key] = [torch.zeros(nbytes, dtype=torch.uint8, device="cuda") for _ in range(self.world)]
+        return [t.data_ptr() for t in self.shared[key]]
+
+    def close(self):
+        pass
+
+
+class DistChunkedMoE:
+    """Chunk-chained top-k dispatch and combine with the all-to-all fused into the kernels."""
+
+    def __init__(self, S, M, k=2, capacity_factor=1.25, n_chunks=4, dtype=torch.float16, device="cuda",
+                 local_experts=2, fabric=None, group=None, timeout_s=5.0, remote_zero=True):
+        self.device = torch.device(device)
+        self.fabric = fabric if fabric is not None else ProcessFabric(self.device, group)
+        self.W, self.rank = self.fabric.world, self.fabric.rank
+        if self.W > 16:
+            raise ValueError("at most 16 ranks per node")
+        if S % n_chunks:
+            raise ValueError("S must be divisible by n_chunks")
+        self.S, self.M, self.k, self.n, self.LE = S, M, k, n_chunks, local_experts
+        self.E = local_experts * self.W
+        self.cf = float(capacity_factor)
+        self.dtype = dtype
+        L = _capi.lib()
+        self.Sp = S // n_chunks
+        self.C = L.lancet_moe_capacity(self.Sp, self.E, self.cf * n_chunks, k)
+        item = torch.empty((), dtype=dtype).element_size()
+        self.recv_bytes = _up(self.W * self.LE * self.C * M * item)
+        flag_bytes = _up(16 * 4)
+        total = 2 * self.recv_bytes + self.recv_bytes + flag_bytes
+        bases = self.fabric.alloc(total)
+        mk = lambda off: (ctypes.c_void_p * 16)(*[b + off for b in bases])
+        self.peer_recv = [mk(0), mk(self.recv_bytes)]
+        self.peer_eo = mk(2 * self.recv_bytes)
+        self.peer_flags = mk(3 * self.recv_bytes)
+        self.base = bases[self.rank]
+        d = self.device
+        self.gates_s = torch.empty((n_chunks, k, self.Sp), dtype=torch.float32, device=d)
+        self.idx_loc = torch.empty((n_chunks, 2 * k, self.Sp), dtype=torch.int32, device=d)
+        self.capused = torch.zeros((n_chunks + 1, self.E), dtype=torch.int32, device=d)
+        self.elems = torch.zeros((n_chunks, self.E), dtype=torch.uint64, device=d)
+        self.out = torch.empty((S, M), dtype=dtype, device=d)
+        self.status = torch.zeros(1, dtype=torch.int32, device=d)
+        nws = L.lancet_moe_dispatch_chunked_workspace_bytes(S, self.E, k, n_chunks)
+        self.ws = torch.empty(max(nws, 256), dtype=torch.uint8, device=d)
+        self.timeout_ns = int(timeout_s * 1e9)
+        self.epoch = 0
+        self.parity = 0
+        self.flags = 0 if remote_zero else _capi.P2P_NO_REMOTE_ZERO
+        shape = (self.W, self.LE, self.C, M)
+        self.recv = [tensor_from_ptr(self.base + i * self.recv_bytes, shape, dtype, d) for i in range(2)]
+        self.expert_out = tensor_from_ptr(self.base + 2 * self.recv_bytes, shape, dtype, d)
+        if self.fabric.real and self.W > 1:
+            torch.cuda.synchronize(d)
+            self.fabric.dist.barrier(group=self.fabric.group)
+
+    # -- kernels -------------------------------------------------------------------------------
+    def barrier(self):
+        """All ranks' earlier kernels on this stream have finished when later kernels start."""
+        if not self.fabric.real or self.W == 1:
+            return
+        self.epoch += 1
+        check(_capi.lib().lancet_p2p_barrier(self.peer_flags, self.W, self.rank, self.epoch, self.timeout_ns,
+                                             _ptr(self.status), _stream(self.status)))
+
+    def dispatch(self, x, gate):
+        """Gate all chunks, scatter rows into the owners' receive buffers, meet the peers.
+        Returns this rank's expert input [W, LE, C, M] (block g from rank g)."""
+        self.parity ^= 1
+        check(_capi.lib().lancet_moe_dispatch_chunked_p2p(
+            _ptr(x), _ptr(gate), _DT[gate.dtype], self.cf, self.S, self.M, self.LE, self.W, self.rank, self.k, self.n,
+            _DT[x.dtype], _ptr(self.gates_s), _ptr(self.idx_loc), _ptr(self.capused), _ptr(self.elems),
+            self.peer_recv[self.parity], _ptr(self.ws), self.ws.numel(), self.flags, _stream(x)))
+        self.barrier()
+        return self.recv[self.parity]
+
+    def combine(self, from_expert_out=False, out=None):
+        """Gather the expert outputs of this rank's tokens from their owners and weight them.
+        With from_expert_out the experts have written `self.expert_out`; otherwise the experts are
+        the identity and the receive buffer itself is read back."""
+        out = self.out if out is None else out
+        if from_expert_out:
+            self.barrier()
+            table = self.peer_eo
+        else:
+            table = self.peer_recv[self.parity]
+        check(_capi.lib().lancet_moe_combine_chunked_p2p(
+            table, _ptr(self.gates_s), _ptr(self.idx_loc), self.S, self.M, self.C, self.LE, self.W, self.rank, self.k,
+            self.n, _DT[self.dtype], _ptr(out), _stream(out)))
+        return out
+
+    def check(self):
+        """Raises LancetError(LANCET_ERR_TIMEOUT) if a bounded wait ran out since construction."""
+        check(_capi.lib().lancet_p2p_status(_ptr(self.status), _stream(self.status)))
+
+    def close(self):
+        torch.cuda.synchronize(self.device)
+        self.recv, self.expert_out = None, None
+        self.fabric.close()
