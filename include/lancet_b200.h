@@ -194,14 +194,17 @@ int lancet_p2p_barrier(void* const* peer_flags, int W, int rank, unsigned epoch,
                        int32_t* status, lancet_stream_t stream);
 int lancet_p2p_status(const int32_t* status, lancet_stream_t stream);
 
-enum { LANCET_P2P_NO_REMOTE_ZERO = 1 }; /* do not zero-fill unowned rows of the peers' buffers */
+/* LANCET_P2P_NO_REMOTE_ZERO: do not send zero rows over NVLink; instead the row count of every
+ * (source rank, local expert) block is written to the owner's peer_counts array (int32 [W*LE]) and
+ * the owner zero-fills its tails after the barrier: lancet_moe_zero_tail(recv, counts, M, C, W*LE). */
+enum { LANCET_P2P_NO_REMOTE_ZERO = 1 };
 /* As lancet_moe_dispatch_chunked with E = LE*W, but rows go straight into the owners' receive
- * buffers.  gates_s is float32 [n][k][Sp]. */
+ * buffers.  gates_s is float32 [n][k][Sp].  peer_counts may be null without the flag. */
 int lancet_moe_dispatch_chunked_p2p(const void* x, const void* gate, int gate_dtype, float capacity_factor, int S,
                                     int M, int LE, int W, int rank, int k, int n_chunks, int dtype, void* gates_s,
                                     int32_t* idx_loc, int32_t* capused_chain, uint64_t* elems,
-                                    void* const* peer_recv, void* ws, size_t ws_bytes, int flags,
-                                    lancet_stream_t stream);
+                                    void* const* peer_recv, void* const* peer_counts, void* ws, size_t ws_bytes,
+                                    int flags, lancet_stream_t stream);
 /* As lancet_moe_combine_chunked, gathering rows from the owners' expert output buffers. */
 int lancet_moe_combine_chunked_p2p(void* const* peer_expert_out, const void* gates_s, const int32_t* idx_loc, int S,
                                    int M, int C, int LE, int W, int rank, int k, int n_chunks, int dtype, void* out,

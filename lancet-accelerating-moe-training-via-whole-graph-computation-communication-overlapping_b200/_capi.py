@@ -68,7 +68,8 @@ SIGNATURES = {
     "lancet_p2p_status": (c_int, [c_void_p, c_void_p]),
     "lancet_moe_dispatch_chunked_p2p": (c_int, [c_void_p, c_void_p, c_int, c_float, c_int, c_int, c_int, c_int, c_int,
                                                 c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-                                                ctypes.POINTER(c_void_p), c_void_p, c_size_t, c_int, c_void_p]),
+                                                ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), c_void_p, c_size_t,
+                                                c_int, c_void_p]),
     "lancet_moe_combine_chunked_p2p": (c_int, [ctypes.POINTER(c_void_p), c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                                c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "lancet_lans_workspace_bytes": (c_size_t, [c_int, ctypes.POINTER(c_i64)]),

@@ -33,10 +33,17 @@ __device__ __forceinline__ size_t il_index_p2p(int s, int Sp, int K2, int row) {
 template <typename V, int K>
 __global__ void __launch_bounds__(kP2PThreads)
 dispatch_rows_peer_kernel(const int32_t* __restrict__ idx_loc, const int32_t* __restrict__ rows_used,
-                          const V* __restrict__ x, PeerTable recv, int S, int Sp, int row_vecs, int C, int E, int LE,
-                          int my_rank, int zero_tail) {
+                          const V* __restrict__ x, PeerTable recv, PeerTable counts, int S, int Sp, int row_vecs, int C,
+                          int E, int LE, int my_rank, int zero_tail) {
   constexpr int U = 8;
   const int lane = threadIdx.x & 31;
+  if (!zero_tail && blockIdx.x == 0 && counts.ptr[0] != nullptr) {
+    // tell every owner how many rows of my block it received; it zero-fills the rest locally
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+      const int owner = e / LE, le = e - owner * LE;
+      static_cast<int32_t*>(counts.ptr[owner])[my_rank * LE + le] = rows_used[e];
+    }
+  }
   const long long gw = (long long)blockIdx.x * kP2PWarps + (threadIdx.x >> 5);
   const long long nwarps = (long long)gridDim.x * kP2PWarps;
   const long long ntasks = (long long)S + (zero_tail ? (long long)E * C : 0);
@@ -278,7 +285,8 @@ int lancet_p2p_status(const int32_t* status, lancet_stream_t stream) {
 int lancet_moe_dispatch_chunked_p2p(const void* x, const void* gate, int gate_dtype, float capacity_factor, int S, int M,
                                     int LE, int W, int rank, int k, int n_chunks, int dtype, void* gates_s,
                                     int32_t* idx_loc, int32_t* capused_chain, uint64_t* elems, void* const* peer_recv,
-                                    void* ws, size_t ws_bytes, int flags, lancet_stream_t stream) {
+                                    void* const* peer_counts, void* ws, size_t ws_bytes, int flags,
+                                    lancet_stream_t stream) {
   LANCET_REQUIRE(W >= 1 && W <= kMaxPeers && rank >= 0 && rank < W && LE >= 1, LANCET_ERR_INVALID,
                  "lancet_moe_dispatch_chunked_p2p: bad world %d / rank %d / local experts %d", W, rank, LE);
   LANCET_REQUIRE(n_chunks >= 1 && S >= 0 && S % n_chunks == 0, LANCET_ERR_INVALID,
@@ -297,10 +305,14 @@ int lancet_moe_dispatch_chunked_p2p(const void* x, const void* gate, int gate_dt
   const size_t row_bytes = (size_t)M * dtype_bytes(dtype);
   LANCET_REQUIRE(row_bytes % 16 == 0 && aligned(x, 16), LANCET_ERR_INVALID,
                  "lancet_moe_dispatch_chunked_p2p: rows must be a multiple of 16 bytes and 16-byte aligned");
-  PeerTable t;
+  PeerTable t, tc;
   for (int i = 0; i < kMaxPeers; ++i) t.ptr[i] = i < W ? peer_recv[i] : nullptr;
+  for (int i = 0; i < kMaxPeers; ++i) tc.ptr[i] = (peer_counts && i < W) ? peer_counts[i] : nullptr;
   for (int i = 0; i < W; ++i)
     LANCET_REQUIRE(t.ptr[i] && aligned(t.ptr[i], 16), LANCET_ERR_NULL, "lancet_moe_dispatch_chunked_p2p: peer buffer %d is null or unaligned", i);
+  if (flags & LANCET_P2P_NO_REMOTE_ZERO)
+    for (int i = 0; i < W; ++i)
+      LANCET_REQUIRE(tc.ptr[i], LANCET_ERR_NULL, "lancet_moe_dispatch_chunked_p2p: LANCET_P2P_NO_REMOTE_ZERO needs peer_counts (entry %d is null)", i);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   LANCET_CUDA(cudaMemsetAsync(capused_chain, 0, (size_t)E * sizeof(int32_t), st));
   int rc = lancet_moe_gate_chained(gate, gate_dtype, S, E, k, n_chunks, capused_chain, C, M, gates_s, LANCET_F32, idx_loc,
@@ -314,10 +326,10 @@ int lancet_moe_dispatch_chunked_p2p(const void* x, const void* gate, int gate_dt
   ProfScope prof("dispatch_rows_peer_kernel", st);
   if (k == 1)
     dispatch_rows_peer_kernel<uint4, 1><<<p2p_grid(tasks), kP2PThreads, 0, st>>>(
-        idx_loc, used, static_cast<const uint4*>(x), t, S, Sp > 0 ? Sp : 1, row_vecs, C, E, LE, rank, zero_tail);
+        idx_loc, used, static_cast<const uint4*>(x), t, tc, S, Sp > 0 ? Sp : 1, row_vecs, C, E, LE, rank, zero_tail);
   else
     dispatch_rows_peer_kernel<uint4, 2><<<p2p_grid(tasks), kP2PThreads, 0, st>>>(
-        idx_loc, used, static_cast<const uint4*>(x), t, S, Sp > 0 ? Sp : 1, row_vecs, C, E, LE, rank, zero_tail);
+        idx_loc, used, static_cast<const uint4*>(x), t, tc, S, Sp > 0 ? Sp : 1, row_vecs, C, E, LE, rank, zero_tail);
   return launch_status("dispatch_rows_peer_kernel");
 }
 

@@ -105,7 +105,7 @@ class DistChunkedMoE:
     """Chunk-chained top-k dispatch and combine with the all-to-all fused into the kernels."""
 
     def __init__(self, S, M, k=2, capacity_factor=1.25, n_chunks=4, dtype=torch.float16, device="cuda",
-                 local_experts=2, fabric=None, group=None, timeout_s=5.0, remote_zero=True):
+                 local_experts=2, fabric=None, group=None, timeout_s=5.0, remote_zero=False):
         self.device = torch.device(device)
         self.fabric = fabric if fabric is not None else ProcessFabric(self.device, group)
         self.W, self.rank = self.fabric.world, self.fabric.rank
@@ -123,12 +123,15 @@ class DistChunkedMoE:
         item = torch.empty((), dtype=dtype).element_size()
         self.recv_bytes = _up(self.W * self.LE * self.C * M * item)
         flag_bytes = _up(16 * 4)
-        total = 2 * self.recv_bytes + self.recv_bytes + flag_bytes
+        cnt_bytes = _up(self.W * self.LE * 4)
+        total = 3 * self.recv_bytes + flag_bytes + 2 * cnt_bytes
         bases = self.fabric.alloc(total)
         mk = lambda off: (ctypes.c_void_p * 16)(*[b + off for b in bases])
         self.peer_recv = [mk(0), mk(self.recv_bytes)]
         self.peer_eo = mk(2 * self.recv_bytes)
         self.peer_flags = mk(3 * self.recv_bytes)
+        cnt_off = 3 * self.recv_bytes + flag_bytes
+        self.peer_counts = [mk(cnt_off), mk(cnt_off + cnt_bytes)]
         self.base = bases[self.rank]
         d = self.device
         self.gates_s = torch.empty((n_chunks, k, self.Sp), dtype=torch.float32, device=d)
@@ -146,6 +149,8 @@ class DistChunkedMoE:
         shape = (self.W, self.LE, self.C, M)
         self.recv = [tensor_from_ptr(self.base + i * self.recv_bytes, shape, dtype, d) for i in range(2)]
         self.expert_out = tensor_from_ptr(self.base + 2 * self.recv_bytes, shape, dtype, d)
+        self.counts = [tensor_from_ptr(self.base + cnt_off + i * cnt_bytes, (self.W * self.LE,), torch.int32, d)
+                       for i in range(2)]
         if self.fabric.real and self.W > 1:
             torch.cuda.synchronize(d)
             self.fabric.dist.barrier(group=self.fabric.group)
@@ -162,12 +167,24 @@ class DistChunkedMoE:
     def dispatch(self, x, gate):
         """Gate all chunks, scatter rows into the owners' receive buffers, meet the peers.
         Returns this rank's expert input [W, LE, C, M] (block g from rank g)."""
+        self.dispatch_send(x, gate)
+        return self.dispatch_finish()
+
+    def dispatch_send(self, x, gate):
         self.parity ^= 1
         check(_capi.lib().lancet_moe_dispatch_chunked_p2p(
             _ptr(x), _ptr(gate), _DT[gate.dtype], self.cf, self.S, self.M, self.LE, self.W, self.rank, self.k, self.n,
             _DT[x.dtype], _ptr(self.gates_s), _ptr(self.idx_loc), _ptr(self.capused), _ptr(self.elems),
-            self.peer_recv[self.parity], _ptr(self.ws), self.ws.numel(), self.flags, _stream(x)))
+            self.peer_recv[self.parity], self.peer_counts[self.parity], _ptr(self.ws), self.ws.numel(), self.flags,
+            _stream(x)))
+
+    def dispatch_finish(self):
+        x = self.out
         self.barrier()
+        if self.flags & _capi.P2P_NO_REMOTE_ZERO:
+            # every source told us how many rows of its block are live; the rest is zero-filled here
+            check(_capi.lib().lancet_moe_zero_tail(_ptr(self.recv[self.parity]), _ptr(self.counts[self.parity]),
+                                                   self.M, self.C, self.W * self.LE, _DT[self.dtype], _stream(x)))
         return self.recv[self.parity]
 
     def combine(self, from_expert_out=False, out=None):
@@ -191,5 +208,5 @@ class DistChunkedMoE:
 
     def close(self):
         torch.cuda.synchronize(self.device)
-        self.recv, self.expert_out = None, None
+        self.recv, self.expert_out, self.counts = None, None, None
         self.fabric.close()

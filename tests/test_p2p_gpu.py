@@ -50,11 +50,12 @@ def test_virtual_ranks_match_oracle(W, S, M, k, n, cf, remote_zero):
     xs = [torch.from_numpy(rng.standard_normal((S, M)).astype(np.float32)).half() for _ in range(W)]
     gates = [torch.softmax(torch.from_numpy(rng.standard_normal((S, E)).astype(np.float32)), dim=1) for _ in range(W)]
     for rep in range(2):                       # two steps: exercises the double-buffered receive side
-        if not remote_zero:
-            for p in plans:
-                for b in p.recv:
-                    b.zero_()
-        recvs = [p.dispatch(xs[r].to(DEV), gates[r].to(DEV)) for r, p in enumerate(plans)]
+        for p in plans:                        # stale contents must not survive
+            for b in p.recv:
+                b.fill_(5.0)
+        for r, p in enumerate(plans):          # virtual ranks: all sends, then all local finishes
+            p.dispatch_send(xs[r].to(DEV), gates[r].to(DEV))
+        recvs = [p.dispatch_finish() for p in plans]
         torch.cuda.synchronize()
         enc = [oracle_rank_encode(xs[r].numpy(), gates[r].numpy(), E, k, n, cf) for r in range(W)]
         want_recv = O.all_to_all([e[0] for e in enc])               # [E,C,M] viewed [W, LE*C*M]
