@@ -153,7 +153,7 @@ def run_reference_arm(args):
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def moe_config(world):
@@ -284,7 +284,8 @@ def run_moe(args):
         if world > 1:
             # the fused dispatch is bound by the bytes that leave this GPU over NVLink: (W-1)/W of the
             # padded expert buffer; peak = the pool's measured peer-copy bandwidth per direction
-            nv_bytes = E * plan.C * row_bytes * (world - 1) / world
+            remote_rows = int(cap[-1][plan.LE:].sum())          # rank 0 owns experts [0, LE): the rest crosses NVLink
+            nv_bytes = remote_rows * row_bytes
             nv = nv_bytes / avg_s / 1e9
             roof.update({"bound": "nvlink", "achieved": nv, "peak": 770.0, "frac": nv / 770.0,
                          "peak_kind": "measured peer copy, per direction", "bytes_per_launch": nv_bytes,
@@ -308,13 +309,13 @@ def run_moe(args):
     if world == 1 and not args.no_cpu:
         rate, cores, sample, _, _ = cpu_reference_sample(15.0, 1)
         line["cpu_baseline"] = {"value": rate, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample}
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
-def lans_shapes():
+def lans_shapes(layers=24):
     """196 fp32 tensors, 354.6 M elements: GPT-2-medium-like (24 layers x 8 tensors + embeddings + final norm)."""
     shapes = [(50257, 1024), (1024, 1024)]
-    for _ in range(24):
+    for _ in range(layers):
         shapes += [(1024, 1024), (1024, 1024), (1024, 1024), (1024, 1024), (4096, 1024), (1024, 4096), (1024,), (1024,)]
     shapes += [(1024,), (1024,)]
     return shapes
@@ -326,7 +327,7 @@ def run_lans(args):
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
     torch.cuda.set_device(dev)
     L = _capi.lib()
-    shapes = lans_shapes()
+    shapes = lans_shapes(args.lans_layers)
     g = torch.Generator(device=dev).manual_seed(0)
     P = [torch.randn(s, device=dev, generator=g) * 0.02 for s in shapes]
     G = [torch.randn(s, device=dev, generator=g) * 1e-3 for s in shapes]
@@ -368,10 +369,30 @@ def run_lans(args):
                      "bytes_per_launch": 24.0 * n_el, "avg_launch_us": avg_s * 1e6},
         "step_hbm_frac": 52.0 * n_el / (ms / 1e3) / 1e9 / hbm_peak,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def main():
+    # libraries (NCCL, torchrun) may write to stdout; keep it clean for the one JSON line
+    saved_stdout = os.dup(1)
+    os.dup2(2, 1)
+    try:
+        _main()
+    finally:
+        sys.stdout.flush()
+        os.dup2(saved_stdout, 1)
+        if _RESULT_LINES:
+            os.write(1, ("\n".join(_RESULT_LINES) + "\n").encode())
+
+
+_RESULT_LINES = []
+
+
+def emit(line):
+    _RESULT_LINES.append(json.dumps(line))
+
+
+def _main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=2000)
@@ -379,6 +400,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="moe", choices=["moe", "lans"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--lans-layers", type=int, default=24, help="transformer layers in the LANS tensor list (24 = 196 tensors)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
