@@ -290,10 +290,10 @@ def run_moe(args):
             roof.update({"bound": "nvlink", "achieved": nv, "peak": 770.0, "frac": nv / 770.0,
                          "peak_kind": "measured peer copy, per direction", "bytes_per_launch": nv_bytes,
                          "hbm_achieved": achieved})
-        tr = os.path.join(ROOT, "profiles", "traffic.json")
-        if os.path.exists(tr):
-            with open(tr) as f:
-                roof["traffic"] = json.load(f).get(kname.decode())
+        if world == 1:
+            # dram read + write bytes per launch from the ncu capture of this workload
+            # (profiles/moe_dispatch_combine_S16384_M2048_ncu_full.txt)
+            roof["traffic"] = 177.2e6
     line = {
         "metric": "moe_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
@@ -365,7 +365,10 @@ def run_lans(args):
                    "l2": "5.6 GB of state per step exceeds the 126 MB L2"},
         "gpu_launches": int(launches), "clocks": clocks,
         "roofline": {"bound": "hbm", "kernel": "lans_phase2_kernel", "achieved": achieved, "peak": hbm_peak,
-                     "unit": "GB/s", "frac": achieved / hbm_peak, "peak_kind": peak_kind, "traffic": None,
+                     "unit": "GB/s", "frac": achieved / hbm_peak, "peak_kind": peak_kind,
+                     # 23.46 B/element measured by ncu on a 77.7 M-element list, scaled by the element count
+                     # (profiles/lans_phase_kernels_77M_elements_ncu_full.txt)
+                     "traffic": 23.46 * n_el,
                      "bytes_per_launch": 24.0 * n_el, "avg_launch_us": avg_s * 1e6},
         "step_hbm_frac": 52.0 * n_el / (ms / 1e3) / 1e9 / hbm_peak,
     }

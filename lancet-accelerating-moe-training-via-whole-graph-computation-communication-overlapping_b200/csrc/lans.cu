@@ -36,6 +36,7 @@ struct LansTensor {
 
 struct LansHyper {
   float lr, beta1, beta2, beta3, eps, bc1, bc2, wd;
+  float inv_bc1, inv_bc2;  // reciprocals: one IEEE division per element instead of four
   int mode, normalize_grad;
 };
 
@@ -122,43 +123,33 @@ __device__ __forceinline__ void finish_tensor(float2 mine, float2* __restrict__ 
   }
 }
 
-__device__ __forceinline__ void lans_directions(float g, float p, float& m, float& v, float gnorm, const LansHyper& h,
+// `inv_gn` is 1 / (||g|| + eps) when the gradient is normalised, else 1.  Multiplying by reciprocals
+// instead of dividing changes results by at most a few ulp, far inside the 1e-5 tolerance.
+__device__ __forceinline__ void lans_directions(float g, float p, float& m, float& v, float inv_gn, const LansHyper& h,
                                                 float& um, float& ug) {
-  float sg = g;
-  if (h.normalize_grad && gnorm != 0.0f) sg = g / (gnorm + h.eps);
-  if (h.mode == 0) {
-    sg = sg + h.wd * p;
-    m = m * h.beta1 + h.beta3 * sg;
-    v = v * h.beta2 + (1.0f - h.beta2) * sg * sg;
-    const float denom = sqrtf(v / h.bc2) + h.eps;
-    um = (m / h.bc1) / denom;
-    ug = sg / denom;
-  } else {
-    m = m * h.beta1 + h.beta3 * sg;
-    v = v * h.beta2 + (1.0f - h.beta2) * sg * sg;
-    const float denom = sqrtf(v / h.bc2) + h.eps;
-    const float sp = h.wd * p;
-    um = (m / h.bc1) / denom + sp;
-    ug = sg / denom + sp;
-  }
+  float sg = g * inv_gn;
+  if (h.mode == 0) sg = sg + h.wd * p;
+  m = m * h.beta1 + h.beta3 * sg;
+  v = v * h.beta2 + (1.0f - h.beta2) * sg * sg;
+  const float r = __frcp_rn(sqrtf(v * h.inv_bc2) + h.eps);
+  const float sp = h.mode == 0 ? 0.0f : h.wd * p;
+  um = (m * h.inv_bc1) * r + sp;
+  ug = sg * r + sp;
 }
 
 // Same as above with m, v already updated (phase 3).
-__device__ __forceinline__ void lans_directions_post(float g, float p, float m, float v, float gnorm, const LansHyper& h,
-                                                     float& um, float& ug) {
-  float sg = g;
-  if (h.normalize_grad && gnorm != 0.0f) sg = g / (gnorm + h.eps);
-  if (h.mode == 0) {
-    sg = sg + h.wd * p;
-    const float denom = sqrtf(v / h.bc2) + h.eps;
-    um = (m / h.bc1) / denom;
-    ug = sg / denom;
-  } else {
-    const float denom = sqrtf(v / h.bc2) + h.eps;
-    const float sp = h.wd * p;
-    um = (m / h.bc1) / denom + sp;
-    ug = sg / denom + sp;
-  }
+__device__ __forceinline__ void lans_directions_post(float g, float p, float m, float v, float inv_gn,
+                                                     const LansHyper& h, float& um, float& ug) {
+  float sg = g * inv_gn;
+  if (h.mode == 0) sg = sg + h.wd * p;
+  const float r = __frcp_rn(sqrtf(v * h.inv_bc2) + h.eps);
+  const float sp = h.mode == 0 ? 0.0f : h.wd * p;
+  um = (m * h.inv_bc1) * r + sp;
+  ug = sg * r + sp;
+}
+
+__device__ __forceinline__ float grad_scale(float gnorm, const LansHyper& h) {
+  return (h.normalize_grad && gnorm != 0.0f) ? 1.0f / (gnorm + h.eps) : 1.0f;
 }
 
 struct ChunkView {
@@ -218,7 +209,7 @@ lans_phase2_kernel(const LansTensor* __restrict__ tensors, int n, LansHyper h, f
   const int t = find_tensor(tensors, n, chunk);
   const LansTensor T = tensors[t];
   const ChunkView c = chunk_view(T, chunk, true);
-  const float gnorm = __ldcg(reinterpret_cast<const float*>(norms + t));
+  const float gnorm = grad_scale(__ldcg(reinterpret_cast<const float*>(norms + t)), h);
   const float4* g4 = reinterpret_cast<const float4*>(T.g + c.off);
   const float4* p4 = reinterpret_cast<const float4*>(T.p + c.off);
   float4* m4 = reinterpret_cast<float4*>(T.m + c.off);
@@ -258,6 +249,7 @@ lans_phase3_kernel(const LansTensor* __restrict__ tensors, int n, LansHyper h, c
   float rg = (nr.w != 0.0f && nr.y != 0.0f) ? h.lr * (nr.y / nr.w) : h.lr;
   rm *= h.beta1;
   rg *= h.beta3;
+  const float inv_gn = grad_scale(nr.x, h);
   const float4* g4 = reinterpret_cast<const float4*>(T.g + c.off);
   float4* p4 = reinterpret_cast<float4*>(T.p + c.off);
   const float4* m4 = reinterpret_cast<const float4*>(T.m + c.off);
@@ -266,16 +258,16 @@ lans_phase3_kernel(const LansTensor* __restrict__ tensors, int n, LansHyper h, c
     const float4 g = g4[i], m = m4[i], v = v4[i];
     float4 p = p4[i];
     float um, ug;
-    lans_directions_post(g.x, p.x, m.x, v.x, nr.x, h, um, ug); p.x = p.x - rm * um - rg * ug;
-    lans_directions_post(g.y, p.y, m.y, v.y, nr.x, h, um, ug); p.y = p.y - rm * um - rg * ug;
-    lans_directions_post(g.z, p.z, m.z, v.z, nr.x, h, um, ug); p.z = p.z - rm * um - rg * ug;
-    lans_directions_post(g.w, p.w, m.w, v.w, nr.x, h, um, ug); p.w = p.w - rm * um - rg * ug;
+    lans_directions_post(g.x, p.x, m.x, v.x, inv_gn, h, um, ug); p.x = p.x - rm * um - rg * ug;
+    lans_directions_post(g.y, p.y, m.y, v.y, inv_gn, h, um, ug); p.y = p.y - rm * um - rg * ug;
+    lans_directions_post(g.z, p.z, m.z, v.z, inv_gn, h, um, ug); p.z = p.z - rm * um - rg * ug;
+    lans_directions_post(g.w, p.w, m.w, v.w, inv_gn, h, um, ug); p.w = p.w - rm * um - rg * ug;
     p4[i] = p;
   }
   for (int e = c.nvec * 4 + threadIdx.x; e < c.n; e += kLansThreads) {
     float um, ug;
     const float p = T.p[c.off + e];
-    lans_directions_post(T.g[c.off + e], p, T.m[c.off + e], T.v[c.off + e], nr.x, h, um, ug);
+    lans_directions_post(T.g[c.off + e], p, T.m[c.off + e], T.v[c.off + e], inv_gn, h, um, ug);
     T.p[c.off + e] = p - rm * um - rg * ug;
   }
 }
@@ -348,6 +340,8 @@ int lancet_lans(void* ws, size_t ws_bytes, int n_tensors, const int64_t* numels,
     h.bc2 = (float)(1 - std::pow((double)beta2, step));
   }
   h.beta3 = grad_averaging == 1 ? 1 - beta1 : 1.0f;
+  h.inv_bc1 = 1.0f / h.bc1;
+  h.inv_bc2 = 1.0f / h.bc2;
   float2* part1 = reinterpret_cast<float2*>(base + L.part1_off);
   float2* part2 = reinterpret_cast<float2*>(base + L.part2_off);
   float4* norms = reinterpret_cast<float4*>(base + L.norms_off);
