@@ -210,6 +210,29 @@ int lancet_moe_combine_chunked_p2p(void* const* peer_expert_out, const void* gat
                                    int M, int C, int LE, int W, int rank, int k, int n_chunks, int dtype, void* out,
                                    lancet_stream_t stream);
 
+/* ---- `_all_to_all` / `_all_to_allv` as stand-alone operators ------------------------------------
+ * NCCL transport: replaces NCCLAllToAll::Execute (src/op/dialect/nccl/nccl.cc:199-227): W grouped
+ * ncclSend/ncclRecv pairs of bytes_per_rank bytes on `stream`; any device buffers.  The
+ * communicator replaces src/distributed/cuda/nccl_communicator.cc:27-60: rank 0 makes the 128-byte
+ * id, the caller broadcasts it over its own host channel (the reference uses MPI). */
+int lancet_comm_unique_id(unsigned char* id128);
+int lancet_comm_init_rank(const unsigned char* id128, int world, int rank, lancet_comm_t* comm);
+int lancet_comm_destroy(lancet_comm_t comm);
+int lancet_all_to_all(const void* send, void* recv, size_t bytes_per_rank, lancet_comm_t comm,
+                      lancet_stream_t stream);
+/* Peer-memory transport for receive buffers in symmetric memory: one kernel stores chunk i of
+ * `send` into block `rank` of peer_recv[i].  Follow with lancet_p2p_barrier before reading. */
+int lancet_all_to_all_p2p(const void* send, void* const* peer_recv, size_t bytes_per_rank, int W, int rank,
+                          lancet_stream_t stream);
+/* Count-aware all-to-all, replaces NCCLAllToAllv::Execute (nccl.cc:357-431) without its host
+ * round trip: send is [W][n_chunks][chunk_elems]; for (peer i, chunk j) only the first
+ * send_counts[i*n_chunks+j] elements (device uint64) travel, the rest of the destination chunk is
+ * zero; the destination's recv_counts[rank*n_chunks+j] (uint64, peer_recv_counts[i]) receives the
+ * count.  Follow with lancet_p2p_barrier. */
+int lancet_all_to_allv_p2p(const void* send, void* const* peer_recv, const uint64_t* send_counts,
+                           void* const* peer_recv_counts, int n_chunks, size_t elem_size, size_t chunk_elems,
+                           int W, int rank, lancet_stream_t stream);
+
 /* ---- LANS optimizer ---------------------------------------------------------------------------
  * Replaces multi_tensor_lans_cuda (kernel_util.cuh:26-34; multi_tensor_lans.cu:401-450) and the
  * host side of LansImpl::Execute (src/op/dialect/cuda/lans.cc:92-148).  g/p/m/v are HOST arrays of

@@ -72,6 +72,13 @@ SIGNATURES = {
                                                 c_int, c_void_p]),
     "lancet_moe_combine_chunked_p2p": (c_int, [ctypes.POINTER(c_void_p), c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                                c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "lancet_comm_unique_id": (c_int, [ctypes.c_char_p]),
+    "lancet_comm_init_rank": (c_int, [ctypes.c_char_p, c_int, c_int, ctypes.POINTER(c_void_p)]),
+    "lancet_comm_destroy": (c_int, [c_void_p]),
+    "lancet_all_to_all": (c_int, [c_void_p, c_void_p, c_size_t, c_void_p, c_void_p]),
+    "lancet_all_to_all_p2p": (c_int, [c_void_p, ctypes.POINTER(c_void_p), c_size_t, c_int, c_int, c_void_p]),
+    "lancet_all_to_allv_p2p": (c_int, [c_void_p, ctypes.POINTER(c_void_p), c_void_p, ctypes.POINTER(c_void_p), c_int,
+                                       c_size_t, c_size_t, c_int, c_int, c_void_p]),
     "lancet_lans_workspace_bytes": (c_size_t, [c_int, ctypes.POINTER(c_i64)]),
     "lancet_lans": (c_int, [c_void_p, c_size_t, c_int, ctypes.POINTER(c_i64), ctypes.POINTER(c_void_p),
                             ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), c_int, c_int,

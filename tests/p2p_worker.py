@@ -39,7 +39,36 @@ def main():
         np.testing.assert_array_equal(recv.cpu().numpy().reshape(E, -1, M), want_recv[rank])
         np.testing.assert_array_equal(out.cpu().numpy().astype(np.float32),
                                       torch.from_numpy(ref).half().float().numpy())
+    # stand-alone _all_to_all over NCCL: rank r sends rows filled with r+1, expects row i = i+1
+    # (tests/python/distributed/test_alltoall.py:22-59 of the reference)
+    comm = LB.Communicator(dev)
+    x = torch.full((world, 4), float(rank + 1), device=dev)
+    y = comm.all_to_all(x)
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(y.cpu().numpy(), np.arange(1, world + 1, dtype=np.float32)[:, None] * np.ones((1, 4), np.float32))
+    big = torch.from_numpy(np.random.default_rng(rank).standard_normal((world, 1 << 18)).astype(np.float32)).to(dev)
+    back = comm.all_to_all(comm.all_to_all(big))
+    torch.cuda.synchronize()
+    assert torch.equal(back, big)
+    # the same exchange over peer memory, and the count-aware variant
+    sa = LB.SymmAllToAll(big.numel() * 4, dev, n_chunks=2)
+    got = sa.all_to_all(big)
+    torch.cuda.synchronize()
+    assert torch.equal(got, comm.all_to_all(big))
+    counts = torch.tensor([(i + j + rank) % 4 + 1 for i in range(world) for j in range(2)], dtype=torch.int64, device=dev)
+    gv, rc = sa.all_to_allv(big, counts)
+    torch.cuda.synchronize()
+    sa.check()
+    chunk = big.numel() // (world * 2)
+    gvh, bigs = gv.cpu().numpy().reshape(world, 2, chunk), None
+    for i in range(world):
+        for j in range(2):
+            c = (rank + j + i) % 4 + 1          # what rank i sent us for chunk j
+            assert rc.cpu().numpy()[i * 2 + j] == c
+            assert np.all(gvh[i, j, c:] == 0)
+    comm.close()
     dist.barrier()
+    sa.close()
     plan.close()
     if rank == 0:
         print("p2p worker ok")

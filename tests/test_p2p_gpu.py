@@ -118,3 +118,43 @@ def test_two_processes_over_nvlink():
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "p2p worker ok" in r.stdout
+
+
+def test_all_to_all_peer_memory_virtual_ranks():
+    """tests/python/distributed/test_alltoall.py:22-59 pattern and a random payload, W virtual ranks."""
+    W, n = 4, 4 * 1024
+    shared = {}
+    ops = [LB.SymmAllToAll(n * 4, DEV, fabric=LB.LocalFabric(W, r, shared)) for r in range(W)]
+    rng = np.random.default_rng(9)
+    bufs = [rng.standard_normal((W, n // W)).astype(np.float32) for _ in range(W)]
+    bufs[0][:] = 1.0
+    xs = [torch.from_numpy(b).to(DEV) for b in bufs]
+    for r in range(W):
+        ops[r].send(xs[r])
+    torch.cuda.synchronize()
+    want = O.all_to_all(bufs)
+    for r in range(W):
+        np.testing.assert_array_equal(ops[r].recv_view(xs[r]).cpu().numpy(), want[r])
+
+
+def test_all_to_allv_peer_memory_virtual_ranks():
+    """Counts (i + j + rank) % 4 + 1 as tests/python/distributed/test_alltoall.py:61-122, plus ragged
+    counts that end inside a 16-byte word and a full chunk."""
+    W, nch, chunk = 2, 3, 24
+    shared = {}
+    ops = [LB.SymmAllToAll(W * nch * chunk * 4, DEV, fabric=LB.LocalFabric(W, r, shared), n_chunks=nch) for r in range(W)]
+    rng = np.random.default_rng(10)
+    bufs = [rng.standard_normal((W, nch * chunk)).astype(np.float32) for _ in range(W)]
+    scs = [np.array([(i + j + r) % 4 + 1 for i in range(W) for j in range(nch)], np.uint64) for r in range(W)]
+    scs[0][1] = chunk
+    scs[1][2] = 0
+    scs[1][4] = 7
+    xs = [torch.from_numpy(b).to(DEV) for b in bufs]
+    for r in range(W):
+        ops[r].recv_view(xs[r]).fill_(9.0)
+        ops[r].sendv(xs[r], torch.from_numpy(scs[r].astype(np.int64)).to(DEV))
+    torch.cuda.synchronize()
+    want, want_rc = O.all_to_allv(bufs, scs, nch)
+    for r in range(W):
+        np.testing.assert_array_equal(ops[r].recv_view(xs[r]).cpu().numpy(), want[r])
+        np.testing.assert_array_equal(ops[r].counts_view().cpu().numpy().astype(np.uint64), want_rc[r])
