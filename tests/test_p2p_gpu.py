@@ -152,6 +152,7 @@ def test_all_to_allv_peer_memory_virtual_ranks():
     xs = [torch.from_numpy(b).to(DEV) for b in bufs]
     for r in range(W):
         ops[r].recv_view(xs[r]).fill_(9.0)
+    for r in range(W):
         ops[r].sendv(xs[r], torch.from_numpy(scs[r].astype(np.int64)).to(DEV))
     torch.cuda.synchronize()
     want, want_rc = O.all_to_allv(bufs, scs, nch)
