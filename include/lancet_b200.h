@@ -233,6 +233,20 @@ int lancet_all_to_allv_p2p(const void* send, void* const* peer_recv, const uint6
                            void* const* peer_recv_counts, int n_chunks, size_t elem_size, size_t chunk_elems,
                            int W, int rank, lancet_stream_t stream);
 
+/* ---- expert FFN grouped GEMM (tcgen05 tensor cores, TMEM accumulators, TMA operand tiles) -------
+ * Replaces the cuBLAS calls of the expert layers: GemmImpl (src/op/dialect/cublas/matmul.cc:30-78),
+ * SparseExpertMatmulNtImpl (:211-303) and the per-expert loop of Experts.forward
+ * (models/benchmark/pytorch/utils.py:546-562).  D[g] = act(A[g] * B[g % LE]^T + bias[g % LE]) for
+ * g in [0, groups): A [groups][C][K], B [LE][N][K] (nn.Linear layout), D [groups][C][N], all bf16 or
+ * fp16 with fp32 accumulation; bias [LE][N] and preact (copy of the pre-activation, [groups][C][N])
+ * nullable.  counts (nullable, device int32 [groups]): only the first counts[g] rows of group g are
+ * computed and written.  act: 0 none, 1 relu, 2 gelu (erf), 3 gelu (tanh).  N % 256 == 0, K % 8 == 0.
+ * status: device int32, zero when healthy; a bounded wait that gave up stores its site there
+ * (read it with lancet_p2p_status). */
+int lancet_grouped_gemm_nt(const void* A, const void* B, void* D, const void* bias, void* preact, int groups,
+                           int LE, int C, int N, int K, const int32_t* counts, int act, int dtype,
+                           int32_t* status, lancet_stream_t stream);
+
 /* ---- LANS optimizer ---------------------------------------------------------------------------
  * Replaces multi_tensor_lans_cuda (kernel_util.cuh:26-34; multi_tensor_lans.cu:401-450) and the
  * host side of LansImpl::Execute (src/op/dialect/cuda/lans.cc:92-148).  g/p/m/v are HOST arrays of

@@ -1,0 +1,418 @@
+// Expert FFN grouped GEMM on the Blackwell tensor cores (tcgen05 + TMEM + TMA).
+//
+// Replaces the cuBLAS calls behind the reference's expert layers: GemmImpl
+// (src/op/dialect/cublas/matmul.cc:30-78, fp16/bf16 inputs with fp32 accumulation),
+// SparseExpertMatmulNtImpl (:211-303, which as shipped multiplies the whole padded buffer) and the
+// per-expert loop of Experts.forward (models/benchmark/pytorch/utils.py:546-562).
+//
+//   D[g] = act(A[g] * B[e(g)]^T + bias[e(g)])        g = group = (source rank, local expert)
+//
+// A is the post-exchange expert input [groups][C][K] (row blocks of C rows, K contiguous), B the
+// expert weights [LE][N][K] in nn.Linear layout (K contiguous), D [groups][C][N].  Only the first
+// counts[g] rows of a group are live: tiles past them are skipped, which is what the reference's
+// count-aware path intended (cublas/matmul.cc:221-247, commented out there).
+//
+// One persistent CTA per SM walks a static list of 128 x 256 output tiles.  Warp 0 is the TMA
+// producer (cp.async.bulk.tensor into 128-byte-swizzled shared memory, 4 stages of 64-wide K
+// blocks), warp 1 issues tcgen05.mma (one thread) into one of two 256-column TMEM accumulators,
+// warps 2-5 are the epilogue (tcgen05.ld, bias + activation, 16-byte stores), so the epilogue of
+// tile i overlaps the main loop of tile i+1.  Every mbarrier wait is bounded: when a limit runs
+// out the CTA raises an abort flag, records the site in *status, lets copies in flight land, frees
+// its TMEM and returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace lancet {
+namespace gemm {
+
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
+constexpr int UMMA_K = 16;
+constexpr int A_STAGE_BYTES = BM * BK * 2;   // 16 KB
+constexpr int B_STAGE_BYTES = BN * BK * 2;   // 32 KB
+constexpr int SMEM_DATA = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES);
+constexpr int SMEM_BYTES = SMEM_DATA + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int THREADS = 192;                 // warps: 0 TMA, 1 MMA, 2..5 epilogue
+constexpr int TMEM_COLS = 512;               // two accumulators of BN fp32 columns
+constexpr int BAND = 16;                     // m-tiles per band (L2 reuse of A against a sweep of B)
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
+
+struct Params {
+  int groups, LE, C, N, K;
+  int m_tiles, n_tiles, tiles_per_group, total_tiles;
+  const int32_t* counts;  // [groups] live rows, or null
+  const void* bias;       // [LE][N] or null
+  void* D;
+  void* preact;           // optional copy of the pre-activation values
+  int act;                // 0 none, 1 relu, 2 gelu (erf), 3 gelu (tanh)
+  int* status;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ unsigned long long now_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false when the limit ran out or another role already gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int site) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = now_ns();
+  while (true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (now_ns() - t0 > WAIT_LIMIT_NS) {
+      *abort_flag = 1;
+      atomicCAS(status, 0, site);
+      return false;
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accum) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accum)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile stored as rows of 64 bf16 (128 bytes) with the
+// 128-byte swizzle TMA applies: 8 rows form a 1024-byte atom, atoms follow each other along M/N.
+__device__ __forceinline__ uint64_t smem_desc_k_sw128(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr >> 4) & 0x3FFF);   // start address
+  d |= (uint64_t)1 << 16;                  // leading byte offset (unused with swizzle, canonical value 1)
+  d |= (uint64_t)(1024 >> 4) << 32;        // stride byte offset: next group of 8 rows
+  d |= (uint64_t)1 << 46;                  // descriptor version of this architecture
+  d |= (uint64_t)2 << 61;                  // 128-byte swizzle
+  return d;
+}
+
+template <typename T>
+__device__ __forceinline__ uint32_t instr_desc() {
+  const uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;  // 0 = f16, 1 = bf16
+  return (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);  // D = f32, K-major A and B
+}
+
+struct Tile {
+  int group, mt, nt, rows;  // rows = live rows of the group
+  bool live;
+};
+
+__device__ __forceinline__ Tile decode_tile(const Params& p, int t) {
+  Tile tl;
+  tl.group = t / p.tiles_per_group;
+  int r = t - tl.group * p.tiles_per_group;
+  const int band_tiles = BAND * p.n_tiles;
+  const int band = r / band_tiles;
+  r -= band * band_tiles;
+  const int m_in_band = min(BAND, p.m_tiles - band * BAND);
+  tl.nt = r / m_in_band;
+  tl.mt = band * BAND + (r - tl.nt * m_in_band);
+  int rows = p.C;
+  if (p.counts) {
+    rows = p.counts[tl.group];
+    rows = rows < 0 ? 0 : (rows > p.C ? p.C : rows);
+  }
+  tl.rows = rows;
+  tl.live = tl.nt < p.n_tiles && tl.mt * BM < rows;
+  return tl;
+}
+
+__device__ __forceinline__ float activate(float v, int act) {
+  if (act == 1) return fmaxf(v, 0.f);
+  if (act == 2) return 0.5f * v * (1.0f + erff(v * 0.70710678118654752f));
+  if (act == 3) return 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+  return v;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(THREADS, 1)
+grouped_gemm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, Params p) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  unsigned char* sA = smem;
+  unsigned char* sB = smem + STAGES * A_STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SMEM_DATA);
+  // barriers: full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2]
+  const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + STAGES);
+  const uint32_t bar_tfull = smem_u32(bars + 2 * STAGES), bar_tempty = smem_u32(bars + 2 * STAGES + 2);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar_tfull + 8 * b, 1);
+      mbar_init(bar_tempty + 8 * b, 4);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int k_blocks = (p.K + BK - 1) / BK;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
+        const Tile tl = decode_tile(p, t);
+        if (!tl.live) continue;
+        const int a_row = tl.group * p.C + tl.mt * BM;
+        const int b_row = (tl.group % p.LE) * p.N + tl.nt * BN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!(ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, p.status, 1))) break;
+          mbar_expect_tx(bar_full + 8 * stage, A_STAGE_BYTES + B_STAGE_BYTES);
+          tma_load_2d(smem_u32(sA + stage * A_STAGE_BYTES), &tmA, bar_full + 8 * stage, kb * BK, a_row);
+          tma_load_2d(smem_u32(sB + stage * B_STAGE_BYTES), &tmB, bar_full + 8 * stage, kb * BK, b_row);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      const uint32_t idesc = instr_desc<T>();
+      int stage = 0;
+      uint32_t phase = 0;
+      int buf = 0;
+      uint32_t tphase[2] = {0, 0};
+      bool ok = true;
+      for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
+        const Tile tl = decode_tile(p, t);
+        if (!tl.live) continue;
+        if (!(ok = mbar_wait(bar_tempty + 8 * buf, tphase[buf] ^ 1, abort_flag, p.status, 2))) break;
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!(ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status, 3))) break;
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(sA + stage * A_STAGE_BYTES);
+          const uint32_t b_addr = smem_u32(sB + stage * B_STAGE_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t adesc = smem_desc_k_sw128(a_addr + k * UMMA_K * 2);
+            const uint64_t bdesc = smem_desc_k_sw128(b_addr + k * UMMA_K * 2);
+            umma_f16(tmem_d, adesc, bdesc, idesc, (kb | k) ? 1u : 0u);
+          }
+          umma_commit(bar_empty + 8 * stage);  // frees the stage when these MMAs have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(bar_tfull + 8 * buf);      // accumulator complete
+        tphase[buf] ^= 1;
+        buf ^= 1;
+      }
+    }
+  } else {
+    // ---------------- epilogue: warps 2..5, TMEM lane quadrant = warp % 4 ----------------
+    const int quad = warp & 3;
+    int buf = 0;
+    uint32_t tphase[2] = {0, 0};
+    bool ok = true;
+    T* D = static_cast<T*>(p.D);
+    T* PRE = static_cast<T*>(p.preact);
+    const T* bias = static_cast<const T*>(p.bias);
+    for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
+      const Tile tl = decode_tile(p, t);
+      if (!tl.live) continue;
+      ok = mbar_wait(bar_tfull + 8 * buf, tphase[buf], abort_flag, p.status, 4);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const int row_in_group = tl.mt * BM + quad * 32 + lane;
+      const bool row_ok = row_in_group < tl.rows;
+      const size_t out_row = (size_t)tl.group * p.C + row_in_group;
+      const int e = tl.group % p.LE;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN + c * 32), r);
+        const int col0 = tl.nt * BN + c * 32;
+        if (row_ok) {
+          alignas(16) T o[32];
+          alignas(16) T pre[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            float v = __uint_as_float(r[i]);
+            if (bias) v += Num<T>::to_f(bias[(size_t)e * p.N + col0 + i]);
+            pre[i] = Num<T>::from_f(v);
+            o[i] = Num<T>::from_f(activate(v, p.act));
+          }
+          uint4* dst = reinterpret_cast<uint4*>(D + out_row * p.N + col0);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) dst[q] = reinterpret_cast<const uint4*>(o)[q];
+          if (PRE) {
+            uint4* dp = reinterpret_cast<uint4*>(PRE + out_row * p.N + col0);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) dp[q] = reinterpret_cast<const uint4*>(pre)[q];
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
+      tphase[buf] ^= 1;
+      buf ^= 1;
+    }
+  }
+  // ---------------- teardown ----------------
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    // a wait gave up: let TMA copies that may still be in flight land before the CTA goes away
+    const unsigned long long t0 = now_ns();
+    while (now_ns() - t0 < 200000ull) {
+    }
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// 2-D row-major tensor [rows][cols] of 16-bit elements, box = box_rows x 64 columns, 128-byte swizzle.
+static int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows, int dtype) {
+  EncodeTiledFn fn = encode_fn();
+  LANCET_REQUIRE(fn, LANCET_ERR_CUDA, "grouped gemm: the driver does not provide cuTensorMapEncodeTiled");
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols * 2};
+  cuuint32_t box[2] = {(cuuint32_t)BK, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, dtype == LANCET_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                  const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  LANCET_REQUIRE(r == CUDA_SUCCESS, LANCET_ERR_CUDA, "grouped gemm: cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return LANCET_OK;
+}
+
+}  // namespace gemm
+}  // namespace lancet
+
+extern "C" {
+using namespace lancet;
+
+int lancet_grouped_gemm_nt(const void* A, const void* B, void* D, const void* bias, void* preact, int groups, int LE,
+                           int C, int N, int K, const int32_t* counts, int act, int dtype, int32_t* status,
+                           lancet_stream_t stream) {
+  using namespace lancet::gemm;
+  LANCET_REQUIRE(dtype == LANCET_BF16 || dtype == LANCET_F16, LANCET_ERR_UNSUPPORTED,
+                 "lancet_grouped_gemm_nt: inputs must be bfloat16 or float16 (dtype code %d)", dtype);
+  LANCET_REQUIRE(groups >= 1 && LE >= 1 && groups % LE == 0 && C >= 0 && N >= 1 && K >= 1, LANCET_ERR_INVALID,
+                 "lancet_grouped_gemm_nt: bad sizes groups=%d LE=%d C=%d N=%d K=%d", groups, LE, C, N, K);
+  LANCET_REQUIRE(N % BN == 0 && K % 8 == 0, LANCET_ERR_INVALID,
+                 "lancet_grouped_gemm_nt: N=%d must be a multiple of %d and K=%d a multiple of 8", N, BN, K);
+  LANCET_REQUIRE(act >= 0 && act <= 3, LANCET_ERR_INVALID, "lancet_grouped_gemm_nt: unknown activation %d", act);
+  if (C == 0) return LANCET_OK;
+  LANCET_REQUIRE(A && B && D && status, LANCET_ERR_NULL, "lancet_grouped_gemm_nt: null pointer argument");
+  LANCET_REQUIRE(aligned(A, 16) && aligned(B, 16) && aligned(D, 16) && aligned(bias, 2) && aligned(preact, 16),
+                 LANCET_ERR_INVALID, "lancet_grouped_gemm_nt: operands must be 16-byte aligned");
+  LANCET_REQUIRE((long long)groups * C < (1ll << 31) && (long long)LE * N < (1ll << 31), LANCET_ERR_INVALID,
+                 "lancet_grouped_gemm_nt: row counts exceed 2^31");
+  Params p;
+  p.groups = groups; p.LE = LE; p.C = C; p.N = N; p.K = K;
+  p.m_tiles = (C + BM - 1) / BM;
+  p.n_tiles = N / BN;
+  p.tiles_per_group = p.m_tiles * p.n_tiles;
+  const long long total = (long long)p.tiles_per_group * groups;
+  LANCET_REQUIRE(total < (1ll << 31), LANCET_ERR_INVALID, "lancet_grouped_gemm_nt: too many tiles");
+  p.total_tiles = (int)total;
+  p.counts = counts; p.bias = bias; p.D = D; p.preact = preact; p.act = act; p.status = status;
+  CUtensorMap tmA, tmB;
+  if (int rc = make_map(&tmA, A, (uint64_t)groups * C, (uint64_t)K, BM, dtype)) return rc;
+  if (int rc = make_map(&tmB, B, (uint64_t)LE * N, (uint64_t)K, BN, dtype)) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int grid = sm_count();
+  if (grid > p.total_tiles) grid = p.total_tiles;
+  static bool attr_set[2] = {false, false};
+  if (dtype == LANCET_BF16) {
+    if (!attr_set[0]) {
+      LANCET_CUDA(cudaFuncSetAttribute(grouped_gemm_nt_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+      attr_set[0] = true;
+    }
+    ProfScope prof("grouped_gemm_nt_kernel", st);
+    grouped_gemm_nt_kernel<__nv_bfloat16><<<grid, THREADS, SMEM_BYTES, st>>>(tmA, tmB, p);
+  } else {
+    if (!attr_set[1]) {
+      LANCET_CUDA(cudaFuncSetAttribute(grouped_gemm_nt_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+      attr_set[1] = true;
+    }
+    ProfScope prof("grouped_gemm_nt_kernel", st);
+    grouped_gemm_nt_kernel<__half><<<grid, THREADS, SMEM_BYTES, st>>>(tmA, tmB, p);
+  }
+  return launch_status("grouped_gemm_nt_kernel");
+}
+}

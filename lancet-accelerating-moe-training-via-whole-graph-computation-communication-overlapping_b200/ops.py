@@ -240,3 +240,36 @@ def lans(tensor_list, step, learning_rate=1e-3, beta1=0.9, beta2=0.999, eps=1e-6
                                   _stream(p[0])))
     state.ready = True
     return tensor_list
+
+
+ACT = {None: 0, "none": 0, "relu": 1, "gelu": 2, "gelu_tanh": 3}
+_gemm_status = {}
+
+
+def gemm_status(device):
+    """Device status word of the grouped GEMM (non-zero after a bounded wait gave up)."""
+    st = _gemm_status.get(device)
+    if st is None:
+        st = torch.zeros(1, dtype=torch.int32, device=device)
+        _gemm_status[device] = st
+    return st
+
+
+def grouped_gemm_nt(a, b, bias=None, counts=None, act=None, out=None, preact=None):
+    """Expert FFN GEMM: out[g] = act(a[g] @ b[g % LE].T + bias[g % LE]).
+
+    a [groups, C, K], b [LE, N, K] (the nn.Linear weight layout of Experts.forward,
+    models/benchmark/pytorch/utils.py:546-562 of the reference), bias [LE, N], counts int32 [groups]
+    (live rows per group; rows past them are neither computed nor written)."""
+    _require_cuda(a, b, bias, counts, out, preact)
+    groups, C, K = a.shape
+    LE, N, K2 = b.shape
+    if K2 != K or groups % LE:
+        raise ValueError("grouped_gemm_nt: shapes do not match")
+    if a.dtype != b.dtype or a.dtype not in (torch.bfloat16, torch.float16):
+        raise TypeError("grouped_gemm_nt: bfloat16 or float16 operands of one type")
+    out = torch.empty((groups, C, N), dtype=a.dtype, device=a.device) if out is None else out
+    st = gemm_status(a.device)
+    check(_capi.lib().lancet_grouped_gemm_nt(_ptr(a), _ptr(b), _ptr(out), _ptr(bias), _ptr(preact), groups, LE, C, N, K,
+                                             _ptr(counts), ACT[act], _dt(a), _ptr(st), _stream(a)))
+    return out

@@ -1,0 +1,81 @@
+"""Grouped expert GEMM (tcgen05) against a float32 torch reference of the same contraction.
+Tolerance for 16-bit operands with fp32 accumulation: rel 1e-2 of the row scale."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+import lancet_b200 as LB
+from lancet_b200 import _capi
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def reference(a, b, bias, act):
+    groups, C, K = a.shape
+    LE = b.shape[0]
+    out = torch.empty((groups, C, b.shape[1]), dtype=torch.float32, device=a.device)
+    for g in range(groups):
+        y = a[g].float() @ b[g % LE].float().t()
+        if bias is not None:
+            y = y + bias[g % LE].float()
+        if act == "relu":
+            y = torch.relu(y)
+        elif act == "gelu":
+            y = torch.nn.functional.gelu(y)
+        elif act == "gelu_tanh":
+            y = torch.nn.functional.gelu(y, approximate="tanh")
+        out[g] = y
+    return out
+
+
+def check_status():
+    st = LB.gemm_status(torch.device(DEV))
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    _capi.check(_capi.lib().lancet_p2p_status(ctypes.c_void_p(st.data_ptr()), stream))
+
+
+@pytest.mark.parametrize("groups,LE,C,N,K,dt,act,use_bias,ragged", [
+    (2, 2, 128, 256, 64, torch.bfloat16, None, False, False),       # one tile, one k block
+    (2, 1, 128, 256, 256, torch.bfloat16, None, False, False),      # pipeline wraps the 4 stages once
+    (4, 2, 256, 512, 1024, torch.bfloat16, "gelu", True, False),
+    (4, 2, 200, 256, 136, torch.float16, "relu", True, True),       # C and K not multiples of the tile
+    (16, 2, 640, 1024, 512, torch.bfloat16, "gelu_tanh", True, True),
+    (6, 2, 2560, 2048, 2048, torch.bfloat16, "gelu", True, True),   # many tiles per CTA, both accumulators
+])
+def test_grouped_gemm_matches_fp32_reference(groups, LE, C, N, K, dt, act, use_bias, ragged):
+    g = torch.Generator(device=DEV).manual_seed(groups * 1000 + C + N + K)
+    a = torch.randn((groups, C, K), device=DEV, generator=g).to(dt)
+    b = (torch.randn((LE, N, K), device=DEV, generator=g) * 0.02).to(dt)
+    bias = (torch.randn((LE, N), device=DEV, generator=g) * 0.1).to(dt) if use_bias else None
+    counts = None
+    if ragged:
+        counts = torch.randint(0, C + 1, (groups,), device=DEV, generator=g, dtype=torch.int32)
+        counts[0] = C
+        counts[-1] = 0
+    out = torch.full((groups, C, N), 7.0, dtype=dt, device=DEV)
+    pre = torch.full((groups, C, N), 7.0, dtype=dt, device=DEV)
+    LB.grouped_gemm_nt(a, b, bias=bias, counts=counts, act=act, out=out, preact=pre)
+    torch.cuda.synchronize()
+    check_status()
+    want = reference(a, b, bias, act)
+    want_pre = reference(a, b, bias, None)
+    scale = float(want_pre.abs().max()) + 1e-6
+    for gi in range(groups):
+        n = C if counts is None else int(counts[gi])
+        got = out[gi, :n].float()
+        assert torch.allclose(got, want[gi, :n], rtol=1e-2, atol=1e-2 * scale), (gi, (got - want[gi, :n]).abs().max())
+        assert torch.allclose(pre[gi, :n].float(), want_pre[gi, :n], rtol=1e-2, atol=1e-2 * scale)
+        assert (out[gi, n:].float() == 7.0).all(), "rows past the live count must not be written"
+
+
+def test_gemm_rejects_bad_arguments():
+    a = torch.zeros((2, 128, 64), dtype=torch.bfloat16, device=DEV)
+    b = torch.zeros((2, 100, 64), dtype=torch.bfloat16, device=DEV)    # N not a multiple of 256
+    with pytest.raises(LB.LancetError) as ei:
+        LB.grouped_gemm_nt(a, b)
+    assert ei.value.code == 1
+    with pytest.raises(TypeError):
+        LB.grouped_gemm_nt(a.float(), b.float())
