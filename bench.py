@@ -375,6 +375,84 @@ def run_lans(args):
     emit(line)
 
 
+def run_ffn(args):
+    """Expert FFN forward (config 'expert FFN grouped GEMM'): per GPU 2 local experts, rows from 8 source
+    ranks x C=2560, M=2048, H=8192, bf16 with fp32 accumulation: GEMM1 + bias + GELU, GEMM2 + bias."""
+    import lancet_b200 as LB
+    from lancet_b200 import _capi
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    L = _capi.lib()
+    G, LE, C, M, H = 8, 2, 2560, 2048, 8192
+    g = torch.Generator(device=dev).manual_seed(0)
+    x = torch.randn((G * LE, C, M), device=dev, generator=g).bfloat16()
+    w1 = (torch.randn((LE, H, M), device=dev, generator=g) * 0.02).bfloat16()
+    w2 = (torch.randn((LE, M, H), device=dev, generator=g) * 0.02).bfloat16()
+    b1 = torch.zeros((LE, H), device=dev).bfloat16()
+    b2 = torch.zeros((LE, M), device=dev).bfloat16()
+    h = torch.empty((G * LE, C, H), device=dev, dtype=torch.bfloat16)
+    y = torch.empty((G * LE, C, M), device=dev, dtype=torch.bfloat16)
+
+    def step():
+        LB.grouped_gemm_nt(x, w1, bias=b1, act="gelu", out=h)
+        LB.grouped_gemm_nt(h, w2, bias=b2, out=y)
+
+    sampler = ClockSampler(dev.index)
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    L.lancet_profile_begin(b"grouped_gemm_nt_kernel")
+    l0 = L.lancet_launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(args.steps):
+        step()
+    ev1.record()
+    torch.cuda.synchronize()
+    ms = ev0.elapsed_time(ev1) / args.steps
+    launches = L.lancet_launch_count() - l0
+    k_ms, k_n = ctypes.c_double(0), ctypes.c_longlong(0)
+    _capi.check(L.lancet_profile_end(ctypes.byref(k_ms), ctypes.byref(k_n)))
+    st = LB.gemm_status(dev)
+    _capi.check(L.lancet_p2p_status(ctypes.c_void_p(st.data_ptr()), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    # same-box bar: the library GEMM the reference calls (cuBLAS through torch.matmul), same shapes
+    xs = x.view(G, LE, C, M)
+    def lib_step():
+        for e in range(LE):
+            a = xs[:, e].reshape(G * C, M)
+            hh = torch.nn.functional.gelu(torch.addmm(b1[e], a, w1[e].t()))
+            torch.addmm(b2[e], hh, w2[e].t())
+    for _ in range(3):
+        lib_step()
+    torch.cuda.synchronize()
+    ev0.record()
+    lib_steps = max(3, min(args.steps, 20))
+    for _ in range(lib_steps):
+        lib_step()
+    ev1.record()
+    torch.cuda.synchronize()
+    lib_ms = ev0.elapsed_time(ev1) / lib_steps
+    clocks = ClockSampler.summarise(sampler.stop())
+    peaks, peak_kind = load_peaks()
+    flops = 2.0 * (G * LE * C) * M * H * 2
+    sustained = float(peaks.get("bf16_tflops_sustained", peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"])))
+    avg_s = k_ms.value / max(1, k_n.value) / 1e3
+    ach = flops / 2 / avg_s / 1e12
+    tokens = G * LE * C
+    emit({
+        "metric": "expert_ffn_rows_per_s", "value": tokens / (ms / 1e3), "unit": "rows/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "expert_ffn_forward: 16 groups x 2560 rows, M=2048, H=8192, 2 local experts, bias+GELU",
+                   "l2": "1.2 GB touched per step exceeds the 126 MB L2"},
+        "gpu_launches": int(launches), "clocks": clocks, "tflops": flops / (ms / 1e3) / 1e12,
+        "library_gemm": {"ms_per_step": lib_ms, "tflops": flops / (lib_ms / 1e3) / 1e12, "what": "torch.addmm + gelu (cuBLAS)"},
+        "roofline": {"bound": "tensor", "kernel": "grouped_gemm_nt_kernel", "achieved": ach, "peak": sustained,
+                     "unit": "TFLOP/s", "frac": ach / sustained, "peak_kind": peak_kind + " (sustained cuBLAS bf16)",
+                     "traffic": None, "flops_per_launch": flops / 2, "avg_launch_us": avg_s * 1e6},
+    })
+
+
 def main():
     # libraries (NCCL, torchrun) may write to stdout; keep it clean for the one JSON line
     saved_stdout = os.dup(1)
@@ -401,7 +479,7 @@ def _main():
     ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="moe", choices=["moe", "lans"])
+    ap.add_argument("--workload", default="moe", choices=["moe", "lans", "ffn"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--lans-layers", type=int, default=24, help="transformer layers in the LANS tensor list (24 = 196 tensors)")
     args = ap.parse_args()
@@ -412,6 +490,8 @@ def _main():
         raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
     if args.workload == "lans":
         run_lans(args)
+    elif args.workload == "ffn":
+        run_ffn(args)
     else:
         run_moe(args)
 
