@@ -415,6 +415,30 @@ def run_ffn(args):
     _capi.check(L.lancet_profile_end(ctypes.byref(k_ms), ctypes.byref(k_n)))
     st = LB.gemm_status(dev)
     _capi.check(L.lancet_p2p_status(ctypes.c_void_p(st.data_ptr()), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    # backward GEMMs of the same layer: dH = (dY W2) * gelu'(H_pre), dW2 = dY^T H, dX = dH W1, dW1 = dH^T X
+    hpre = torch.empty_like(h)
+    LB.grouped_gemm_nt(x, w1, bias=b1, act="gelu", out=h, preact=hpre)
+    dy = torch.randn((G * LE, C, M), device=dev, generator=g).bfloat16()
+    dh, dx = torch.empty_like(h), torch.empty_like(x)
+    dw1, dw2 = torch.empty_like(w1), torch.empty_like(w2)
+
+    def bwd_step():
+        LB.grouped_gemm_nn(dy, w2, act="gelu", preact=hpre, out=dh)       # w2 is [LE, M, H]: contraction over M
+        LB.grouped_gemm_tn(dy, h, LE, out=dw2)                            # [LE, M, H]
+        LB.grouped_gemm_nn(dh, w1, out=dx)                                # w1 is [LE, H, M]: contraction over H
+        LB.grouped_gemm_tn(dh, x, LE, out=dw1)                            # [LE, H, M]
+
+    for _ in range(3):
+        bwd_step()
+    torch.cuda.synchronize()
+    bsteps = max(3, min(args.steps, 20))
+    ev0.record()
+    for _ in range(bsteps):
+        bwd_step()
+    ev1.record()
+    torch.cuda.synchronize()
+    bwd_ms = ev0.elapsed_time(ev1) / bsteps
+    _capi.check(L.lancet_p2p_status(ctypes.c_void_p(st.data_ptr()), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
     # same-box bar: the library GEMM the reference calls (cuBLAS through torch.matmul), same shapes
     xs = x.view(G, LE, C, M)
     def lib_step():
@@ -446,6 +470,8 @@ def run_ffn(args):
         "config": {"workload": "expert_ffn_forward: 16 groups x 2560 rows, M=2048, H=8192, 2 local experts, bias+GELU",
                    "l2": "1.2 GB touched per step exceeds the 126 MB L2"},
         "gpu_launches": int(launches), "clocks": clocks, "tflops": flops / (ms / 1e3) / 1e12,
+        "backward": {"ms_per_step": bwd_ms, "tflops": 2.0 * flops / (bwd_ms / 1e3) / 1e12,
+                     "what": "dH (NN, fused gelu'), dW2 (TN), dX (NN), dW1 (TN)"},
         "library_gemm": {"ms_per_step": lib_ms, "tflops": flops / (lib_ms / 1e3) / 1e12, "what": "torch.addmm + gelu (cuBLAS)"},
         "roofline": {"bound": "tensor", "kernel": "grouped_gemm_nt_kernel", "achieved": ach, "peak": sustained,
                      "unit": "TFLOP/s", "frac": ach / sustained, "peak_kind": peak_kind + " (sustained cuBLAS bf16)",

@@ -240,12 +240,28 @@ int lancet_all_to_allv_p2p(const void* send, void* const* peer_recv, const uint6
  * g in [0, groups): A [groups][C][K], B [LE][N][K] (nn.Linear layout), D [groups][C][N], all bf16 or
  * fp16 with fp32 accumulation; bias [LE][N] and preact (copy of the pre-activation, [groups][C][N])
  * nullable.  counts (nullable, device int32 [groups]): only the first counts[g] rows of group g are
- * computed and written.  act: 0 none, 1 relu, 2 gelu (erf), 3 gelu (tanh).  N % 256 == 0, K % 8 == 0.
+ * computed; rows from counts[g] up to the end of the last 128-row tile that holds a live row are
+ * written as zeros, later rows are not touched.  act: 0 none, 1 relu, 2 gelu (erf), 3 gelu (tanh).
+ * N % 256 == 0, K % 8 == 0.
  * status: device int32, zero when healthy; a bounded wait that gave up stores its site there
  * (read it with lancet_p2p_status). */
 int lancet_grouped_gemm_nt(const void* A, const void* B, void* D, const void* bias, void* preact, int groups,
                            int LE, int C, int N, int K, const int32_t* counts, int act, int dtype,
                            int32_t* status, lancet_stream_t stream);
+/* Data gradient of the layer above (the reference's dX = matmul_nt(dy, w), src/op/grad/gemm.cc:31-36,
+ * with w stored [N_out][K_in] so that the contraction runs over its rows):
+ * D[g] = (A[g] * B[g % LE]) .* act'(preact[g]);  A [groups][C][K], B [LE][K][N] (N contiguous),
+ * D and preact [groups][C][N]; preact is required when act != 0.  K % 64 == 0, N % 256 == 0. */
+int lancet_grouped_gemm_nn(const void* A, const void* B, void* D, const void* preact, int groups, int LE, int C,
+                           int N, int K, const int32_t* counts, int act, int dtype, int32_t* status,
+                           lancet_stream_t stream);
+/* Weight gradient (the reference's dW = matmul_tn(a, dy), src/op/grad/gemm.cc:31-36), summed over the
+ * source ranks of an expert: D[e] = sum over groups g with g % LE == e of A[g][:counts[g]]^T * B[g][:counts[g]];
+ * A [groups][C][Mout], B [groups][C][N], D [LE][Mout][N].  Rows from counts[g] to the next multiple
+ * of 64 must be zero in A or B and finite in both (the forms above leave their outputs that way;
+ * dispatch zero-fills the expert input).  Mout % 128 == 0, N % 256 == 0. */
+int lancet_grouped_gemm_tn(const void* A, const void* B, void* D, int groups, int LE, int C, int Mout, int N,
+                           const int32_t* counts, int dtype, int32_t* status, lancet_stream_t stream);
 
 /* ---- LANS optimizer ---------------------------------------------------------------------------
  * Replaces multi_tensor_lans_cuda (kernel_util.cuh:26-34; multi_tensor_lans.cu:401-450) and the

@@ -37,14 +37,23 @@ constexpr int TMEM_COLS = 512;               // two accumulators of BN fp32 colu
 constexpr int BAND = 16;                     // m-tiles per band (L2 reuse of A against a sweep of B)
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
 
+// MODE_ROWS:   D[g] (C x N) = epilogue(A[g] (C x K) * op(B[e])), tiles over (group, m-tile, n-tile), reduction over K.
+//              B is [LE][N][K] (K-major, "NT") or [LE][K][N] (N contiguous, "NN", B_MN).
+// MODE_REDUCE: D[e] (Mout x N) = sum over groups g of expert e and their live rows r of A[g][r][:]^T * B[g][r][:]
+//              ("TN": weight gradients), tiles over (expert, m-tile, n-tile), reduction over rows.
+constexpr int MODE_ROWS = 0, MODE_REDUCE = 1;
+constexpr int EPI_ACT = 0, EPI_DACT = 1;
+
 struct Params {
   int groups, LE, C, N, K;
+  int Mout;               // MODE_REDUCE: output rows per expert
   int m_tiles, n_tiles, tiles_per_group, total_tiles;
   const int32_t* counts;  // [groups] live rows, or null
   const void* bias;       // [LE][N] or null
   void* D;
-  void* preact;           // optional copy of the pre-activation values
+  void* preact;           // EPI_ACT: optional copy of the pre-activation; EPI_DACT: the saved pre-activation (input)
   int act;                // 0 none, 1 relu, 2 gelu (erf), 3 gelu (tanh)
+  int epi;
   int* status;
 };
 
@@ -129,10 +138,36 @@ __device__ __forceinline__ uint64_t smem_desc_k_sw128(uint32_t addr) {
   return d;
 }
 
+// Descriptor of an MN-major tile stored as TMA boxes of 64 reduction rows x 64 elements (128 bytes, swizzled):
+// inside a box 8 reduction rows form a 1024-byte atom (stride byte offset), the next 64 elements along M/N
+// live in the next box, BOX_BYTES further (leading byte offset).
+constexpr int BOX_BYTES = 64 * 128;
+__device__ __forceinline__ uint64_t smem_desc_mn_sw128(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr >> 4) & 0x3FFF);
+  d |= (uint64_t)(BOX_BYTES >> 4) << 16;   // leading byte offset: next block of 64 along M/N
+  d |= (uint64_t)(1024 >> 4) << 32;        // stride byte offset: next group of 8 reduction rows
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
 template <typename T>
-__device__ __forceinline__ uint32_t instr_desc() {
+__device__ __forceinline__ uint32_t instr_desc(bool a_mn, bool b_mn) {
   const uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;  // 0 = f16, 1 = bf16
-  return (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);  // D = f32, K-major A and B
+  return (1u << 4) | (fmt << 7) | (fmt << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) |
+         ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);  // D = f32
+}
+
+__device__ __forceinline__ float dactivate(float x, int act) {
+  if (act == 1) return x > 0.f ? 1.f : 0.f;
+  if (act == 2) return 0.5f * (1.0f + erff(x * 0.70710678118654752f)) + x * 0.3989422804014327f * __expf(-0.5f * x * x);
+  if (act == 3) {
+    const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+    const float t = tanhf(u);
+    return 0.5f * (1.0f + t) + 0.5f * x * (1.0f - t * t) * 0.7978845608028654f * (1.0f + 3.0f * 0.044715f * x * x);
+  }
+  return 1.f;
 }
 
 struct Tile {
@@ -140,8 +175,29 @@ struct Tile {
   bool live;
 };
 
+// Number of 64-row reduction blocks of group g (MODE_REDUCE).
+__device__ __forceinline__ int group_row_blocks(const Params& p, int g) {
+  int rows = p.C;
+  if (p.counts) {
+    rows = p.counts[g];
+    rows = rows < 0 ? 0 : (rows > p.C ? p.C : rows);
+  }
+  return (rows + BK - 1) / BK;
+}
+
+template <int MODE>
 __device__ __forceinline__ Tile decode_tile(const Params& p, int t) {
   Tile tl;
+  if (MODE == MODE_REDUCE) {
+    // tiles_per_group = m_tiles * n_tiles per expert; `group` holds the expert index
+    tl.group = t / p.tiles_per_group;
+    const int r = t - tl.group * p.tiles_per_group;
+    tl.nt = r / p.m_tiles;
+    tl.mt = r - tl.nt * p.m_tiles;
+    tl.rows = p.Mout;
+    tl.live = true;
+    return tl;
+  }
   tl.group = t / p.tiles_per_group;
   int r = t - tl.group * p.tiles_per_group;
   const int band_tiles = BAND * p.n_tiles;
@@ -167,9 +223,18 @@ __device__ __forceinline__ float activate(float v, int act) {
   return v;
 }
 
-template <typename T>
+template <int MODE>
+__device__ __forceinline__ int tile_k_blocks(const Params& p, const Tile& tl) {
+  if (MODE == MODE_ROWS) return (p.K + BK - 1) / BK;
+  int n = 0;
+  for (int g = tl.group; g < p.groups; g += p.LE) n += group_row_blocks(p, g);
+  return n;
+}
+
+template <typename T, int MODE, bool B_MN, int EPI>
 __global__ void __launch_bounds__(THREADS, 1)
-grouped_gemm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, Params p) {
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, Params p) {
+  constexpr bool A_MN = (MODE == MODE_REDUCE);
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   unsigned char* sA = smem;
@@ -203,7 +268,6 @@ grouped_gemm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const int k_blocks = (p.K + BK - 1) / BK;
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -212,31 +276,62 @@ grouped_gemm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
       uint32_t phase = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
-        const Tile tl = decode_tile(p, t);
+        const Tile tl = decode_tile<MODE>(p, t);
         if (!tl.live) continue;
-        const int a_row = tl.group * p.C + tl.mt * BM;
-        const int b_row = (tl.group % p.LE) * p.N + tl.nt * BN;
-        for (int kb = 0; kb < k_blocks; ++kb) {
-          if (!(ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, p.status, 1))) break;
-          mbar_expect_tx(bar_full + 8 * stage, A_STAGE_BYTES + B_STAGE_BYTES);
-          tma_load_2d(smem_u32(sA + stage * A_STAGE_BYTES), &tmA, bar_full + 8 * stage, kb * BK, a_row);
-          tma_load_2d(smem_u32(sB + stage * B_STAGE_BYTES), &tmB, bar_full + 8 * stage, kb * BK, b_row);
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        if (MODE == MODE_ROWS) {
+          const int e = tl.group % p.LE;
+          const int a_row = tl.group * p.C + tl.mt * BM;
+          const int k_blocks = (p.K + BK - 1) / BK;
+          for (int kb = 0; kb < k_blocks; ++kb) {
+            if (!(ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, p.status, 1))) break;
+            const uint32_t full = bar_full + 8 * stage;
+            mbar_expect_tx(full, A_STAGE_BYTES + B_STAGE_BYTES);
+            tma_load_2d(smem_u32(sA + stage * A_STAGE_BYTES), &tmA, full, kb * BK, a_row);
+            const uint32_t b_dst = smem_u32(sB + stage * B_STAGE_BYTES);
+            if (!B_MN) {
+              tma_load_2d(b_dst, &tmB, full, kb * BK, e * p.N + tl.nt * BN);
+            } else {
+#pragma unroll
+              for (int j = 0; j < BN / 64; ++j)
+                tma_load_2d(b_dst + j * BOX_BYTES, &tmB, full, tl.nt * BN + j * 64, e * p.K + kb * BK);
+            }
+            if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          }
+        } else {
+          for (int g = tl.group; g < p.groups && ok; g += p.LE) {
+            const int nb = group_row_blocks(p, g);
+            for (int rb = 0; rb < nb; ++rb) {
+              if (!(ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, p.status, 1))) break;
+              const uint32_t full = bar_full + 8 * stage;
+              mbar_expect_tx(full, A_STAGE_BYTES + B_STAGE_BYTES);
+              const int row = g * p.C + rb * BK;
+              const uint32_t a_dst = smem_u32(sA + stage * A_STAGE_BYTES);
+              const uint32_t b_dst = smem_u32(sB + stage * B_STAGE_BYTES);
+#pragma unroll
+              for (int j = 0; j < BM / 64; ++j) tma_load_2d(a_dst + j * BOX_BYTES, &tmA, full, tl.mt * BM + j * 64, row);
+#pragma unroll
+              for (int j = 0; j < BN / 64; ++j) tma_load_2d(b_dst + j * BOX_BYTES, &tmB, full, tl.nt * BN + j * 64, row);
+              if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            }
+          }
         }
       }
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
-      const uint32_t idesc = instr_desc<T>();
+      const uint32_t idesc = instr_desc<T>(A_MN, B_MN);
       int stage = 0;
       uint32_t phase = 0;
       int buf = 0;
       uint32_t tphase[2] = {0, 0};
       bool ok = true;
       for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
-        const Tile tl = decode_tile(p, t);
+        const Tile tl = decode_tile<MODE>(p, t);
         if (!tl.live) continue;
+        // an empty reduction (weight-gradient form, all counts zero) still hands the accumulator over:
+        // the epilogue masks its contents to zero
+        const int k_blocks = tile_k_blocks<MODE>(p, tl);
         if (!(ok = mbar_wait(bar_tempty + 8 * buf, tphase[buf] ^ 1, abort_flag, p.status, 2))) break;
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
@@ -247,8 +342,9 @@ grouped_gemm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
           const uint32_t b_addr = smem_u32(sB + stage * B_STAGE_BYTES);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint64_t adesc = smem_desc_k_sw128(a_addr + k * UMMA_K * 2);
-            const uint64_t bdesc = smem_desc_k_sw128(b_addr + k * UMMA_K * 2);
+            // K-major: 16 elements further inside the 128-byte row; MN-major: 16 reduction rows = two 1024-byte atoms
+            const uint64_t adesc = A_MN ? smem_desc_mn_sw128(a_addr + k * 2048) : smem_desc_k_sw128(a_addr + k * UMMA_K * 2);
+            const uint64_t bdesc = B_MN ? smem_desc_mn_sw128(b_addr + k * 2048) : smem_desc_k_sw128(b_addr + k * UMMA_K * 2);
             umma_f16(tmem_d, adesc, bdesc, idesc, (kb | k) ? 1u : 0u);
           }
           umma_commit(bar_empty + 8 * stage);  // frees the stage when these MMAs have read it
@@ -270,39 +366,68 @@ grouped_gemm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     T* PRE = static_cast<T*>(p.preact);
     const T* bias = static_cast<const T*>(p.bias);
     for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
-      const Tile tl = decode_tile(p, t);
+      const Tile tl = decode_tile<MODE>(p, t);
       if (!tl.live) continue;
+      // row-parallel forms always reduce over K >= 1; only the weight-gradient form can meet an empty
+      // reduction, whose accumulator holds stale values: they are masked to zero bit-wise (no branch in
+      // the hot loop: extra control flow here made the compiler serialise the epilogue)
+      const uint32_t acc_mask = (MODE == MODE_ROWS || tile_k_blocks<MODE>(p, tl) > 0) ? 0xffffffffu : 0u;
       ok = mbar_wait(bar_tfull + 8 * buf, tphase[buf], abort_flag, p.status, 4);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const int row_in_group = tl.mt * BM + quad * 32 + lane;
-      const bool row_ok = row_in_group < tl.rows;
-      const size_t out_row = (size_t)tl.group * p.C + row_in_group;
-      const int e = tl.group % p.LE;
+      const int row_in_tile = quad * 32 + lane;
+      int e;
+      size_t out_row;
+      bool row_live;
+      if (MODE == MODE_ROWS) {
+        const int row_in_group = tl.mt * BM + row_in_tile;
+        row_live = row_in_group < tl.rows;
+        out_row = (size_t)tl.group * p.C + row_in_group;
+        e = tl.group % p.LE;
+      } else {
+        const int r = tl.mt * BM + row_in_tile;
+        row_live = r < p.Mout;
+        out_row = (size_t)tl.group * p.Mout + r;
+        e = tl.group;
+      }
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
         tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN + c * 32), r);
-        const int col0 = tl.nt * BN + c * 32;
-        if (row_ok) {
-          alignas(16) T o[32];
-          alignas(16) T pre[32];
+        if (MODE == MODE_REDUCE) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            float v = __uint_as_float(r[i]);
-            if (bias) v += Num<T>::to_f(bias[(size_t)e * p.N + col0 + i]);
-            pre[i] = Num<T>::from_f(v);
-            o[i] = Num<T>::from_f(activate(v, p.act));
+          for (int i = 0; i < 32; ++i) r[i] &= acc_mask;
+        }
+        const int col0 = tl.nt * BN + c * 32;
+        if (row_live) {
+          alignas(16) T o[32];
+          if (EPI == EPI_DACT) {
+            alignas(16) T pre[32];
+            const uint4* pp = reinterpret_cast<const uint4*>(PRE + out_row * p.N + col0);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) reinterpret_cast<uint4*>(pre)[q] = pp[q];
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              o[i] = Num<T>::from_f(__uint_as_float(r[i]) * dactivate(Num<T>::to_f(pre[i]), p.act));
+          } else {
+            alignas(16) T pre[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              float v = __uint_as_float(r[i]);
+              if (bias) v += Num<T>::to_f(bias[(size_t)e * p.N + col0 + i]);
+              pre[i] = Num<T>::from_f(v);
+              o[i] = Num<T>::from_f(activate(v, p.act));
+            }
+            if (PRE) {
+              uint4* dp = reinterpret_cast<uint4*>(PRE + out_row * p.N + col0);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) dp[q] = reinterpret_cast<const uint4*>(pre)[q];
+            }
           }
           uint4* dst = reinterpret_cast<uint4*>(D + out_row * p.N + col0);
 #pragma unroll
           for (int q = 0; q < 4; ++q) dst[q] = reinterpret_cast<const uint4*>(o)[q];
-          if (PRE) {
-            uint4* dp = reinterpret_cast<uint4*>(PRE + out_row * p.N + col0);
-#pragma unroll
-            for (int q = 0; q < 4; ++q) dp[q] = reinterpret_cast<const uint4*>(pre)[q];
-          }
         }
       }
       tc_fence_before();
@@ -326,6 +451,24 @@ grouped_gemm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
   }
+}
+
+// Rows [counts[g], end of the last 128-row tile holding a live row) of every group are set to zero, so that
+// a consumer that reduces over rows in blocks of 64 (the weight-gradient form) meets zeros, not stale data.
+// A kernel of its own: merged into the epilogue above it slowed the live path down 2.5x.
+template <typename T>
+__global__ void __launch_bounds__(256)
+zero_dead_rows_kernel(T* __restrict__ D, const int32_t* __restrict__ counts, int C, int N) {
+  const int g = blockIdx.y;
+  int rows = counts[g];
+  rows = rows < 0 ? 0 : (rows > C ? C : rows);
+  int end = (rows + BM - 1) / BM * BM;
+  if (end > C) end = C;
+  const size_t vec_per_row = (size_t)N * sizeof(T) / 16;
+  const size_t total = (size_t)(end - rows) * vec_per_row;
+  uint4* base = reinterpret_cast<uint4*>(D + ((size_t)g * C + rows) * N);
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
+    base[i] = make_uint4(0, 0, 0, 0);
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -359,6 +502,59 @@ static int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t 
   return LANCET_OK;
 }
 
+template <typename T, int MODE, bool B_MN, int EPI>
+static int launch_t(const CUtensorMap& tmA, const CUtensorMap& tmB, const Params& p, const char* name, cudaStream_t st) {
+  static bool attr_set = false;
+  if (!attr_set) {
+    LANCET_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel<T, MODE, B_MN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    attr_set = true;
+  }
+  int grid = sm_count();
+  if (grid > p.total_tiles) grid = p.total_tiles;
+  {
+    ProfScope prof(name, st);
+    grouped_gemm_kernel<T, MODE, B_MN, EPI><<<grid, THREADS, SMEM_BYTES, st>>>(tmA, tmB, p);
+  }
+  return launch_status(name);
+}
+
+template <int MODE, bool B_MN, int EPI>
+static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const Params& p, int dtype, const char* name, cudaStream_t st) {
+  int rc = dtype == LANCET_BF16 ? launch_t<__nv_bfloat16, MODE, B_MN, EPI>(tmA, tmB, p, name, st)
+                                : launch_t<__half, MODE, B_MN, EPI>(tmA, tmB, p, name, st);
+  if (rc != LANCET_OK || MODE != MODE_ROWS || !p.counts) return rc;
+  // both 16-bit types have the same size: one instantiation serves them
+  zero_dead_rows_kernel<__half><<<dim3(8, p.groups), 256, 0, st>>>(static_cast<__half*>(p.D), p.counts, p.C, p.N);
+  return launch_status("zero_dead_rows_kernel");
+}
+
+// Shared argument checks and tile bookkeeping of the row-parallel forms (NT, NN).
+static int rows_common(const char* fn, const void* A, const void* B, void* D, int groups, int LE, int C, int N, int K,
+                       int act, int dtype, int32_t* status, Params* p) {
+  LANCET_REQUIRE(dtype == LANCET_BF16 || dtype == LANCET_F16, LANCET_ERR_UNSUPPORTED,
+                 "%s: inputs must be bfloat16 or float16 (dtype code %d)", fn, dtype);
+  LANCET_REQUIRE(groups >= 1 && LE >= 1 && groups % LE == 0 && C >= 0 && N >= 1 && K >= 1, LANCET_ERR_INVALID,
+                 "%s: bad sizes groups=%d LE=%d C=%d N=%d K=%d", fn, groups, LE, C, N, K);
+  LANCET_REQUIRE(N % BN == 0 && K % 8 == 0, LANCET_ERR_INVALID, "%s: N=%d must be a multiple of %d and K=%d a multiple of 8",
+                 fn, N, BN, K);
+  LANCET_REQUIRE(act >= 0 && act <= 3, LANCET_ERR_INVALID, "%s: unknown activation %d", fn, act);
+  if (C == 0) return LANCET_OK;
+  LANCET_REQUIRE(A && B && D && status, LANCET_ERR_NULL, "%s: null pointer argument", fn);
+  LANCET_REQUIRE(aligned(A, 16) && aligned(B, 16) && aligned(D, 16), LANCET_ERR_INVALID, "%s: operands must be 16-byte aligned", fn);
+  LANCET_REQUIRE((long long)groups * C < (1ll << 31) && (long long)LE * N < (1ll << 31) && (long long)LE * K < (1ll << 31),
+                 LANCET_ERR_INVALID, "%s: row counts exceed 2^31", fn);
+  p->groups = groups; p->LE = LE; p->C = C; p->N = N; p->K = K; p->Mout = 0;
+  p->m_tiles = (C + BM - 1) / BM;
+  p->n_tiles = N / BN;
+  p->tiles_per_group = p->m_tiles * p->n_tiles;
+  const long long total = (long long)p->tiles_per_group * groups;
+  LANCET_REQUIRE(total < (1ll << 31), LANCET_ERR_INVALID, "%s: too many tiles", fn);
+  p->total_tiles = (int)total;
+  p->status = status;
+  p->act = act;
+  return LANCET_OK;
+}
+
 }  // namespace gemm
 }  // namespace lancet
 
@@ -369,50 +565,61 @@ int lancet_grouped_gemm_nt(const void* A, const void* B, void* D, const void* bi
                            int C, int N, int K, const int32_t* counts, int act, int dtype, int32_t* status,
                            lancet_stream_t stream) {
   using namespace lancet::gemm;
-  LANCET_REQUIRE(dtype == LANCET_BF16 || dtype == LANCET_F16, LANCET_ERR_UNSUPPORTED,
-                 "lancet_grouped_gemm_nt: inputs must be bfloat16 or float16 (dtype code %d)", dtype);
-  LANCET_REQUIRE(groups >= 1 && LE >= 1 && groups % LE == 0 && C >= 0 && N >= 1 && K >= 1, LANCET_ERR_INVALID,
-                 "lancet_grouped_gemm_nt: bad sizes groups=%d LE=%d C=%d N=%d K=%d", groups, LE, C, N, K);
-  LANCET_REQUIRE(N % BN == 0 && K % 8 == 0, LANCET_ERR_INVALID,
-                 "lancet_grouped_gemm_nt: N=%d must be a multiple of %d and K=%d a multiple of 8", N, BN, K);
-  LANCET_REQUIRE(act >= 0 && act <= 3, LANCET_ERR_INVALID, "lancet_grouped_gemm_nt: unknown activation %d", act);
-  if (C == 0) return LANCET_OK;
-  LANCET_REQUIRE(A && B && D && status, LANCET_ERR_NULL, "lancet_grouped_gemm_nt: null pointer argument");
-  LANCET_REQUIRE(aligned(A, 16) && aligned(B, 16) && aligned(D, 16) && aligned(bias, 2) && aligned(preact, 16),
-                 LANCET_ERR_INVALID, "lancet_grouped_gemm_nt: operands must be 16-byte aligned");
-  LANCET_REQUIRE((long long)groups * C < (1ll << 31) && (long long)LE * N < (1ll << 31), LANCET_ERR_INVALID,
-                 "lancet_grouped_gemm_nt: row counts exceed 2^31");
   Params p;
-  p.groups = groups; p.LE = LE; p.C = C; p.N = N; p.K = K;
-  p.m_tiles = (C + BM - 1) / BM;
-  p.n_tiles = N / BN;
-  p.tiles_per_group = p.m_tiles * p.n_tiles;
-  const long long total = (long long)p.tiles_per_group * groups;
-  LANCET_REQUIRE(total < (1ll << 31), LANCET_ERR_INVALID, "lancet_grouped_gemm_nt: too many tiles");
-  p.total_tiles = (int)total;
-  p.counts = counts; p.bias = bias; p.D = D; p.preact = preact; p.act = act; p.status = status;
+  if (int rc = rows_common("lancet_grouped_gemm_nt", A, B, D, groups, LE, C, N, K, act, dtype, status, &p)) return rc;
+  if (C == 0) return LANCET_OK;
+  LANCET_REQUIRE(aligned(bias, 2) && aligned(preact, 16), LANCET_ERR_INVALID, "lancet_grouped_gemm_nt: bias/preact alignment");
+  p.counts = counts; p.bias = bias; p.D = D; p.preact = preact; p.epi = EPI_ACT;
   CUtensorMap tmA, tmB;
   if (int rc = make_map(&tmA, A, (uint64_t)groups * C, (uint64_t)K, BM, dtype)) return rc;
   if (int rc = make_map(&tmB, B, (uint64_t)LE * N, (uint64_t)K, BN, dtype)) return rc;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  int grid = sm_count();
-  if (grid > p.total_tiles) grid = p.total_tiles;
-  static bool attr_set[2] = {false, false};
-  if (dtype == LANCET_BF16) {
-    if (!attr_set[0]) {
-      LANCET_CUDA(cudaFuncSetAttribute(grouped_gemm_nt_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-      attr_set[0] = true;
-    }
-    ProfScope prof("grouped_gemm_nt_kernel", st);
-    grouped_gemm_nt_kernel<__nv_bfloat16><<<grid, THREADS, SMEM_BYTES, st>>>(tmA, tmB, p);
-  } else {
-    if (!attr_set[1]) {
-      LANCET_CUDA(cudaFuncSetAttribute(grouped_gemm_nt_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-      attr_set[1] = true;
-    }
-    ProfScope prof("grouped_gemm_nt_kernel", st);
-    grouped_gemm_nt_kernel<__half><<<grid, THREADS, SMEM_BYTES, st>>>(tmA, tmB, p);
-  }
-  return launch_status("grouped_gemm_nt_kernel");
+  return launch<MODE_ROWS, false, EPI_ACT>(tmA, tmB, p, dtype, "grouped_gemm_nt_kernel", static_cast<cudaStream_t>(stream));
+}
+
+int lancet_grouped_gemm_nn(const void* A, const void* B, void* D, const void* preact, int groups, int LE, int C, int N,
+                           int K, const int32_t* counts, int act, int dtype, int32_t* status, lancet_stream_t stream) {
+  using namespace lancet::gemm;
+  Params p;
+  if (int rc = rows_common("lancet_grouped_gemm_nn", A, B, D, groups, LE, C, N, K, act, dtype, status, &p)) return rc;
+  if (C == 0) return LANCET_OK;
+  LANCET_REQUIRE(K % BK == 0, LANCET_ERR_INVALID, "lancet_grouped_gemm_nn: K=%d must be a multiple of %d", K, BK);
+  LANCET_REQUIRE(act == 0 || preact, LANCET_ERR_NULL, "lancet_grouped_gemm_nn: an activation derivative needs the saved pre-activation");
+  LANCET_REQUIRE(aligned(preact, 16), LANCET_ERR_INVALID, "lancet_grouped_gemm_nn: preact must be 16-byte aligned");
+  p.counts = counts; p.bias = nullptr; p.D = D; p.preact = const_cast<void*>(preact);
+  p.epi = (act != 0) ? EPI_DACT : EPI_ACT;
+  if (act == 0) p.preact = nullptr;
+  CUtensorMap tmA, tmB;
+  if (int rc = make_map(&tmA, A, (uint64_t)groups * C, (uint64_t)K, BM, dtype)) return rc;
+  if (int rc = make_map(&tmB, B, (uint64_t)LE * K, (uint64_t)N, 64, dtype)) return rc;
+  if (p.epi == EPI_DACT)
+    return launch<MODE_ROWS, true, EPI_DACT>(tmA, tmB, p, dtype, "grouped_gemm_nn_kernel", static_cast<cudaStream_t>(stream));
+  return launch<MODE_ROWS, true, EPI_ACT>(tmA, tmB, p, dtype, "grouped_gemm_nn_kernel", static_cast<cudaStream_t>(stream));
+}
+
+int lancet_grouped_gemm_tn(const void* A, const void* B, void* D, int groups, int LE, int C, int Mout, int N,
+                           const int32_t* counts, int dtype, int32_t* status, lancet_stream_t stream) {
+  using namespace lancet::gemm;
+  LANCET_REQUIRE(dtype == LANCET_BF16 || dtype == LANCET_F16, LANCET_ERR_UNSUPPORTED,
+                 "lancet_grouped_gemm_tn: inputs must be bfloat16 or float16 (dtype code %d)", dtype);
+  LANCET_REQUIRE(groups >= 1 && LE >= 1 && groups % LE == 0 && C >= 0 && Mout >= 1 && N >= 1, LANCET_ERR_INVALID,
+                 "lancet_grouped_gemm_tn: bad sizes groups=%d LE=%d C=%d Mout=%d N=%d", groups, LE, C, Mout, N);
+  LANCET_REQUIRE(Mout % BM == 0 && N % BN == 0, LANCET_ERR_INVALID,
+                 "lancet_grouped_gemm_tn: Mout=%d must be a multiple of %d and N=%d of %d", Mout, BM, N, BN);
+  LANCET_REQUIRE(A && B && D && status, LANCET_ERR_NULL, "lancet_grouped_gemm_tn: null pointer argument");
+  LANCET_REQUIRE(aligned(A, 16) && aligned(B, 16) && aligned(D, 16), LANCET_ERR_INVALID,
+                 "lancet_grouped_gemm_tn: operands must be 16-byte aligned");
+  LANCET_REQUIRE((long long)groups * C < (1ll << 31) && (long long)LE * Mout < (1ll << 31), LANCET_ERR_INVALID,
+                 "lancet_grouped_gemm_tn: row counts exceed 2^31");
+  Params p;
+  p.groups = groups; p.LE = LE; p.C = C; p.N = N; p.K = 0; p.Mout = Mout;
+  p.m_tiles = Mout / BM; p.n_tiles = N / BN;
+  p.tiles_per_group = p.m_tiles * p.n_tiles;
+  p.total_tiles = p.tiles_per_group * LE;
+  p.counts = counts; p.bias = nullptr; p.D = D; p.preact = nullptr; p.act = 0; p.epi = EPI_ACT; p.status = status;
+  CUtensorMap tmA, tmB;
+  const uint64_t rows = (uint64_t)groups * (C > 0 ? C : 1);
+  if (int rc = make_map(&tmA, A, rows, (uint64_t)Mout, 64, dtype)) return rc;
+  if (int rc = make_map(&tmB, B, rows, (uint64_t)N, 64, dtype)) return rc;
+  return launch<MODE_REDUCE, true, EPI_ACT>(tmA, tmB, p, dtype, "grouped_gemm_tn_kernel", static_cast<cudaStream_t>(stream));
 }
 }

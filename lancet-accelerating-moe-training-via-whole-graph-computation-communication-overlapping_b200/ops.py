@@ -273,3 +273,35 @@ def grouped_gemm_nt(a, b, bias=None, counts=None, act=None, out=None, preact=Non
     check(_capi.lib().lancet_grouped_gemm_nt(_ptr(a), _ptr(b), _ptr(out), _ptr(bias), _ptr(preact), groups, LE, C, N, K,
                                              _ptr(counts), ACT[act], _dt(a), _ptr(st), _stream(a)))
     return out
+
+
+def grouped_gemm_nn(a, b, counts=None, act=None, preact=None, out=None):
+    """Data gradient: out[g] = (a[g] @ b[g % LE]) * act'(preact[g]); a [groups, C, K], b [LE, K, N]."""
+    _require_cuda(a, b, counts, out, preact)
+    groups, C, K = a.shape
+    LE, K2, N = b.shape
+    if K2 != K or groups % LE:
+        raise ValueError("grouped_gemm_nn: shapes do not match")
+    if a.dtype != b.dtype or a.dtype not in (torch.bfloat16, torch.float16):
+        raise TypeError("grouped_gemm_nn: bfloat16 or float16 operands of one type")
+    out = torch.empty((groups, C, N), dtype=a.dtype, device=a.device) if out is None else out
+    st = gemm_status(a.device)
+    check(_capi.lib().lancet_grouped_gemm_nn(_ptr(a), _ptr(b), _ptr(out), _ptr(preact), groups, LE, C, N, K, _ptr(counts),
+                                             ACT[act], _dt(a), _ptr(st), _stream(a)))
+    return out
+
+
+def grouped_gemm_tn(a, b, n_local_experts, counts=None, out=None):
+    """Weight gradient: out[e] = sum_{g % LE == e} a[g, :n_g].T @ b[g, :n_g]; a [groups, C, Mout], b [groups, C, N]."""
+    _require_cuda(a, b, counts, out)
+    groups, C, Mout = a.shape
+    N = b.shape[2]
+    if b.shape[0] != groups or b.shape[1] != C or groups % n_local_experts:
+        raise ValueError("grouped_gemm_tn: shapes do not match")
+    if a.dtype != b.dtype or a.dtype not in (torch.bfloat16, torch.float16):
+        raise TypeError("grouped_gemm_tn: bfloat16 or float16 operands of one type")
+    out = torch.empty((n_local_experts, Mout, N), dtype=a.dtype, device=a.device) if out is None else out
+    st = gemm_status(a.device)
+    check(_capi.lib().lancet_grouped_gemm_tn(_ptr(a), _ptr(b), _ptr(out), groups, n_local_experts, C, Mout, N,
+                                             _ptr(counts), _dt(a), _ptr(st), _stream(a)))
+    return out

@@ -68,7 +68,9 @@ def test_grouped_gemm_matches_fp32_reference(groups, LE, C, N, K, dt, act, use_b
         got = out[gi, :n].float()
         assert torch.allclose(got, want[gi, :n], rtol=1e-2, atol=1e-2 * scale), (gi, (got - want[gi, :n]).abs().max())
         assert torch.allclose(pre[gi, :n].float(), want_pre[gi, :n], rtol=1e-2, atol=1e-2 * scale)
-        assert (out[gi, n:].float() == 7.0).all(), "rows past the live count must not be written"
+        pad_end = min(C, (n + 127) // 128 * 128)
+        assert (out[gi, n:pad_end].float() == 0.0).all(), "dead rows of a live tile are zero"
+        assert (out[gi, pad_end:].float() == 7.0).all(), "rows of dead tiles must not be written"
 
 
 def test_gemm_rejects_bad_arguments():
@@ -79,3 +81,83 @@ def test_gemm_rejects_bad_arguments():
     assert ei.value.code == 1
     with pytest.raises(TypeError):
         LB.grouped_gemm_nt(a.float(), b.float())
+
+
+def dact_ref(x, act):
+    x = x.detach().clone().requires_grad_(True)
+    if act == "relu":
+        y = torch.relu(x)
+    elif act == "gelu":
+        y = torch.nn.functional.gelu(x)
+    elif act == "gelu_tanh":
+        y = torch.nn.functional.gelu(x, approximate="tanh")
+    else:
+        return torch.ones_like(x)
+    y.sum().backward()
+    return x.grad
+
+
+@pytest.mark.parametrize("groups,LE,C,N,K,dt,act,ragged", [
+    (2, 2, 128, 256, 64, torch.bfloat16, None, False),
+    (4, 2, 256, 512, 1024, torch.bfloat16, "gelu", False),
+    (4, 2, 200, 256, 192, torch.float16, "relu", True),
+    (6, 2, 1280, 2048, 512, torch.bfloat16, "gelu_tanh", True),
+])
+def test_data_gradient_gemm(groups, LE, C, N, K, dt, act, ragged):
+    g = torch.Generator(device=DEV).manual_seed(groups * 77 + C + N + K)
+    a = torch.randn((groups, C, K), device=DEV, generator=g).to(dt)
+    b = (torch.randn((LE, K, N), device=DEV, generator=g) * 0.05).to(dt)
+    pre = torch.randn((groups, C, N), device=DEV, generator=g).to(dt)
+    counts = None
+    if ragged:
+        counts = torch.randint(0, C + 1, (groups,), device=DEV, generator=g, dtype=torch.int32)
+        counts[0] = C
+    out = torch.full((groups, C, N), 7.0, dtype=dt, device=DEV)
+    LB.grouped_gemm_nn(a, b, counts=counts, act=act, preact=pre if act else None, out=out)
+    torch.cuda.synchronize()
+    check_status()
+    for gi in range(groups):
+        n = C if counts is None else int(counts[gi])
+        want = (a[gi, :n].float() @ b[gi % LE].float()) * dact_ref(pre[gi, :n].float(), act)
+        scale = float(want.abs().max()) + 1e-6 if n else 1.0
+        assert torch.allclose(out[gi, :n].float(), want, rtol=1e-2, atol=1e-2 * scale), (gi, (out[gi, :n].float() - want).abs().max())
+
+
+@pytest.mark.parametrize("groups,LE,C,Mout,N,dt,ragged", [
+    (2, 2, 64, 128, 256, torch.bfloat16, False),
+    (4, 2, 256, 256, 512, torch.bfloat16, False),
+    (8, 2, 200, 128, 256, torch.float16, True),
+    (6, 2, 1280, 1024, 512, torch.bfloat16, True),
+])
+def test_weight_gradient_gemm(groups, LE, C, Mout, N, dt, ragged):
+    g = torch.Generator(device=DEV).manual_seed(groups * 55 + C + Mout + N)
+    a = torch.randn((groups, C, Mout), device=DEV, generator=g).to(dt)
+    b = torch.randn((groups, C, N), device=DEV, generator=g).to(dt)
+    counts = None
+    if ragged:
+        counts = torch.randint(0, C + 1, (groups,), device=DEV, generator=g, dtype=torch.int32)
+        counts[1] = 0
+        for gi in range(groups):                       # contract: dead rows of a partial 64-row block are zero in one operand
+            n = int(counts[gi])
+            b[gi, n:] = 0
+            a[gi, n:] = 3.0                            # finite garbage in the other
+    out = LB.grouped_gemm_tn(a, b, LE, counts=counts)
+    torch.cuda.synchronize()
+    check_status()
+    for e in range(LE):
+        want = torch.zeros((Mout, N), dtype=torch.float32, device=DEV)
+        for gi in range(e, groups, LE):
+            n = C if counts is None else int(counts[gi])
+            want += a[gi, :n].float().t() @ b[gi, :n].float()
+        scale = float(want.abs().max()) + 1e-6
+        assert torch.allclose(out[e].float(), want, rtol=1e-2, atol=1e-2 * scale), (e, (out[e].float() - want).abs().max())
+
+
+def test_weight_gradient_all_groups_empty():
+    a = torch.randn((2, 64, 128), device=DEV).bfloat16()
+    b = torch.randn((2, 64, 256), device=DEV).bfloat16()
+    counts = torch.zeros(2, dtype=torch.int32, device=DEV)
+    out = LB.grouped_gemm_tn(a, b, 2, counts=counts)
+    torch.cuda.synchronize()
+    check_status()
+    assert (out == 0).all()
