@@ -220,6 +220,10 @@ int lancet_comm_init_rank(const unsigned char* id128, int world, int rank, lance
 int lancet_comm_destroy(lancet_comm_t comm);
 int lancet_all_to_all(const void* send, void* recv, size_t bytes_per_rank, lancet_comm_t comm,
                       lancet_stream_t stream);
+/* Same, taking the whole tensor size: splits it evenly over the communicator's ranks and fails with
+ * the reference's message when it does not divide (nccl.cc:213). */
+int lancet_all_to_all_evenly(const void* send, void* recv, size_t total_bytes, lancet_comm_t comm,
+                             lancet_stream_t stream);
 /* Peer-memory transport for receive buffers in symmetric memory: one kernel stores chunk i of
  * `send` into block `rank` of peer_recv[i].  Follow with lancet_p2p_barrier before reading. */
 int lancet_all_to_all_p2p(const void* send, void* const* peer_recv, size_t bytes_per_rank, int W, int rank,

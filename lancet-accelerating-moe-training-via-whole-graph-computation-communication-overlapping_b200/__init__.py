@@ -1,6 +1,6 @@
 """lancet_b200: B200-native MoE dispatch/combine, all-to-all, expert GEMM and LANS behind the
 operator surface of the reference (RAF `moe_encode`, `moe_decode`, `_all_to_all`, `lans`)."""
-from . import _capi, build  # noqa: F401
+from . import _capi, build, raf  # noqa: F401
 from ._capi import LancetError  # noqa: F401
 from .pipeline import ChunkedMoE  # noqa: F401
 from .collective import Communicator, SymmAllToAll  # noqa: F401

@@ -17,7 +17,15 @@ c_float = ctypes.c_float
 c_size_t = ctypes.c_size_t
 c_i64 = ctypes.c_int64
 
-HEADER = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "include", "lancet_b200.h")
+INCLUDE_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "include")
+HEADER = os.path.join(INCLUDE_DIR, "lancet_b200.h")
+
+
+class RafValue(ctypes.Structure):
+    """lancet_raf_value_t of include/lancet_raf_shim.h"""
+    _fields_ = [("kind", ctypes.c_int), ("data", ctypes.c_void_p), ("dtype_code", ctypes.c_int),
+                ("dtype_bits", ctypes.c_int), ("ndim", ctypes.c_int), ("shape", ctypes.c_int64 * 6),
+                ("scalar", ctypes.c_double), ("device_type", ctypes.c_int)]
 
 # name -> (restype, argtypes).  Kept next to the header; tests check that both list the same names.
 SIGNATURES = {
@@ -85,6 +93,14 @@ SIGNATURES = {
                                        c_int, c_int, c_void_p, c_void_p]),
     "lancet_grouped_gemm_tn": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int,
                                        c_void_p, c_void_p]),
+    "lancet_all_to_all_evenly": (c_int, [c_void_p, c_void_p, c_size_t, c_void_p, c_void_p]),
+    "lancet_raf_last_error": (ctypes.c_char_p, []),
+    "lancet_raf_declare": (c_int, [ctypes.c_char_p, ctypes.POINTER(RafValue), c_int, ctypes.POINTER(RafValue), c_int,
+                                   ctypes.POINTER(c_int)]),
+    "lancet_raf_execute": (c_int, [ctypes.c_char_p, ctypes.POINTER(RafValue), c_int, ctypes.POINTER(RafValue), c_int,
+                                   ctypes.c_char_p, c_int, c_void_p]),
+    "lancet_raf_set_communicator": (c_int, [c_void_p, c_int, c_int]),
+    "lancet_raf_dialect_ops": (c_int, [ctypes.c_char_p, ctypes.c_char_p, c_int]),
     "lancet_lans_workspace_bytes": (c_size_t, [c_int, ctypes.POINTER(c_i64)]),
     "lancet_lans": (c_int, [c_void_p, c_size_t, c_int, ctypes.POINTER(c_i64), ctypes.POINTER(c_void_p),
                             ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), c_int, c_int,
@@ -107,10 +123,15 @@ class LancetError(RuntimeError):
 
 
 def header_symbols():
-    """Names of all functions declared in include/lancet_b200.h."""
-    text = open(HEADER).read()
-    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(lancet_[a-z0-9_]+)\s*\(", text)))
+    """Names of all functions declared in include/*.h."""
+    names = set()
+    for fn in sorted(os.listdir(INCLUDE_DIR)):
+        if not fn.endswith(".h"):
+            continue
+        text = open(os.path.join(INCLUDE_DIR, fn)).read()
+        text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+        names.update(re.findall(r"\b(lancet_[a-z0-9_]+)\s*\(", text))
+    return sorted(names)
 
 
 def lib_path():

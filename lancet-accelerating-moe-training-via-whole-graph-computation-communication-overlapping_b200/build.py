@@ -46,11 +46,11 @@ def _compile(src, obj, verbose):
 def build(force=False, verbose=False):
     """Compile and link; returns the path of the shared library."""
     os.makedirs(OUT_DIR, exist_ok=True)
-    srcs = sorted(glob.glob(os.path.join(CSRC, "*.cu")))
+    srcs = sorted(glob.glob(os.path.join(CSRC, "*.cu"))) + sorted(glob.glob(os.path.join(CSRC, "raf_shim", "*.cc")))
     hdr_time = _newest_header()
     jobs, objs = [], []
     for src in srcs:
-        obj = os.path.join(OUT_DIR, os.path.basename(src)[:-3] + ".o")
+        obj = os.path.join(OUT_DIR, os.path.splitext(os.path.basename(src))[0] + ".o")
         objs.append(obj)
         stale = force or not os.path.exists(obj) or os.path.getmtime(obj) < max(os.path.getmtime(src), hdr_time)
         if stale:

@@ -188,6 +188,16 @@ int lancet_all_to_all(const void* send, void* recv, size_t bytes_per_rank, lance
   return LANCET_OK;
 }
 
+int lancet_all_to_all_evenly(const void* send, void* recv, size_t total_bytes, lancet_comm_t comm, lancet_stream_t stream) {
+  LANCET_REQUIRE(comm, LANCET_ERR_NULL, "lancet_all_to_all_evenly: null communicator");
+  LANCET_REQUIRE(nccl().ok, LANCET_ERR_COMM, "NCCL (libnccl.so.2) could not be loaded");
+  int W = 0;
+  LANCET_NCCL(nccl().CommCount(static_cast<ncclComm_t>(comm), &W));
+  LANCET_REQUIRE(W > 0 && total_bytes % (size_t)W == 0, LANCET_ERR_INVALID,
+                 "Cannot evenly distribute input tensor to all ranks (%zu bytes over %d ranks).", total_bytes, W);
+  return lancet_all_to_all(send, recv, total_bytes / W, comm, stream);
+}
+
 int lancet_all_to_all_p2p(const void* send, void* const* peer_recv, size_t bytes_per_rank, int W, int rank,
                           lancet_stream_t stream) {
   LANCET_REQUIRE(W >= 1 && W <= kMaxPeersA2A && rank >= 0 && rank < W, LANCET_ERR_INVALID,

@@ -1,0 +1,555 @@
+// OpEnvs of the MoE hot path, registered under the reference's dialect-qualified names so that a
+// RAF-style executor finds them where it found the originals:
+//   raf.op.cuda.{moe_encode, moe_decode, moe_encode_dx, moe_encode_dg, moe_decode_dx, moe_decode_dg, lans}
+//     (src/op/dialect/cuda/moe.cc:411, :1152, :1224, :1310, :1394, :1480; cuda/lans.cc:176-177)
+//   raf.op.nccl._all_to_all (src/op/dialect/nccl/nccl.cc:285-286)
+//   raf.op.cublas.matmul_nt (src/op/dialect/cublas/matmul.cc: the expert GEMM, here on tcgen05)
+// Constructors see the concrete shapes and issue their workspace / stream requests; Execute only
+// calls the C ABI on the current stream.  Declarations restate src/op/declare/moe.cc:26-299,
+// declare/optimizer.cc:46-63 and declare/collective_comm.cc:54-81.
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstring>
+
+#include "../../../include/lancet_b200.h"
+#include "../../../include/lancet_raf_shim.h"
+#include "raf_shim.h"
+
+namespace raf_shim {
+namespace {
+
+int LancetDType(const DType& d) {
+  if (d.code == kFloat && d.bits == 32) return LANCET_F32;
+  if (d.code == kFloat && d.bits == 16) return LANCET_F16;
+  if (d.code == kBFloat && d.bits == 16) return LANCET_BF16;
+  throw Error("unsupported dtype (float32, float16, bfloat16 only)");
+}
+
+void Ok(int rc) {
+  if (rc != LANCET_OK) throw Error(std::string("lancet_b200: ") + lancet_last_error());
+}
+
+const Tensor& TensorArg(const CallValues& cv, size_t i) {
+  RAF_SHIM_CHECK(i < cv.args.size() && cv.args[i].kind == Value::kTensor, "argument " + std::to_string(i) + " must be a tensor");
+  return cv.args[i].tensor;
+}
+
+Tensor Make(const Device& dev, DType dt, std::vector<int64_t> shape) {
+  Tensor t;
+  t.device = dev;
+  t.dtype = dt;
+  t.shape = std::move(shape);
+  return t;
+}
+
+int Capacity(int64_t S, int64_t E, float cf) { return lancet_moe_capacity((int)S, (int)E, cf, 1); }
+
+// ---------------------------------------------------------------- declarations
+void MoeEncodeDeclare(CallValues* call) {
+  const Tensor& data = TensorArg(*call, 0);
+  const Tensor& gate = TensorArg(*call, 1);
+  const Tensor& used = TensorArg(*call, 2);
+  RAF_SHIM_CHECK(data.shape.size() == 2, "Input data should be 2-D.");
+  RAF_SHIM_CHECK(gate.shape.size() == 2, "Input gate should be 2-D.");
+  RAF_SHIM_CHECK(used.shape.size() == 1, "Input used_capacity should be 1-D.");
+  RAF_SHIM_CHECK(data.shape[0] == gate.shape[0], "Input data and gate should have matching shape in dim 0.");
+  const float cf = call->args.size() > 3 ? (float)call->args[3].f : 1.0f;
+  const int64_t S = data.shape[0], M = data.shape[1], E = gate.shape[1];
+  const int64_t C = Capacity(S, E, cf);
+  call->out = Value::Tuple({Value::T(Make(data.device, {kFloat, 32}, {S})), Value::T(Make(data.device, {kInt, 32}, {2, S})),
+                            Value::T(Make(data.device, {kInt, 32}, {E})), Value::T(Make(data.device, {kUInt, 64}, {E})),
+                            Value::T(Make(data.device, data.dtype, {E, C, M}))});
+  call->device = data.device;
+}
+
+void MoeDecodeDeclare(CallValues* call) {
+  const Tensor& data = TensorArg(*call, 0);
+  const Tensor& il = TensorArg(*call, 2);
+  RAF_SHIM_CHECK(data.shape.size() == 3 && il.shape.size() == 2, "moe_decode: data must be 3-D, indices_locations 2-D");
+  call->out = Value::T(Make(data.device, data.dtype, {il.shape[1], data.shape[2]}));
+  call->device = data.device;
+}
+
+void MoeEncodeDxDeclare(CallValues* call) {
+  const Tensor& dy = TensorArg(*call, 0);
+  const Tensor& il = TensorArg(*call, 1);
+  RAF_SHIM_CHECK(dy.shape.size() == 3 && il.shape.size() == 2, "moe_encode_dx: dy must be 3-D, indices_locations 2-D");
+  call->out = Value::T(Make(dy.device, dy.dtype, {il.shape[1], dy.shape[2]}));
+  call->device = dy.device;
+}
+
+void MoeEncodeDgDeclare(CallValues* call) {
+  const Tensor& dy = TensorArg(*call, 0);
+  const Tensor& il = TensorArg(*call, 1);
+  RAF_SHIM_CHECK(call->args.size() > 2, "moe_encode_dg: n_experts is required");
+  call->out = Value::T(Make(dy.device, dy.dtype, {il.shape[1], call->args[2].i}));
+  call->device = dy.device;
+}
+
+void MoeDecodeDxDeclare(CallValues* call) {
+  const Tensor& dy = TensorArg(*call, 0);
+  RAF_SHIM_CHECK(call->args.size() > 4 && dy.shape.size() == 2, "moe_decode_dx: dy [S,M], gate, indices_locations, n_experts, capacity");
+  call->out = Value::T(Make(dy.device, dy.dtype, {call->args[3].i, call->args[4].i, dy.shape[1]}));
+  call->device = dy.device;
+}
+
+void MoeDecodeDgDeclare(CallValues* call) {
+  const Tensor& dy = TensorArg(*call, 0);
+  call->out = Value::T(Make(dy.device, dy.dtype, {dy.shape[0]}));
+  call->device = dy.device;
+}
+
+void LansDeclare(CallValues* call) {
+  RAF_SHIM_CHECK(!call->args.empty() && call->args[0].kind == Value::kTuple, "lans: tensor_list must be a tuple");
+  RAF_SHIM_CHECK(call->args[0].fields.size() % 4 == 0, "lans: tensor_list must hold 4 lists of equal length");
+  call->out = call->args[0];  // in place: the output tuple aliases the inputs (declare/optimizer.cc:46-63)
+  if (!call->out.fields.empty()) call->device = call->out.fields[0].tensor.device;
+}
+
+void AllToAllDeclare(CallValues* call) {
+  RAF_SHIM_CHECK(!call->args.empty() && call->args[0].kind == Value::kTuple && !call->args[0].fields.empty(),
+                 "_all_to_all: x must be a non-empty tuple of tensors");
+  const auto& f = call->args[0].fields;
+  if (f.size() == 1) {
+    call->out = Value::T(Make(f[0].tensor.device, f[0].tensor.dtype, f[0].tensor.shape));
+  } else {
+    std::vector<Value> outs;
+    for (const Value& v : f) outs.push_back(Value::T(Make(v.tensor.device, v.tensor.dtype, v.tensor.shape)));
+    call->out = Value::Tuple(outs);
+  }
+  call->device = f[0].tensor.device;
+}
+
+void MatmulNtDeclare(CallValues* call) {
+  const Tensor& a = TensorArg(*call, 0);
+  const Tensor& b = TensorArg(*call, 1);
+  RAF_SHIM_CHECK(a.shape.size() == 2 && b.shape.size() == 2 && a.shape[1] == b.shape[1], "matmul_nt: a [n,k], b [m,k]");
+  call->out = Value::T(Make(a.device, a.dtype, {a.shape[0], b.shape[0]}));
+  call->device = a.device;
+}
+
+RAF_OP_DECLARE("raf.op.moe_encode", MoeEncodeDeclare);
+RAF_OP_DECLARE("raf.op.moe_decode", MoeDecodeDeclare);
+RAF_OP_DECLARE("raf.op.moe_encode_dx", MoeEncodeDxDeclare);
+RAF_OP_DECLARE("raf.op.moe_encode_dg", MoeEncodeDgDeclare);
+RAF_OP_DECLARE("raf.op.moe_decode_dx", MoeDecodeDxDeclare);
+RAF_OP_DECLARE("raf.op.moe_decode_dg", MoeDecodeDgDeclare);
+RAF_OP_DECLARE("raf.op.lans", LansDeclare);
+RAF_OP_DECLARE("raf.op._all_to_all", AllToAllDeclare);
+RAF_OP_DECLARE("raf.op.matmul_nt", MatmulNtDeclare);
+
+// ---------------------------------------------------------------- op envs
+class MoeEncode : public OpEnv {
+ public:
+  explicit MoeEncode(const CallValues& cv) {
+    const Tensor& data = TensorArg(cv, 0);
+    const Tensor& gate = TensorArg(cv, 1);
+    S_ = (int)data.shape[0]; M_ = (int)data.shape[1]; E_ = (int)gate.shape[1];
+    cf_ = cv.args.size() > 3 ? (float)cv.args[3].f : 1.0f;
+    dtype_ = LancetDType(data.dtype);
+    gate_dtype_ = LancetDType(gate.dtype);
+    arg_indices = {0, 1, 2};  // data, gate, used_capacity
+    ws_bytes_ = lancet_moe_gate_workspace_bytes(S_, E_, 1);
+    RequestWorkspace(&ws_, cv.device, (int64_t)ws_bytes_);  // replaces the S*E one-hot workspace (cuda/moe.cc:133)
+  }
+  std::string name() const override { return "raf.op.cuda.moe_encode"; }
+  void Execute(const CallValues& cv) override { Execute({cv.args[0], cv.args[1], cv.args[2]}, cv.out); }
+  void Execute(const std::vector<Value>& in, Value out) override {
+    RAF_SHIM_CHECK(out.kind == Value::kTuple && out.fields.size() == 5, "Expected output to be a 5-Tuple");
+    const auto& o = out.fields;
+    Ok(lancet_moe_encode(in[0].tensor.data, in[1].tensor.data, gate_dtype_, (const int32_t*)in[2].tensor.data, cf_, S_, M_, E_,
+                         1, dtype_, o[0].tensor.data, LancetDType(o[0].tensor.dtype), (int32_t*)o[1].tensor.data,
+                         (int32_t*)o[2].tensor.data, (uint64_t*)o[3].tensor.data, o[4].tensor.data, ws_, ws_bytes_, 0,
+                         GetStream()));
+  }
+  static OpEnv* make(const CallValues& cv) { return new MoeEncode(cv); }
+
+ private:
+  int S_, M_, E_, dtype_, gate_dtype_;
+  float cf_;
+  void* ws_ = nullptr;
+  size_t ws_bytes_ = 0;
+};
+RAF_REGISTER_DIALECT_OP(cuda, moe_encode, 20);
+RAF_OP_ENV_MAKER("raf.op.cuda.moe_encode", MoeEncode::make);
+
+class MoeDecode : public OpEnv {
+ public:
+  explicit MoeDecode(const CallValues& cv) {
+    const Tensor& data = TensorArg(cv, 0);
+    E_ = (int)data.shape[0]; C_ = (int)data.shape[1]; M_ = (int)data.shape[2];
+    S_ = (int)TensorArg(cv, 2).shape[1];
+    dtype_ = LancetDType(data.dtype);
+    arg_indices = {0, 1, 2};
+  }
+  std::string name() const override { return "raf.op.cuda.moe_decode"; }
+  void Execute(const CallValues& cv) override { Execute({cv.args[0], cv.args[1], cv.args[2]}, cv.out); }
+  void Execute(const std::vector<Value>& in, Value out) override {
+    Ok(lancet_moe_decode_fwd(in[1].tensor.data, LancetDType(in[1].tensor.dtype), (const int32_t*)in[2].tensor.data, 1,
+                             in[0].tensor.data, out.tensor.data, S_, M_, C_, E_, dtype_, GetStream()));
+  }
+  static OpEnv* make(const CallValues& cv) { return new MoeDecode(cv); }
+
+ private:
+  int S_, M_, C_, E_, dtype_;
+};
+RAF_REGISTER_DIALECT_OP(cuda, moe_decode, 20);
+RAF_OP_ENV_MAKER("raf.op.cuda.moe_decode", MoeDecode::make);
+
+class MoeEncodeDx : public OpEnv {
+ public:
+  explicit MoeEncodeDx(const CallValues& cv) {
+    const Tensor& dy = TensorArg(cv, 0);
+    E_ = (int)dy.shape[0]; C_ = (int)dy.shape[1]; M_ = (int)dy.shape[2];
+    S_ = (int)TensorArg(cv, 1).shape[1];
+    dtype_ = LancetDType(dy.dtype);
+    arg_indices = {0, 1};
+  }
+  std::string name() const override { return "raf.op.cuda.moe_encode_dx"; }
+  void Execute(const CallValues& cv) override { Execute({cv.args[0], cv.args[1]}, cv.out); }
+  void Execute(const std::vector<Value>& in, Value out) override {
+    Ok(lancet_moe_encode_bwd_data((const int32_t*)in[1].tensor.data, 1, in[0].tensor.data, out.tensor.data, S_, M_, C_, E_,
+                                  dtype_, GetStream()));
+  }
+  static OpEnv* make(const CallValues& cv) { return new MoeEncodeDx(cv); }
+
+ private:
+  int S_, M_, C_, E_, dtype_;
+};
+RAF_REGISTER_DIALECT_OP(cuda, moe_encode_dx, 20);
+RAF_OP_ENV_MAKER("raf.op.cuda.moe_encode_dx", MoeEncodeDx::make);
+
+class MoeEncodeDg : public OpEnv {
+ public:
+  explicit MoeEncodeDg(const CallValues& cv) {
+    S_ = (int)TensorArg(cv, 1).shape[1];
+    E_ = (int)cv.args.at(2).i;
+    dtype_ = LancetDType(TensorArg(cv, 0).dtype);
+    arg_indices = {0, 1};
+  }
+  std::string name() const override { return "raf.op.cuda.moe_encode_dg"; }
+  void Execute(const CallValues& cv) override { Execute({cv.args[0], cv.args[1]}, cv.out); }
+  void Execute(const std::vector<Value>& in, Value out) override {
+    Ok(lancet_moe_encode_bwd_gate(in[0].tensor.data, dtype_, (const int32_t*)in[1].tensor.data, 1, nullptr, dtype_,
+                                  out.tensor.data, S_, E_, GetStream()));
+  }
+  static OpEnv* make(const CallValues& cv) { return new MoeEncodeDg(cv); }
+
+ private:
+  int S_, E_, dtype_;
+};
+RAF_REGISTER_DIALECT_OP(cuda, moe_encode_dg, 20);
+RAF_OP_ENV_MAKER("raf.op.cuda.moe_encode_dg", MoeEncodeDg::make);
+
+class MoeDecodeDx : public OpEnv {
+ public:
+  explicit MoeDecodeDx(const CallValues& cv) {
+    const Tensor& dy = TensorArg(cv, 0);
+    S_ = (int)dy.shape[0]; M_ = (int)dy.shape[1];
+    E_ = (int)cv.args.at(3).i; C_ = (int)cv.args.at(4).i;
+    dtype_ = LancetDType(dy.dtype);
+    arg_indices = {0, 1, 2};
+  }
+  std::string name() const override { return "raf.op.cuda.moe_decode_dx"; }
+  void Execute(const CallValues& cv) override { Execute({cv.args[0], cv.args[1], cv.args[2]}, cv.out); }
+  void Execute(const std::vector<Value>& in, Value out) override {
+    Ok(lancet_moe_decode_bwd_data(in[1].tensor.data, LancetDType(in[1].tensor.dtype), (const int32_t*)in[2].tensor.data, 1,
+                                  in[0].tensor.data, out.tensor.data, nullptr, S_, M_, C_, E_, dtype_, GetStream()));
+  }
+  static OpEnv* make(const CallValues& cv) { return new MoeDecodeDx(cv); }
+
+ private:
+  int S_, M_, C_, E_, dtype_;
+};
+RAF_REGISTER_DIALECT_OP(cuda, moe_decode_dx, 20);
+RAF_OP_ENV_MAKER("raf.op.cuda.moe_decode_dx", MoeDecodeDx::make);
+
+class MoeDecodeDg : public OpEnv {
+ public:
+  explicit MoeDecodeDg(const CallValues& cv) {
+    const Tensor& dy = TensorArg(cv, 0);
+    const Tensor& data = TensorArg(cv, 1);
+    S_ = (int)dy.shape[0]; M_ = (int)dy.shape[1];
+    E_ = (int)data.shape[0]; C_ = (int)data.shape[1];
+    dtype_ = LancetDType(dy.dtype);
+    arg_indices = {0, 1, 2};
+  }
+  std::string name() const override { return "raf.op.cuda.moe_decode_dg"; }
+  void Execute(const CallValues& cv) override { Execute({cv.args[0], cv.args[1], cv.args[2]}, cv.out); }
+  void Execute(const std::vector<Value>& in, Value out) override {
+    Ok(lancet_moe_decode_bwd_gate((const int32_t*)in[2].tensor.data, 1, in[0].tensor.data, in[1].tensor.data, out.tensor.data,
+                                  LancetDType(out.tensor.dtype), S_, M_, C_, E_, dtype_, GetStream()));
+  }
+  static OpEnv* make(const CallValues& cv) { return new MoeDecodeDg(cv); }
+
+ private:
+  int S_, M_, C_, E_, dtype_;
+};
+RAF_REGISTER_DIALECT_OP(cuda, moe_decode_dg, 20);
+RAF_OP_ENV_MAKER("raf.op.cuda.moe_decode_dg", MoeDecodeDg::make);
+
+// lans(tensor_list = g + x + m + v, step, learning_rate, beta1, beta2, eps, bias_correction, weight_decay,
+//      grad_averaging, mode, normalize_grad): scripts/src_codegen/def_schema.py:726-742, cuda/lans.cc:26-177
+class LansImpl : public OpEnv {
+ public:
+  explicit LansImpl(const CallValues& cv) {
+    RAF_SHIM_CHECK(cv.args.size() >= 11, "lans takes 11 arguments");
+    const auto& tl = cv.args[0].fields;
+    RAF_SHIM_CHECK(tl.size() % 4 == 0, "lans: tensor_list must hold 4 lists of equal length");
+    n_ = (int)tl.size() / 4;
+    for (int i = 0; i < n_; ++i) {
+      RAF_SHIM_CHECK(tl[i].tensor.dtype.code == kFloat && tl[i].tensor.dtype.bits == 32, "Unsupported dtype: only float32");
+      numels_.push_back(tl[i].tensor.numel());
+    }
+    lr_ = (float)cv.args[2].f; beta1_ = (float)cv.args[3].f; beta2_ = (float)cv.args[4].f; eps_ = (float)cv.args[5].f;
+    bias_correction_ = (int)cv.args[6].i; wd_ = (float)cv.args[7].f; grad_averaging_ = (int)cv.args[8].i;
+    mode_ = (int)cv.args[9].i; normalize_grad_ = cv.args[10].i != 0;
+    arg_indices = {0, 1};
+    ws_bytes_ = n_ ? lancet_lans_workspace_bytes(n_, numels_.data()) : 0;
+    if (ws_bytes_) RequestWorkspace(&ws_, cv.device, (int64_t)ws_bytes_);
+  }
+  std::string name() const override { return "raf.op.cuda.lans"; }
+  void Execute(const CallValues& cv) override { Execute({cv.args[0], cv.args[1]}, cv.out); }
+  void Execute(const std::vector<Value>& in, Value /*output aliases the inputs*/) override {
+    if (n_ == 0) return;
+    const auto& tl = in[0].fields;
+    // step: host scalar, CPU tensor, or (as in the reference, cuda/lans.cc:102-107) a device tensor read back
+    float fstep = 0;
+    const Value& s = in[1];
+    if (s.kind == Value::kTensor) {
+      if (s.tensor.device.device_type == 1) {
+        fstep = *static_cast<const float*>(s.tensor.data);
+      } else {
+        RAF_SHIM_CHECK(cudaMemcpy(&fstep, s.tensor.data, sizeof(float), cudaMemcpyDeviceToHost) == cudaSuccess, "reading step failed");
+      }
+    } else {
+      fstep = (float)s.f;
+    }
+    std::vector<void*> g(n_), p(n_), m(n_), v(n_);
+    for (int i = 0; i < n_; ++i) {
+      g[i] = tl[i].tensor.data; p[i] = tl[n_ + i].tensor.data; m[i] = tl[2 * n_ + i].tensor.data; v[i] = tl[3 * n_ + i].tensor.data;
+    }
+    // the executor may hand out a different workspace on every call (src/impl/vm/vm.cc:1260-1266): the
+    // tensor table is reused only while workspace and tensor addresses stay the same
+    std::vector<void*> key = g;
+    key.insert(key.end(), p.begin(), p.end());
+    key.insert(key.end(), m.begin(), m.end());
+    key.insert(key.end(), v.begin(), v.end());
+    key.push_back(ws_);
+    const int flags = (key == last_key_) ? LANCET_LANS_TABLES_READY : 0;
+    Ok(lancet_lans(ws_, ws_bytes_, n_, numels_.data(), g.data(), p.data(), m.data(), v.data(), LANCET_F32, (int)fstep, lr_, beta1_,
+                   beta2_, eps_, bias_correction_, wd_, grad_averaging_, mode_, normalize_grad_ ? 1 : 0, flags, GetStream()));
+    last_key_ = key;
+  }
+  static OpEnv* make(const CallValues& cv) { return new LansImpl(cv); }
+
+ private:
+  int n_ = 0, bias_correction_ = 1, grad_averaging_ = 1, mode_ = 1;
+  bool normalize_grad_ = true;
+  float lr_, beta1_, beta2_, eps_, wd_;
+  std::vector<int64_t> numels_;
+  std::vector<void*> last_key_;
+  void* ws_ = nullptr;
+  size_t ws_bytes_ = 0;
+};
+RAF_REGISTER_DIALECT_OP(cuda, lans, 20);
+RAF_OP_ENV_MAKER("raf.op.cuda.lans", LansImpl::make);
+
+// _all_to_all over NCCL, single tensor (the tuple form of nccl.cc:228-277 is declined)
+class NCCLAllToAll : public OpEnv {
+ public:
+  explicit NCCLAllToAll(const CallValues& cv) {
+    arg_indices = {0};
+    RequestStream(&stream_, cv.device, kCudaCommunicate);
+    RequestDistributed(&communicator_);
+    total_bytes_ = (size_t)cv.args[0].fields[0].tensor.nbytes();
+  }
+  std::string name() const override { return "raf.op.nccl._all_to_all"; }
+  void Execute(const CallValues& cv) override { Execute({cv.args[0]}, cv.out); }
+  void Execute(const std::vector<Value>& in, Value out) override {
+    RAF_SHIM_CHECK(communicator_ != nullptr, "_all_to_all: no communicator (RequestDistributed was not satisfied)");
+    // the world size is the communicator's; the split must be even (nccl.cc:213)
+    Ok(lancet_all_to_all_evenly(in[0].fields[0].tensor.data, out.tensor.data, total_bytes_, communicator_, stream_));
+  }
+  static OpEnv* make(const CallValues& cv) {
+    if (cv.args.empty() || cv.args[0].kind != Value::kTuple || cv.args[0].fields.size() != 1) return nullptr;
+    return new NCCLAllToAll(cv);
+  }
+
+ private:
+  void* stream_ = nullptr;
+  void* communicator_ = nullptr;
+  size_t total_bytes_ = 0;
+};
+RAF_REGISTER_DIALECT_OP(nccl, _all_to_all, 10);
+RAF_OP_ENV_MAKER("raf.op.nccl._all_to_all", NCCLAllToAll::make);
+
+// matmul_nt(a [n,k], b [m,k]) -> [n,m]: the expert GEMM as one group on the tcgen05 kernel.  Declines
+// shapes or types the kernel does not take (the dispatcher then tries the next dialect).
+class MatmulNt : public OpEnv {
+ public:
+  explicit MatmulNt(const CallValues& cv) {
+    const Tensor& a = TensorArg(cv, 0);
+    const Tensor& b = TensorArg(cv, 1);
+    n_ = (int)a.shape[0]; k_ = (int)a.shape[1]; m_ = (int)b.shape[0];
+    dtype_ = LancetDType(a.dtype);
+    arg_indices = {0, 1};
+    RequestWorkspace(&status_, cv.device, 256);
+  }
+  std::string name() const override { return "raf.op.cublas.matmul_nt"; }
+  void Execute(const CallValues& cv) override { Execute({cv.args[0], cv.args[1]}, cv.out); }
+  void Execute(const std::vector<Value>& in, Value out) override {
+    RAF_SHIM_CHECK(cudaMemsetAsync(status_, 0, 4, (cudaStream_t)GetStream()) == cudaSuccess, "memset failed");
+    Ok(lancet_grouped_gemm_nt(in[0].tensor.data, in[1].tensor.data, out.tensor.data, nullptr, nullptr, 1, 1, n_, m_, k_, nullptr, 0,
+                              dtype_, (int32_t*)status_, GetStream()));
+  }
+  static OpEnv* make(const CallValues& cv) {
+    if (cv.args.size() < 2 || cv.args[0].kind != Value::kTensor || cv.args[1].kind != Value::kTensor) return nullptr;
+    const Tensor& a = cv.args[0].tensor;
+    const Tensor& b = cv.args[1].tensor;
+    if (a.dtype.bits != 16 || !(a.dtype == b.dtype)) return nullptr;
+    if (a.shape.size() != 2 || b.shape.size() != 2 || b.shape[0] % 256 != 0 || a.shape[1] % 8 != 0) return nullptr;
+    return new MatmulNt(cv);
+  }
+
+ private:
+  int n_, k_, m_, dtype_;
+  void* status_ = nullptr;
+};
+RAF_REGISTER_DIALECT_OP(cublas, matmul_nt, 15);
+RAF_OP_ENV_MAKER("raf.op.cublas.matmul_nt", MatmulNt::make);
+
+// ---------------------------------------------------------------- C bridge for hosts without C++ (tests)
+Value FromC(const lancet_raf_value_t* a, int n, int* pos) {
+  const lancet_raf_value_t& v = a[(*pos)++];
+  if (v.kind == LANCET_RAF_TENSOR) {
+    Tensor t;
+    t.data = v.data;
+    t.device.device_type = v.device_type ? v.device_type : 2;
+    t.dtype = {v.dtype_code, v.dtype_bits};
+    t.shape.assign(v.shape, v.shape + v.ndim);
+    return Value::T(t);
+  }
+  if (v.kind == LANCET_RAF_TUPLE) {
+    std::vector<Value> f;
+    for (int i = 0; i < v.ndim && *pos < n; ++i) f.push_back(FromC(a, n, pos));
+    return Value::Tuple(f);
+  }
+  if (v.kind == LANCET_RAF_INT) return Value::Int((int64_t)v.scalar);
+  if (v.kind == LANCET_RAF_FLOAT) return Value::Float(v.scalar);
+  return Value();
+}
+
+void ToC(const Value& v, lancet_raf_value_t* outs, int max_outs, int* n) {
+  if (v.kind == Value::kTuple) {
+    for (const Value& f : v.fields) ToC(f, outs, max_outs, n);
+    return;
+  }
+  if (v.kind != Value::kTensor) return;
+  RAF_SHIM_CHECK(*n < max_outs, "too many outputs");
+  lancet_raf_value_t& o = outs[(*n)++];
+  std::memset(&o, 0, sizeof(o));
+  o.kind = LANCET_RAF_TENSOR;
+  o.data = v.tensor.data;
+  o.dtype_code = v.tensor.dtype.code;
+  o.dtype_bits = v.tensor.dtype.bits;
+  o.device_type = v.tensor.device.device_type;
+  RAF_SHIM_CHECK(v.tensor.shape.size() <= 6, "rank above 6");
+  o.ndim = (int)v.tensor.shape.size();
+  for (int i = 0; i < o.ndim; ++i) o.shape[i] = v.tensor.shape[i];
+}
+
+thread_local std::string g_err;
+
+CallValues BuildCall(const char* op, const lancet_raf_value_t* args, int n_values) {
+  CallValues cv;
+  cv.op = op;
+  int pos = 0;
+  while (pos < n_values) cv.args.push_back(FromC(args, n_values, &pos));
+  return cv;
+}
+
+}  // namespace
+}  // namespace raf_shim
+
+extern "C" {
+using namespace raf_shim;
+
+const char* lancet_raf_last_error(void) { return g_err.c_str(); }
+
+int lancet_raf_declare(const char* op, const lancet_raf_value_t* args, int n_values, lancet_raf_value_t* outs, int max_outs,
+                       int* n_outs) {
+  try {
+    CallValues cv = BuildCall(op, args, n_values);
+    Declare(&cv);
+    int n = 0;
+    ToC(cv.out, outs, max_outs, &n);
+    *n_outs = n;
+    return 0;
+  } catch (const std::exception& e) {
+    g_err = e.what();
+    return 1;
+  }
+}
+
+int lancet_raf_execute(const char* op, const lancet_raf_value_t* args, int n_values, const lancet_raf_value_t* outs, int n_outs,
+                       char* dialect_op, int dialect_op_len, void* stream) {
+  std::vector<void*> workspaces;
+  try {
+    CallValues cv = BuildCall(op, args, n_values);
+    Declare(&cv);
+    // bind the caller's output buffers (the executor allocates them from the declaration)
+    int k = 0;
+    std::function<void(Value&)> bind = [&](Value& v) {
+      if (v.kind == Value::kTuple) {
+        for (Value& f : v.fields) bind(f);
+      } else if (v.kind == Value::kTensor) {
+        RAF_SHIM_CHECK(k < n_outs, "not enough output buffers");
+        if (cv.op != "raf.op.lans") v.tensor.data = outs[k].data;
+        ++k;
+      }
+    };
+    bind(cv.out);
+    SetStream(stream);
+    std::shared_ptr<OpEnv> env = Dispatch(cv);
+    if (dialect_op && dialect_op_len > 0) {
+      std::strncpy(dialect_op, env->name().c_str(), dialect_op_len - 1);
+      dialect_op[dialect_op_len - 1] = 0;
+    }
+    // what an executor does before Execute: satisfy the requests (src/impl/vm/vm.cc:1237-1266)
+    const Requests& rq = env->GetRequests();
+    for (const auto& w : rq.workspace) {
+      void* p = nullptr;
+      RAF_SHIM_CHECK(cudaMalloc(&p, (size_t)(w.nbytes > 0 ? w.nbytes : 1)) == cudaSuccess, "workspace allocation failed");
+      workspaces.push_back(p);
+      *w.dest = p;
+    }
+    for (const auto& s : rq.stream) *s.dest = stream;
+    for (const auto& d : rq.distributed) *d.dest = GetCommunicator();
+    env->Execute(cv);
+    RAF_SHIM_CHECK(cudaStreamSynchronize((cudaStream_t)stream) == cudaSuccess, "stream synchronisation failed");
+    for (void* p : workspaces) cudaFree(p);
+    return 0;
+  } catch (const std::exception& e) {
+    for (void* p : workspaces) cudaFree(p);
+    g_err = e.what();
+    return 1;
+  }
+}
+
+int lancet_raf_set_communicator(void* comm, int rank, int size) {
+  SetCommunicator(comm, rank, size);
+  return 0;
+}
+
+int lancet_raf_dialect_ops(const char* base_op, char* buf, int buf_len) {
+  std::string s;
+  for (const DialectEntry& e : DialectOps(base_op)) s += e.dialect_op + ":" + std::to_string(e.plevel) + ";";
+  if (buf && buf_len > 0) {
+    std::strncpy(buf, s.c_str(), buf_len - 1);
+    buf[buf_len - 1] = 0;
+  }
+  return (int)DialectOps(base_op).size();
+}
+}

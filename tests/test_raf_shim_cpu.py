@@ -1,0 +1,55 @@
+"""The RAF-style registry without a GPU: dialect priorities, declarations (output shapes and dtypes
+of src/op/declare/moe.cc of the reference) and error messages."""
+import os
+import subprocess
+
+import pytest
+import torch
+
+import lancet_b200 as LB
+from lancet_b200 import raf
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module", autouse=True)
+def built():
+    LB.build.build()
+
+
+def test_registry_cpp(tmp_path):
+    shim = os.path.join(LB.build.CSRC, "raf_shim")
+    exe = str(tmp_path / "test_raf_shim")
+    subprocess.run(["g++", "-std=c++17", "-O1", "-I", shim, os.path.join(ROOT, "tests", "cpp", "test_raf_shim.cc"),
+                    os.path.join(shim, "registry.cc"), "-o", exe], check=True)
+    r = subprocess.run([exe], capture_output=True, text=True)
+    assert r.returncode == 0 and "raf shim ok" in r.stdout, r.stdout + r.stderr
+
+
+def test_dialect_names_and_priorities():
+    assert raf.dialect_ops("raf.op.moe_encode") == [("raf.op.cuda.moe_encode", "20")]
+    assert raf.dialect_ops("raf.op._all_to_all") == [("raf.op.nccl._all_to_all", "10")]
+    assert raf.dialect_ops("raf.op.lans") == [("raf.op.cuda.lans", "20")]
+    assert raf.dialect_ops("raf.op.matmul_nt") == [("raf.op.cublas.matmul_nt", "15")]
+    for op in ("moe_decode", "moe_encode_dx", "moe_encode_dg", "moe_decode_dx", "moe_decode_dg"):
+        assert raf.dialect_ops("raf.op." + op) == [("raf.op.cuda." + op, "20")]
+
+
+def test_declarations():
+    x = torch.zeros(2048, 512)
+    gate = torch.zeros(2048, 8)
+    used = torch.zeros(8, dtype=torch.int32)
+    outs = raf.declare("raf.op.moe_encode", x, gate, used, 1.0)
+    assert outs == [((2048,), torch.float32), ((2, 2048), torch.int32), ((8,), torch.int32), ((8,), torch.uint64),
+                    ((8, 256, 512), torch.float32)]
+    outs = raf.declare("raf.op.moe_encode", x.half(), gate.half(), used, 2.0)
+    assert outs[4] == ((8, 512, 512), torch.float16)
+    il = torch.zeros(2, 2048, dtype=torch.int32)
+    assert raf.declare("raf.op.moe_decode", torch.zeros(8, 256, 512), torch.zeros(2048), il) == [((2048, 512), torch.float32)]
+    assert raf.declare("raf.op.moe_encode_dg", torch.zeros(2048), il, 8) == [((2048, 8), torch.float32)]
+    assert raf.declare("raf.op.moe_decode_dx", x, torch.zeros(2048), il, 8, 256) == [((8, 256, 512), torch.float32)]
+    assert raf.declare("raf.op._all_to_all", [torch.zeros(4, 6)]) == [((4, 6), torch.float32)]
+    with pytest.raises(raf.RafError, match="matching shape in dim 0"):
+        raf.declare("raf.op.moe_encode", x, torch.zeros(100, 8), used, 1.0)
+    with pytest.raises(raf.RafError, match="no declaration"):
+        raf.declare("raf.op.not_an_op", x)

@@ -1,0 +1,74 @@
+"""The operators run through the registry (dispatch + requests + Execute) reproduce the golden vectors
+of the reference's own operators."""
+import glob
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from lancet_b200 import raf
+from oracle import lans_oracle
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+GOLDEN = sorted(p for p in glob.glob(os.path.join(os.path.dirname(__file__), "golden", "moe_ref_*.npz"))
+                if "x" in np.load(p).files)
+
+
+def cu(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
+
+
+@pytest.mark.parametrize("path", GOLDEN, ids=[os.path.basename(p)[8:-4] for p in GOLDEN])
+def test_moe_ops_through_registry(path):
+    rec = np.load(path)
+    S, E, M, C = (int(rec[k]) for k in ("S", "E", "M", "C"))
+    outs, name = raf.call("raf.op.moe_encode", cu(rec["x"]), cu(rec["gate"]), torch.zeros(E, dtype=torch.int32, device=DEV), 1.0)
+    assert name == "raf.op.cuda.moe_encode"
+    gs, il, cap, el, disp = outs
+    np.testing.assert_array_equal(il.cpu().numpy(), rec["idx_loc"])
+    np.testing.assert_array_equal(cap.cpu().numpy(), rec["capused"])
+    np.testing.assert_array_equal(gs.cpu().numpy(), rec["gates_s"])
+    np.testing.assert_array_equal(disp.cpu().numpy(), rec["disp"])
+    (out,), name = raf.call("raf.op.moe_decode", cu(rec["eo"]), gs, il)
+    assert name == "raf.op.cuda.moe_decode"
+    np.testing.assert_array_equal(out.cpu().numpy(), rec["out"])
+    (dx,), _ = raf.call("raf.op.moe_encode_dx", cu(rec["d_disp"]), il)
+    np.testing.assert_array_equal(dx.cpu().numpy(), rec["enc_dx"])
+    (dg,), _ = raf.call("raf.op.moe_encode_dg", cu(rec["d_gates"]), il, E)
+    ref_dg = np.zeros((S, E), np.float32)
+    ref_dg[tuple(rec["enc_dg_nnz"])] = rec["enc_dg_val"]
+    np.testing.assert_array_equal(dg.cpu().numpy(), ref_dg)
+    (ddx,), _ = raf.call("raf.op.moe_decode_dx", cu(rec["d_out"]), gs, il, E, C)
+    np.testing.assert_array_equal(ddx.cpu().numpy(), rec["dec_dx"])
+    (ddg,), _ = raf.call("raf.op.moe_decode_dg", cu(rec["d_out"]), cu(rec["eo"]), il)
+    np.testing.assert_allclose(ddg.cpu().numpy(), rec["dec_dg"], rtol=1e-5, atol=1e-5)
+
+
+def test_lans_through_registry_with_device_step():
+    shapes = [(33, 65), (9000,), (5,)]
+    rng = np.random.default_rng(0)
+    p = [rng.normal(0, 0.02, s).astype(np.float32) for s in shapes]
+    g = [rng.normal(0, 1e-3, s).astype(np.float32) for s in shapes]
+    m = [rng.normal(0, 1e-4, s).astype(np.float32) for s in shapes]
+    v = [rng.uniform(0, 1e-6, s).astype(np.float32) for s in shapes]
+    wp, wm, wv = lans_oracle.lans_step(g, p, m, v, step=7, lr=1e-3)
+    tl = [cu(a) for a in g + p + m + v]
+    step = torch.tensor(7.0, device=DEV)            # the reference passes step as a 0-d device tensor
+    outs, name = raf.call("raf.op.lans", tl, step, 1e-3, 0.9, 0.999, 1e-6, 1, 0.01, 1, 1, True)
+    assert name == "raf.op.cuda.lans"
+    for i in range(3):
+        np.testing.assert_allclose(tl[3 + i].cpu().numpy(), wp[i], rtol=1e-5, atol=1e-8)
+        np.testing.assert_allclose(tl[6 + i].cpu().numpy(), wm[i], rtol=1e-5, atol=1e-10)
+
+
+def test_matmul_nt_dispatch_and_decline():
+    a = torch.randn(300, 128, device=DEV).bfloat16()
+    b = (torch.randn(512, 128, device=DEV) * 0.1).bfloat16()
+    (y,), name = raf.call("raf.op.matmul_nt", a, b)
+    assert name == "raf.op.cublas.matmul_nt"
+    want = a.float() @ b.float().t()
+    assert torch.allclose(y.float(), want, rtol=1e-2, atol=1e-2 * float(want.abs().max()))
+    with pytest.raises(raf.RafError, match="declined"):       # fp32 operands: the tensor-core op declines
+        raf.call("raf.op.matmul_nt", a.float(), b.float())
