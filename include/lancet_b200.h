@@ -169,6 +169,45 @@ int lancet_moe_combine_chunked(const void* expert_out, const void* gates_s, int 
                                const int32_t* idx_loc, int S, int M, int C, int E, int k, int n_chunks, int dtype,
                                void* out, lancet_stream_t stream);
 
+/* ---- batch-prioritized routing -------------------------------------------------------------------
+ * Replaces launch_gen_location_bpr and the argsort in front of it (kernel_util.cuh:67;
+ * src/op/dialect/cuda/moe.cc:415-729; tutel_moe_dispatch.cu:259-363).  gate is [S_orig,E] for the whole
+ * batch; the outputs describe partition `partition_id` of n_partitions (Sp = S_orig/n_partitions
+ * tokens): gates_s [Sp], idx_loc [2,Sp] with (-1,-1) for dropped tokens, out_capused / out_elems [E].
+ * Each expert keeps its C highest-gate tokens of the whole batch; ties go to the lower token index.
+ * lancet_moe_encode_bpr is the whole `raf.op.cuda.moe_encode_batch_prioritized` op: capacity
+ * (int)(cf * ceil(Sp / E)), gating, then dispatch of the partition's rows of x [S_orig, M]. */
+size_t lancet_moe_gate_bpr_workspace_bytes(int S_orig, int E);
+int lancet_moe_gate_bpr(const void* gate, int gate_dtype, int S_orig, int E, int n_partitions, int partition_id, int C,
+                        int M, void* out_gates_s, int gates_dtype, int32_t* out_idx_loc, int32_t* out_capused,
+                        uint64_t* out_elems, void* ws, size_t ws_bytes, lancet_stream_t stream);
+int lancet_moe_encode_bpr(const void* x, const void* gate, int gate_dtype, int n_partitions, int partition_id,
+                          float capacity_factor, int S_orig, int M, int E, int dtype, void* out_gates_s,
+                          int gates_dtype, int32_t* out_idx_loc, int32_t* out_capused, uint64_t* out_elems,
+                          void* dispatched, void* ws, size_t ws_bytes, lancet_stream_t stream);
+
+/* ---- re-compaction operators of graphs partitioned the reference's way --------------------------
+ * idx_locs / datas / recv_counts are HOST arrays of n_partitions device pointers (at most 16).
+ * ws: lancet_moe_partition_workspace_bytes(n_partitions, E) bytes.
+ * lancet_moe_merge_masks replaces launch_merge_masks (kernel_util.cuh:61-62; tutel_moe_dispatch.cu:214-255):
+ *   idx_locs[p] is [2,S]; out [2, n*S]; locations of partition p are shifted by the tokens kept for
+ *   the same expert in partitions < p; dropped tokens become (-1,-1).
+ * lancet_moe_redispatch replaces launch_redispatch (kernel_util.cuh:50-52; tutel_moe_dispatch.cu:365-408):
+ *   datas[p] is [E,C,M]; out [E,C,M] holds, per expert, the kept rows of all partitions one after the
+ *   other; rows past the merged count are zero (the reference leaves them unwritten).
+ * lancet_moe_redispatch_expert_input replaces launch_redispatch_expert_input (kernel_util.cuh:53-55;
+ *   tutel_moe_dispatch.cu:436-459): datas[p] is [C,G,M], recv_counts[p] uint64 [G*LE] (elements); column
+ *   g of out [C,G,M] is the concatenation over p of the first recv_counts[p][g*LE+le]*scale elements of
+ *   column g of datas[p]; the rest is zero. */
+size_t lancet_moe_partition_workspace_bytes(int n_partitions, int E);
+int lancet_moe_merge_masks(const int32_t* const* idx_locs, int n_partitions, int S, int E, int32_t* out, void* ws,
+                           size_t ws_bytes, lancet_stream_t stream);
+int lancet_moe_redispatch(const void* const* datas, const int32_t* const* idx_locs, int n_partitions, int S, int M,
+                          int C, int E, int dtype, void* out, void* ws, size_t ws_bytes, lancet_stream_t stream);
+int lancet_moe_redispatch_expert_input(const void* const* datas, const uint64_t* const* recv_counts, int n_partitions,
+                                       int local_expert_id, int n_local_experts, int C, int G, int M,
+                                       int recv_cnts_scale, int dtype, void* out, lancet_stream_t stream);
+
 /* ---- expert-parallel exchange fused into dispatch / combine over NVLink peer memory ------------
  * Replaces `moe_encode -> _all_to_all` and `_all_to_all -> moe_decode` of the MoE layer
  * (NCCLAllToAll::Execute, src/op/dialect/nccl/nccl.cc:199-227; layer wiring in

@@ -101,6 +101,17 @@ SIGNATURES = {
                                    ctypes.c_char_p, c_int, c_void_p]),
     "lancet_raf_set_communicator": (c_int, [c_void_p, c_int, c_int]),
     "lancet_raf_dialect_ops": (c_int, [ctypes.c_char_p, ctypes.c_char_p, c_int]),
+    "lancet_moe_gate_bpr_workspace_bytes": (c_size_t, [c_int, c_int]),
+    "lancet_moe_gate_bpr": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p,
+                                    c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "lancet_moe_encode_bpr": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_int, c_void_p,
+                                      c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "lancet_moe_partition_workspace_bytes": (c_size_t, [c_int, c_int]),
+    "lancet_moe_merge_masks": (c_int, [ctypes.POINTER(c_void_p), c_int, c_int, c_int, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "lancet_moe_redispatch": (c_int, [ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), c_int, c_int, c_int, c_int, c_int,
+                                      c_int, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "lancet_moe_redispatch_expert_input": (c_int, [ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), c_int, c_int, c_int,
+                                                   c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "lancet_lans_workspace_bytes": (c_size_t, [c_int, ctypes.POINTER(c_i64)]),
     "lancet_lans": (c_int, [c_void_p, c_size_t, c_int, ctypes.POINTER(c_i64), ctypes.POINTER(c_void_p),
                             ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), c_int, c_int,

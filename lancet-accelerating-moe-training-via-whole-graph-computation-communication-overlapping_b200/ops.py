@@ -305,3 +305,69 @@ def grouped_gemm_tn(a, b, n_local_experts, counts=None, out=None):
     check(_capi.lib().lancet_grouped_gemm_tn(_ptr(a), _ptr(b), _ptr(out), groups, n_local_experts, C, Mout, N,
                                              _ptr(counts), _dt(a), _ptr(st), _stream(a)))
     return out
+
+
+def _ptr_table(ts):
+    return (ctypes.c_void_p * len(ts))(*[t.data_ptr() for t in ts])
+
+
+def moe_merge_masks(indices_locations, n_experts):
+    """`raf.op.moe_merge_masks`: list of n [2,S] masks -> [2, n*S] with running per-expert offsets."""
+    _require_cuda(*indices_locations)
+    n, S = len(indices_locations), indices_locations[0].shape[1]
+    dev = indices_locations[0].device
+    out = torch.empty((2, n * S), dtype=torch.int32, device=dev)
+    L = _capi.lib()
+    ws = workspace(dev, L.lancet_moe_partition_workspace_bytes(n, n_experts), "partition")
+    check(L.lancet_moe_merge_masks(_ptr_table(indices_locations), n, S, n_experts, _ptr(out), _ptr(ws), ws.numel(),
+                                   _stream(out)))
+    return out
+
+
+def moe_redispatch(data, indices_locations):
+    """`raf.op.moe_redispatch`: n partitioned [E,C,M] buffers -> one compacted [E,C,M]."""
+    _require_cuda(*data, *indices_locations)
+    n = len(data)
+    E, C, M = data[0].shape
+    S = indices_locations[0].shape[1]
+    out = torch.empty_like(data[0])
+    L = _capi.lib()
+    ws = workspace(out.device, L.lancet_moe_partition_workspace_bytes(n, E), "partition")
+    check(L.lancet_moe_redispatch(_ptr_table(data), _ptr_table(indices_locations), n, S, M, C, E, _dt(out), _ptr(out),
+                                  _ptr(ws), ws.numel(), _stream(out)))
+    return out
+
+
+def moe_redispatch_expert_input(data, recv_cnts, local_expert_id, n_local_experts, recv_cnts_scale=1):
+    """`raf.op.moe_redispatch_expert_input`: n post-exchange [C,G,M] inputs -> one compacted [C,G,M]."""
+    _require_cuda(*data, *recv_cnts)
+    C, G, M = data[0].shape
+    out = torch.empty_like(data[0])
+    check(_capi.lib().lancet_moe_redispatch_expert_input(_ptr_table(data), _ptr_table(recv_cnts), len(data), local_expert_id,
+                                                         n_local_experts, C, G, M, recv_cnts_scale, _dt(out), _ptr(out),
+                                                         _stream(out)))
+    return out
+
+
+def moe_encode_batch_prioritized(data, gate, n_partitions=1, partition_id=0, capacity_factor=1.0):
+    """`raf.op.moe_encode_batch_prioritized`: data [S_orig, M] and gate [S_orig, E] of the whole batch;
+    returns the tuple5 of `moe_encode` for partition `partition_id`."""
+    _require_cuda(data, gate)
+    S_orig, M = data.shape
+    E = gate.shape[1]
+    if S_orig % n_partitions:
+        raise ValueError("S must be divisible by n_partitions")
+    Sp = S_orig // n_partitions
+    dev = data.device
+    L = _capi.lib()
+    C = L.lancet_moe_capacity(Sp, E, capacity_factor, 1)
+    gates_s = torch.empty((Sp,), dtype=torch.float32, device=dev)
+    idx_loc = torch.empty((2, Sp), dtype=torch.int32, device=dev)
+    capused = torch.empty((E,), dtype=torch.int32, device=dev)
+    elems = torch.empty((E,), dtype=torch.uint64, device=dev)
+    disp = torch.empty((E, C, M), dtype=data.dtype, device=dev)
+    ws = workspace(dev, L.lancet_moe_gate_bpr_workspace_bytes(S_orig, E), "bpr")
+    check(L.lancet_moe_encode_bpr(_ptr(data), _ptr(gate), _dt(gate), n_partitions, partition_id, capacity_factor, S_orig, M,
+                                  E, _dt(data), _ptr(gates_s), _capi.F32, _ptr(idx_loc), _ptr(capused), _ptr(elems),
+                                  _ptr(disp), _ptr(ws), ws.numel(), _stream(data)))
+    return gates_s, idx_loc, capused, elems, disp

@@ -271,3 +271,67 @@ def test_chunked_plan_matches_chained_oracle(S, E, M, k, n, cf):
         ref = np.concatenate([O.moe_decode_fwd(want.astype(np.float32), gs, gl) for gs, gl in outs])
         np.testing.assert_array_equal(host(out).astype(np.float32),
                                       torch.from_numpy(ref).half().float().numpy())
+
+
+@pytest.mark.parametrize("n,dt", [(2, "f32"), (4, "f32"), (3, "f16")])
+def test_merge_masks_and_redispatch_equal_unpartitioned(n, dt):
+    """tests/python/op/cuda/test_cuda_moe.py:387-471 of the reference: n chained moe_encode(cf*n) +
+    moe_merge_masks + moe_redispatch == one moe_encode(cf) after masking."""
+    rng = np.random.default_rng(n)
+    S, M, E = 1536, 24, 2 if n != 3 else 6
+    tdt = TDT[dt]
+    x = torch.from_numpy(rng.standard_normal((S, M)).astype(np.float32)).to(tdt)
+    gate = torch.from_numpy(rng.random((S, E), dtype=np.float32))
+    ref = LB.moe_encode(x.to(DEV), gate.to(DEV), torch.zeros(E, dtype=torch.int32, device=DEV), 1.0)
+    cap = torch.zeros(E, dtype=torch.int32, device=DEV)
+    ils, ds = [], []
+    for i in range(n):
+        sl = slice(i * S // n, (i + 1) * S // n)
+        out = LB.moe_encode(x[sl].to(DEV), gate[sl].to(DEV), cap, float(n))
+        ils.append(out[1]); ds.append(out[4]); cap = out[2]
+    mil = LB.moe_merge_masks(ils, E)
+    md = LB.moe_redispatch(ds, ils)
+    w_mil = O.moe_merge_masks([host(t) for t in ils], E)
+    w_md = O.moe_redispatch([host(t).astype(np.float32) for t in ds], [host(t) for t in ils])
+    np.testing.assert_array_equal(host(mil), w_mil)
+    np.testing.assert_array_equal(host(md).astype(np.float32), w_md)
+    ril = host(ref[1]).copy()
+    ril[1][ril[0] < 0] = -1
+    np.testing.assert_array_equal(host(mil), ril)
+    for e in range(E):
+        kept = int((ril[0] == e).sum())
+        np.testing.assert_array_equal(host(md)[e, :kept], host(ref[4])[e, :kept])
+
+
+def test_redispatch_expert_input():
+    """tests/python/distributed/test_partitioned_moe.py:99-196 pattern: [C,G,M] partitions compacted by counts."""
+    rng = np.random.default_rng(12)
+    n, C, G, M, LE, le = 3, 40, 4, 16, 2, 1
+    datas = [rng.standard_normal((C, G, M)).astype(np.float32) for _ in range(n)]
+    rcs = [(rng.integers(0, 15, G * LE) * M).astype(np.uint64) for _ in range(n)]
+    rcs[1][0 * LE + le] = 30 * M                                   # overflow past C is clipped
+    got = LB.moe_redispatch_expert_input([cu(d) for d in datas], [cu(r.astype(np.int64)) for r in rcs], le, LE)
+    want = O.moe_redispatch_expert_input(datas, rcs, le, LE, M)
+    np.testing.assert_array_equal(host(got), want)
+
+
+@pytest.mark.parametrize("S,E,M,n,cf,dt", [(1024, 32, 128, 1, 1.0, "f32"), (2048, 64, 128, 1, 1.0, "f32"),
+                                           (2048, 32, 16, 2, 2.0, "f32"), (2048, 64, 8, 4, 4.0, "f16"),
+                                           (999, 3, 8, 1, 1.0, "f32"), (1200, 8, 8, 3, 1.5, "f32")])
+def test_batch_prioritized_routing(S, E, M, n, cf, dt):
+    """Shapes of tests/python/op/cuda/test_cuda_moe.py:160-327 of the reference (gate ~ U[0,1), seed 0),
+    plus ragged ones and a case with many ties."""
+    rng = np.random.default_rng(0)
+    x = torch.from_numpy(rng.standard_normal((S, M)).astype(np.float32)).to(TDT[dt])
+    gate = rng.random((S, E), dtype=np.float32)
+    if S == 999:
+        gate = np.round(gate * 4) / 4                # heavy ties: resolved towards the lower token index
+    x_np = x.float().numpy() if dt != "f32" else x.numpy()
+    for pid in range(n):
+        want = O.moe_encode_bpr(x_np, gate, n, pid, cf)
+        got = LB.moe_encode_batch_prioritized(x.to(DEV), cu(gate), n, pid, cf)
+        np.testing.assert_array_equal(host(got[0]), want[0])
+        np.testing.assert_array_equal(host(got[1]), want[1])
+        np.testing.assert_array_equal(host(got[2]), want[2])
+        np.testing.assert_array_equal(host(got[3]), want[3])
+        np.testing.assert_array_equal(host(got[4]).astype(np.float32), want[4].astype(np.float32))
