@@ -228,24 +228,52 @@ def run_moe(args):
     value = S_TOKENS * world / (ms_step / 1e3)
 
     # ---- end to end: pinned host inputs in, combined output back, every step ---------------------
+    # Three streams, double-buffered device tensors: the host->device copy of step i+1 and the device->host copy
+    # of step i-1 run while step i computes (PCIe is full duplex), as a data loader with prefetch would do.
     e2e_steps = max(3, min(args.steps, 50))
     x_pin = [x.pin_memory() for x in xs_h]
     g_pin = [g.pin_memory() for g in gates_h]
-    out_pin = torch.empty((S_TOKENS, M_DIM), dtype=torch.float16).pin_memory()
-    x_dev, g_dev = torch.empty_like(xs[0]), torch.empty_like(gates[0])
+    out_pin = [torch.empty((S_TOKENS, M_DIM), dtype=torch.float16).pin_memory() for _ in range(2)]
+    x_dev = [torch.empty_like(xs[0]) for _ in range(2)]
+    g_dev = [torch.empty_like(gates[0]) for _ in range(2)]
+    out_dev = [torch.empty((S_TOKENS, M_DIM), dtype=torch.float16, device=dev) for _ in range(2)]
+    s_comp = torch.cuda.current_stream()
+    s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+    ev_in = [torch.cuda.Event() for _ in range(2)]
+    ev_comp = [torch.cuda.Event() for _ in range(2)]
+    ev_outd = [torch.cuda.Event() for _ in range(2)]
 
     def e2e_step(i):
-        x_dev.copy_(x_pin[i % 2], non_blocking=True)
-        g_dev.copy_(g_pin[i % 2], non_blocking=True)
-        plan.dispatch(x_dev, g_dev)
-        out_pin.copy_(plan.combine(), non_blocking=True)
+        b = i % 2
+        with torch.cuda.stream(s_in):
+            if i >= 2:
+                s_in.wait_event(ev_comp[b])          # step i-2 has finished reading x_dev[b]
+            x_dev[b].copy_(x_pin[b], non_blocking=True)
+            g_dev[b].copy_(g_pin[b], non_blocking=True)
+            ev_in[b].record(s_in)
+        s_comp.wait_event(ev_in[b])
+        if i >= 2:
+            s_comp.wait_event(ev_outd[b])            # step i-2's result has left out_dev[b]
+        plan.dispatch(x_dev[b], g_dev[b])
+        plan.combine(out=out_dev[b])
+        ev_comp[b].record(s_comp)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(ev_comp[b])
+            out_pin[b].copy_(out_dev[b], non_blocking=True)
+            ev_outd[b].record(s_out)
 
-    for i in range(3):
+    def e2e_join():
+        s_comp.wait_stream(s_in)
+        s_comp.wait_stream(s_out)
+
+    for i in range(4):
         e2e_step(i)
+    e2e_join()
     sync_all()
     ev0.record()
     for i in range(e2e_steps):
         e2e_step(i)
+    e2e_join()
     ev1.record()
     sync_all()
     e2e_ms = ev0.elapsed_time(ev1)

@@ -129,6 +129,57 @@ void MatmulNtDeclare(CallValues* call) {
   call->device = a.device;
 }
 
+
+void MoeEncodeBprDeclare(CallValues* call) {
+  const Tensor& data = TensorArg(*call, 0);
+  const Tensor& gate = TensorArg(*call, 1);
+  RAF_SHIM_CHECK(data.shape.size() == 2 && gate.shape.size() == 2, "Expected input data to be 2D.");
+  RAF_SHIM_CHECK(data.shape[0] == gate.shape[0], "Input data and gate should have matching shape in dim 0.");
+  const int64_t n = call->args.size() > 2 ? call->args[2].i : 1;
+  const float cf = call->args.size() > 4 ? (float)call->args[4].f : 1.0f;
+  RAF_SHIM_CHECK(n >= 1 && data.shape[0] % n == 0, "the batch must split evenly into n_partitions");
+  const int64_t S = data.shape[0] / n, M = data.shape[1], E = gate.shape[1];
+  const int64_t C = Capacity(S, E, cf);  // from the per-partition token count (cuda/moe.cc:433-438)
+  call->out = Value::Tuple({Value::T(Make(data.device, {kFloat, 32}, {S})), Value::T(Make(data.device, {kInt, 32}, {2, S})),
+                            Value::T(Make(data.device, {kInt, 32}, {E})), Value::T(Make(data.device, {kUInt, 64}, {E})),
+                            Value::T(Make(data.device, data.dtype, {E, C, M}))});
+  call->device = data.device;
+}
+
+void MoeMergeMasksDeclare(CallValues* call) {
+  RAF_SHIM_CHECK(!call->args.empty() && call->args[0].kind == Value::kTuple && !call->args[0].fields.empty(),
+                 "moe_merge_masks: indices_locations must be a non-empty tuple");
+  const Tensor& m0 = call->args[0].fields[0].tensor;
+  RAF_SHIM_CHECK(m0.shape.size() == 2, "Input indices_locations should be 2-D.");
+  call->out = Value::T(Make(m0.device, {kInt, 32}, {2, m0.shape[1] * (int64_t)call->args[0].fields.size()}));
+  call->device = m0.device;
+}
+
+void MoeRedispatchDeclare(CallValues* call) {
+  RAF_SHIM_CHECK(call->args.size() >= 2 && call->args[0].kind == Value::kTuple && !call->args[0].fields.empty(),
+                 "moe_redispatch: data must be a non-empty tuple");
+  const Tensor& d0 = call->args[0].fields[0].tensor;
+  RAF_SHIM_CHECK(d0.shape.size() == 3, "moe_redispatch: data should be 3-D.");
+  // the reference's declaration hard-codes float32 here (declare/moe.cc:136) while its type relation keeps the
+  // input dtype (ty/moe.cc:141); the input dtype is used
+  call->out = Value::T(Make(d0.device, d0.dtype, d0.shape));
+  call->device = d0.device;
+}
+
+void MoeRedispatchExpertInputDeclare(CallValues* call) {
+  RAF_SHIM_CHECK(call->args.size() >= 4 && call->args[0].kind == Value::kTuple && !call->args[0].fields.empty(),
+                 "moe_redispatch_expert_input: data must be a non-empty tuple");
+  const Tensor& d0 = call->args[0].fields[0].tensor;
+  RAF_SHIM_CHECK(d0.shape.size() == 3, "moe_redispatch_expert_input: data should be [C, G, M].");
+  call->out = Value::T(Make(d0.device, d0.dtype, d0.shape));
+  call->device = d0.device;
+}
+
+RAF_OP_DECLARE("raf.op.moe_encode_batch_prioritized", MoeEncodeBprDeclare);
+RAF_OP_DECLARE("raf.op.moe_merge_masks", MoeMergeMasksDeclare);
+RAF_OP_DECLARE("raf.op.moe_redispatch", MoeRedispatchDeclare);
+RAF_OP_DECLARE("raf.op.moe_redispatch_expert_input", MoeRedispatchExpertInputDeclare);
+
 RAF_OP_DECLARE("raf.op.moe_encode", MoeEncodeDeclare);
 RAF_OP_DECLARE("raf.op.moe_decode", MoeDecodeDeclare);
 RAF_OP_DECLARE("raf.op.moe_encode_dx", MoeEncodeDxDeclare);
@@ -288,6 +339,132 @@ class MoeDecodeDg : public OpEnv {
 };
 RAF_REGISTER_DIALECT_OP(cuda, moe_decode_dg, 20);
 RAF_OP_ENV_MAKER("raf.op.cuda.moe_decode_dg", MoeDecodeDg::make);
+
+
+// moe_encode_batch_prioritized(data, gate, n_partitions, partition_id, capacity_factor): def_schema.py:648-654
+class MoeEncodeBatchPrioritized : public OpEnv {
+ public:
+  explicit MoeEncodeBatchPrioritized(const CallValues& cv) {
+    const Tensor& data = TensorArg(cv, 0);
+    const Tensor& gate = TensorArg(cv, 1);
+    S_ = (int)data.shape[0]; M_ = (int)data.shape[1]; E_ = (int)gate.shape[1];
+    n_ = cv.args.size() > 2 ? (int)cv.args[2].i : 1;
+    pid_ = cv.args.size() > 3 ? (int)cv.args[3].i : 0;
+    cf_ = cv.args.size() > 4 ? (float)cv.args[4].f : 1.0f;
+    dtype_ = LancetDType(data.dtype);
+    gate_dtype_ = LancetDType(gate.dtype);
+    arg_indices = {0, 1};
+    ws_bytes_ = lancet_moe_gate_bpr_workspace_bytes(S_, E_);
+    RequestWorkspace(&ws_, cv.device, (int64_t)ws_bytes_);
+  }
+  std::string name() const override { return "raf.op.cuda.moe_encode_batch_prioritized"; }
+  void Execute(const CallValues& cv) override { Execute({cv.args[0], cv.args[1]}, cv.out); }
+  void Execute(const std::vector<Value>& in, Value out) override {
+    RAF_SHIM_CHECK(out.kind == Value::kTuple && out.fields.size() == 5, "Expected output to be a 5-Tuple");
+    const auto& o = out.fields;
+    Ok(lancet_moe_encode_bpr(in[0].tensor.data, in[1].tensor.data, gate_dtype_, n_, pid_, cf_, S_, M_, E_, dtype_, o[0].tensor.data,
+                             LancetDType(o[0].tensor.dtype), (int32_t*)o[1].tensor.data, (int32_t*)o[2].tensor.data,
+                             (uint64_t*)o[3].tensor.data, o[4].tensor.data, ws_, ws_bytes_, GetStream()));
+  }
+  static OpEnv* make(const CallValues& cv) { return new MoeEncodeBatchPrioritized(cv); }
+
+ private:
+  int S_, M_, E_, n_, pid_, dtype_, gate_dtype_;
+  float cf_;
+  void* ws_ = nullptr;
+  size_t ws_bytes_ = 0;
+};
+RAF_REGISTER_DIALECT_OP(cuda, moe_encode_batch_prioritized, 20);
+RAF_OP_ENV_MAKER("raf.op.cuda.moe_encode_batch_prioritized", MoeEncodeBatchPrioritized::make);
+
+class MoeMergeMasks : public OpEnv {
+ public:
+  explicit MoeMergeMasks(const CallValues& cv) {
+    n_ = (int)cv.args[0].fields.size();
+    S_ = (int)cv.args[0].fields[0].tensor.shape[1];
+    E_ = (int)cv.args.at(1).i;
+    arg_indices = {0};
+    ws_bytes_ = lancet_moe_partition_workspace_bytes(n_, E_);
+    RequestWorkspace(&ws_, cv.device, (int64_t)ws_bytes_);  // replaces the pinned pointer table of cuda/moe.cc:755-789
+  }
+  std::string name() const override { return "raf.op.cuda.moe_merge_masks"; }
+  void Execute(const CallValues& cv) override { Execute({cv.args[0]}, cv.out); }
+  void Execute(const std::vector<Value>& in, Value out) override {
+    std::vector<const int32_t*> p;
+    for (const Value& v : in[0].fields) p.push_back((const int32_t*)v.tensor.data);
+    Ok(lancet_moe_merge_masks(p.data(), n_, S_, E_, (int32_t*)out.tensor.data, ws_, ws_bytes_, GetStream()));
+  }
+  static OpEnv* make(const CallValues& cv) { return new MoeMergeMasks(cv); }
+
+ private:
+  int n_, S_, E_;
+  void* ws_ = nullptr;
+  size_t ws_bytes_ = 0;
+};
+RAF_REGISTER_DIALECT_OP(cuda, moe_merge_masks, 20);
+RAF_OP_ENV_MAKER("raf.op.cuda.moe_merge_masks", MoeMergeMasks::make);
+
+class MoeRedispatch : public OpEnv {
+ public:
+  explicit MoeRedispatch(const CallValues& cv) {
+    const Tensor& d0 = cv.args[0].fields[0].tensor;
+    n_ = (int)cv.args[0].fields.size();
+    RAF_SHIM_CHECK(cv.args[1].fields.size() == (size_t)n_, "moe_redispatch: one indices_locations per data tensor");
+    E_ = (int)d0.shape[0]; C_ = (int)d0.shape[1]; M_ = (int)d0.shape[2];
+    S_ = (int)cv.args[1].fields[0].tensor.shape[1];
+    dtype_ = LancetDType(d0.dtype);
+    arg_indices = {0, 1};
+    ws_bytes_ = lancet_moe_partition_workspace_bytes(n_, E_);
+    RequestWorkspace(&ws_, cv.device, (int64_t)ws_bytes_);
+  }
+  std::string name() const override { return "raf.op.cuda.moe_redispatch"; }
+  void Execute(const CallValues& cv) override { Execute({cv.args[0], cv.args[1]}, cv.out); }
+  void Execute(const std::vector<Value>& in, Value out) override {
+    std::vector<const void*> d;
+    std::vector<const int32_t*> il;
+    for (const Value& v : in[0].fields) d.push_back(v.tensor.data);
+    for (const Value& v : in[1].fields) il.push_back((const int32_t*)v.tensor.data);
+    Ok(lancet_moe_redispatch(d.data(), il.data(), n_, S_, M_, C_, E_, dtype_, out.tensor.data, ws_, ws_bytes_, GetStream()));
+  }
+  static OpEnv* make(const CallValues& cv) { return new MoeRedispatch(cv); }
+
+ private:
+  int n_, S_, M_, C_, E_, dtype_;
+  void* ws_ = nullptr;
+  size_t ws_bytes_ = 0;
+};
+RAF_REGISTER_DIALECT_OP(cuda, moe_redispatch, 20);
+RAF_OP_ENV_MAKER("raf.op.cuda.moe_redispatch", MoeRedispatch::make);
+
+// moe_redispatch_expert_input(data, recv_cnts, local_expert_id, n_local_experts, recv_cnts_scale): def_schema.py:670-684
+class MoeRedispatchExpertInput : public OpEnv {
+ public:
+  explicit MoeRedispatchExpertInput(const CallValues& cv) {
+    const Tensor& d0 = cv.args[0].fields[0].tensor;
+    n_ = (int)cv.args[0].fields.size();
+    RAF_SHIM_CHECK(cv.args[1].fields.size() == (size_t)n_, "moe_redispatch_expert_input: one recv_cnts per data tensor");
+    C_ = (int)d0.shape[0]; G_ = (int)d0.shape[1]; M_ = (int)d0.shape[2];
+    le_ = (int)cv.args.at(2).i; LE_ = (int)cv.args.at(3).i;
+    scale_ = cv.args.size() > 4 ? (int)cv.args[4].i : 1;
+    dtype_ = LancetDType(d0.dtype);
+    arg_indices = {0, 1};
+  }
+  std::string name() const override { return "raf.op.cuda.moe_redispatch_expert_input"; }
+  void Execute(const CallValues& cv) override { Execute({cv.args[0], cv.args[1]}, cv.out); }
+  void Execute(const std::vector<Value>& in, Value out) override {
+    std::vector<const void*> d;
+    std::vector<const uint64_t*> rc;
+    for (const Value& v : in[0].fields) d.push_back(v.tensor.data);
+    for (const Value& v : in[1].fields) rc.push_back((const uint64_t*)v.tensor.data);
+    Ok(lancet_moe_redispatch_expert_input(d.data(), rc.data(), n_, le_, LE_, C_, G_, M_, scale_, dtype_, out.tensor.data, GetStream()));
+  }
+  static OpEnv* make(const CallValues& cv) { return new MoeRedispatchExpertInput(cv); }
+
+ private:
+  int n_, C_, G_, M_, le_, LE_, scale_, dtype_;
+};
+RAF_REGISTER_DIALECT_OP(cuda, moe_redispatch_expert_input, 20);
+RAF_OP_ENV_MAKER("raf.op.cuda.moe_redispatch_expert_input", MoeRedispatchExpertInput::make);
 
 // lans(tensor_list = g + x + m + v, step, learning_rate, beta1, beta2, eps, bias_correction, weight_decay,
 //      grad_averaging, mode, normalize_grad): scripts/src_codegen/def_schema.py:726-742, cuda/lans.cc:26-177

@@ -31,7 +31,8 @@ def test_dialect_names_and_priorities():
     assert raf.dialect_ops("raf.op._all_to_all") == [("raf.op.nccl._all_to_all", "10")]
     assert raf.dialect_ops("raf.op.lans") == [("raf.op.cuda.lans", "20")]
     assert raf.dialect_ops("raf.op.matmul_nt") == [("raf.op.cublas.matmul_nt", "15")]
-    for op in ("moe_decode", "moe_encode_dx", "moe_encode_dg", "moe_decode_dx", "moe_decode_dg"):
+    for op in ("moe_decode", "moe_encode_dx", "moe_encode_dg", "moe_decode_dx", "moe_decode_dg",
+               "moe_encode_batch_prioritized", "moe_merge_masks", "moe_redispatch", "moe_redispatch_expert_input"):
         assert raf.dialect_ops("raf.op." + op) == [("raf.op.cuda." + op, "20")]
 
 
@@ -49,6 +50,10 @@ def test_declarations():
     assert raf.declare("raf.op.moe_encode_dg", torch.zeros(2048), il, 8) == [((2048, 8), torch.float32)]
     assert raf.declare("raf.op.moe_decode_dx", x, torch.zeros(2048), il, 8, 256) == [((8, 256, 512), torch.float32)]
     assert raf.declare("raf.op._all_to_all", [torch.zeros(4, 6)]) == [((4, 6), torch.float32)]
+    outs = raf.declare("raf.op.moe_encode_batch_prioritized", x, gate, 4, 1, 4.0)
+    assert outs[1] == ((2, 512), torch.int32) and outs[4] == ((8, 256, 512), torch.float32)
+    assert raf.declare("raf.op.moe_merge_masks", [il, il, il], 8) == [((2, 3 * 2048), torch.int32)]
+    assert raf.declare("raf.op.moe_redispatch", [torch.zeros(8, 16, 4).half()] * 2, [il, il]) == [((8, 16, 4), torch.float16)]
     with pytest.raises(raf.RafError, match="matching shape in dim 0"):
         raf.declare("raf.op.moe_encode", x, torch.zeros(100, 8), used, 1.0)
     with pytest.raises(raf.RafError, match="no declaration"):

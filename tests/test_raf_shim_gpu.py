@@ -72,3 +72,30 @@ def test_matmul_nt_dispatch_and_decline():
     assert torch.allclose(y.float(), want, rtol=1e-2, atol=1e-2 * float(want.abs().max()))
     with pytest.raises(raf.RafError, match="declined"):       # fp32 operands: the tensor-core op declines
         raf.call("raf.op.matmul_nt", a.float(), b.float())
+
+
+def test_partitioned_graph_ops_through_registry():
+    """n chained moe_encode + moe_merge_masks + moe_redispatch, as the reference's scheduler emits them
+    (tests/python/op/cuda/test_cuda_moe.py:387-471), all through dispatch."""
+    from oracle import moe_oracle as O
+    rng = np.random.default_rng(3)
+    S, M, E, n = 1024, 16, 2, 4
+    x = rng.standard_normal((S, M)).astype(np.float32)
+    gate = rng.random((S, E), dtype=np.float32)
+    cap = torch.zeros(E, dtype=torch.int32, device=DEV)
+    ils, ds = [], []
+    for i in range(n):
+        sl = slice(i * S // n, (i + 1) * S // n)
+        (gs, il, cap, el, d), _ = raf.call("raf.op.moe_encode", cu(x[sl]), cu(gate[sl]), cap, float(n))
+        ils.append(il); ds.append(d)
+    (mil,), name = raf.call("raf.op.moe_merge_masks", ils, E)
+    assert name == "raf.op.cuda.moe_merge_masks"
+    (md,), name = raf.call("raf.op.moe_redispatch", ds, ils)
+    assert name == "raf.op.cuda.moe_redispatch"
+    np.testing.assert_array_equal(mil.cpu().numpy(), O.moe_merge_masks([t.cpu().numpy() for t in ils], E))
+    np.testing.assert_array_equal(md.cpu().numpy(), O.moe_redispatch([t.cpu().numpy() for t in ds], [t.cpu().numpy() for t in ils]))
+    want = O.moe_encode_bpr(x, gate, 2, 1, 2.0)
+    got, name = raf.call("raf.op.moe_encode_batch_prioritized", cu(x), cu(gate), 2, 1, 2.0)
+    assert name == "raf.op.cuda.moe_encode_batch_prioritized"
+    for a, b in zip(got, want):
+        np.testing.assert_array_equal(a.cpu().numpy() if a.dtype != torch.uint64 else a.cpu().view(torch.int64).numpy().astype(np.uint64), b)
