@@ -205,18 +205,49 @@ def run_moe(args):
     for i in range(max(args.warmup, 3)):
         step(i)
     sync_all()
-    # ---- timed region: K steps, device resident inputs ------------------------------------------
     kname = b"dispatch_rows_kernel" if world == 1 else b"dispatch_rows_peer_kernel"
-    L.lancet_profile_begin(kname)
-    launches0 = L.lancet_launch_count()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ev0.record()
-    for i in range(args.steps):
-        step(i)
-    ev1.record()
-    sync_all()
-    ms_total = ev0.elapsed_time(ev1)
-    launches = L.lancet_launch_count() - launches0
+    use_graph = world == 1 and not args.no_graph
+    if use_graph:
+        # the step is 5 short launches: replay it from a CUDA graph (one per input set) to cut launch gaps
+        graphs = []
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for i in range(2):
+                gph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gph, stream=side):
+                    step(i)
+                graphs.append(gph)
+        torch.cuda.current_stream().wait_stream(side)
+        launches_per_step = None
+        for i in range(4):
+            graphs[i % 2].replay()
+        sync_all()
+    # ---- timed region: K steps, device resident inputs ------------------------------------------
+    launches0 = L.lancet_launch_count()
+    if use_graph:
+        ev0.record()
+        for i in range(args.steps):
+            graphs[i % 2].replay()
+        ev1.record()
+        sync_all()
+        ms_total = ev0.elapsed_time(ev1)
+        # per-kernel durations: the same steps launched eagerly right after, bracketed by events in the library
+        L.lancet_profile_begin(kname)
+        for i in range(min(args.steps, 200)):
+            step(i)
+        sync_all()
+        launches = (L.lancet_launch_count() - launches0) // max(1, min(args.steps, 200)) * args.steps
+    else:
+        L.lancet_profile_begin(kname)
+        ev0.record()
+        for i in range(args.steps):
+            step(i)
+        ev1.record()
+        sync_all()
+        ms_total = ev0.elapsed_time(ev1)
+        launches = L.lancet_launch_count() - launches0
     k_ms, k_n = ctypes.c_double(0), ctypes.c_longlong(0)
     _capi.check(L.lancet_profile_end(ctypes.byref(k_ms), ctypes.byref(k_n)))
     if world > 1:
@@ -329,6 +360,7 @@ def run_moe(args):
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": S_TOKENS * row_bytes + S_TOKENS * E * 4,
                 "d2h_bytes_per_step": S_TOKENS * row_bytes, "steps": e2e_steps},
         "gpu_launches": int(launches), "clocks": clocks, "roofline": roof,
+        "launch_mode": "cuda graph replay (kernel durations from an eager loop of the same steps)" if use_graph else "eager",
         "step_bytes": {"dispatch_read": S_TOKENS * row_bytes, "dispatch_write": E * plan.C * row_bytes,
                        "combine_read": kept_rows * row_bytes, "combine_write": S_TOKENS * row_bytes},
     }
@@ -535,6 +567,7 @@ def _main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="moe", choices=["moe", "lans", "ffn"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-graph", action="store_true", help="launch every step eagerly instead of replaying a CUDA graph")
     ap.add_argument("--lans-layers", type=int, default=24, help="transformer layers in the LANS tensor list (24 = 196 tensors)")
     args = ap.parse_args()
     if args.impl == "reference":
