@@ -244,7 +244,9 @@ int lancet_moe_dispatch_chunked_p2p(const void* x, const void* gate, int gate_dt
                                     int32_t* idx_loc, int32_t* capused_chain, uint64_t* elems,
                                     void* const* peer_recv, void* const* peer_counts, void* ws, size_t ws_bytes,
                                     int flags, lancet_stream_t stream);
-/* As lancet_moe_combine_chunked, gathering rows from the owners' expert output buffers. */
+/* As lancet_moe_combine_chunked, gathering rows from the owners' expert output buffers.  With
+ * gates_s == NULL every kept row has weight 1: the data gradient of dispatch (moe_encode_dx,
+ * src/op/dialect/cuda/moe.cc:1108-1133) fused with the returning all-to-all. */
 int lancet_moe_combine_chunked_p2p(void* const* peer_expert_out, const void* gates_s, const int32_t* idx_loc, int S,
                                    int M, int C, int LE, int W, int rank, int k, int n_chunks, int dtype, void* out,
                                    lancet_stream_t stream);
@@ -301,10 +303,19 @@ int lancet_grouped_gemm_nn(const void* A, const void* B, void* D, const void* pr
 /* Weight gradient (the reference's dW = matmul_tn(a, dy), src/op/grad/gemm.cc:31-36), summed over the
  * source ranks of an expert: D[e] = sum over groups g with g % LE == e of A[g][:counts[g]]^T * B[g][:counts[g]];
  * A [groups][C][Mout], B [groups][C][N], D [LE][Mout][N].  Rows from counts[g] to the next multiple
- * of 64 must be zero in A or B and finite in both (the forms above leave their outputs that way;
+ * of 64 (or to C) must be zero in A or B and finite in both (the forms above leave their outputs that way;
  * dispatch zero-fills the expert input).  Mout % 128 == 0, N % 256 == 0. */
 int lancet_grouped_gemm_tn(const void* A, const void* B, void* D, int groups, int LE, int C, int Mout, int N,
                            const int32_t* counts, int dtype, int32_t* status, lancet_stream_t stream);
+/* Backward of combine fused with the exchange (moe_decode_dx + moe_decode_dg + _all_to_all of the
+ * reference, src/op/dialect/cuda/moe.cc:1345-1375, :1431-1461): for every kept choice the row
+ * gates * dout[s] is stored into the owner's d_expert_out buffer [W][LE][C][M] and
+ * dgates_s [n][k][Sp] (float32) receives <expert_out row, dout[s]>.  Rows nobody owns are left to
+ * the owner (zero-fill with lancet_moe_zero_tail and the row counts of the forward pass). */
+int lancet_moe_combine_bwd_p2p(const void* dout, const void* gates_s, const int32_t* idx_loc,
+                               void* const* peer_d_expert_out, void* const* peer_expert_out, void* dgates_s, int S,
+                               int M, int C, int LE, int W, int rank, int k, int n_chunks, int dtype,
+                               lancet_stream_t stream);
 
 /* ---- LANS optimizer ---------------------------------------------------------------------------
  * Replaces multi_tensor_lans_cuda (kernel_util.cuh:26-34; multi_tensor_lans.cu:401-450) and the

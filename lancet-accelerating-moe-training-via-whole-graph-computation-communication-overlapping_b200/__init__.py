@@ -3,6 +3,7 @@ operator surface of the reference (RAF `moe_encode`, `moe_decode`, `_all_to_all`
 from . import _capi, build, raf  # noqa: F401
 from ._capi import LancetError  # noqa: F401
 from .pipeline import ChunkedMoE  # noqa: F401
+from .layer import MoELayer  # noqa: F401
 from .collective import Communicator, SymmAllToAll  # noqa: F401
 from .dist import DistChunkedMoE, LocalFabric, ProcessFabric, tensor_from_ptr  # noqa: F401
 from .ops import (  # noqa: F401

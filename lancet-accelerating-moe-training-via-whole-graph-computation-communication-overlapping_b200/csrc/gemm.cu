@@ -101,6 +101,14 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
       : "memory");
 }
+// 3-D form for tensors viewed [groups][C][cols]: rows past C are out of bounds in their own dimension and
+// arrive as zeros instead of running into the next group.
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accum) {
@@ -304,13 +312,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
               if (!(ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, p.status, 1))) break;
               const uint32_t full = bar_full + 8 * stage;
               mbar_expect_tx(full, A_STAGE_BYTES + B_STAGE_BYTES);
-              const int row = g * p.C + rb * BK;
               const uint32_t a_dst = smem_u32(sA + stage * A_STAGE_BYTES);
               const uint32_t b_dst = smem_u32(sB + stage * B_STAGE_BYTES);
 #pragma unroll
-              for (int j = 0; j < BM / 64; ++j) tma_load_2d(a_dst + j * BOX_BYTES, &tmA, full, tl.mt * BM + j * 64, row);
+              for (int j = 0; j < BM / 64; ++j) tma_load_3d(a_dst + j * BOX_BYTES, &tmA, full, tl.mt * BM + j * 64, rb * BK, g);
 #pragma unroll
-              for (int j = 0; j < BN / 64; ++j) tma_load_2d(b_dst + j * BOX_BYTES, &tmB, full, tl.nt * BN + j * 64, row);
+              for (int j = 0; j < BN / 64; ++j) tma_load_3d(b_dst + j * BOX_BYTES, &tmB, full, tl.nt * BN + j * 64, rb * BK, g);
               if (++stage == STAGES) { stage = 0; phase ^= 1; }
             }
           }
@@ -502,6 +509,21 @@ static int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t 
   return LANCET_OK;
 }
 
+// 3-D tensor [groups][rows][cols] of 16-bit elements, box = 1 x 64 x 64, 128-byte swizzle.
+static int make_map3(CUtensorMap* map, const void* base, uint64_t groups, uint64_t rows, uint64_t cols, int dtype) {
+  EncodeTiledFn fn = encode_fn();
+  LANCET_REQUIRE(fn, LANCET_ERR_CUDA, "grouped gemm: the driver does not provide cuTensorMapEncodeTiled");
+  cuuint64_t dims[3] = {cols, rows, groups};
+  cuuint64_t strides[2] = {cols * 2, rows * cols * 2};
+  cuuint32_t box[3] = {(cuuint32_t)BK, 64, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, dtype == LANCET_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+                  const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  LANCET_REQUIRE(r == CUDA_SUCCESS, LANCET_ERR_CUDA, "grouped gemm: cuTensorMapEncodeTiled (3-D) failed with code %d", (int)r);
+  return LANCET_OK;
+}
+
 template <typename T, int MODE, bool B_MN, int EPI>
 static int launch_t(const CUtensorMap& tmA, const CUtensorMap& tmB, const Params& p, const char* name, cudaStream_t st) {
   static bool attr_set = false;
@@ -617,9 +639,12 @@ int lancet_grouped_gemm_tn(const void* A, const void* B, void* D, int groups, in
   p.total_tiles = p.tiles_per_group * LE;
   p.counts = counts; p.bias = nullptr; p.D = D; p.preact = nullptr; p.act = 0; p.epi = EPI_ACT; p.status = status;
   CUtensorMap tmA, tmB;
-  const uint64_t rows = (uint64_t)groups * (C > 0 ? C : 1);
-  if (int rc = make_map(&tmA, A, rows, (uint64_t)Mout, 64, dtype)) return rc;
-  if (int rc = make_map(&tmB, B, rows, (uint64_t)N, 64, dtype)) return rc;
+  if (C == 0) {
+    LANCET_CUDA(cudaMemsetAsync(D, 0, (size_t)LE * Mout * N * 2, static_cast<cudaStream_t>(stream)));
+    return LANCET_OK;
+  }
+  if (int rc = make_map3(&tmA, A, (uint64_t)groups, (uint64_t)C, (uint64_t)Mout, dtype)) return rc;
+  if (int rc = make_map3(&tmB, B, (uint64_t)groups, (uint64_t)C, (uint64_t)N, dtype)) return rc;
   return launch<MODE_REDUCE, true, EPI_ACT>(tmA, tmB, p, dtype, "grouped_gemm_tn_kernel", static_cast<cudaStream_t>(stream));
 }
 }

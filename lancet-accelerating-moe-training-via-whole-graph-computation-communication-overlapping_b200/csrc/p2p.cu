@@ -124,7 +124,7 @@ combine_rows_peer_kernel(const float* __restrict__ gates, const int32_t* __restr
         srow[j] = reinterpret_cast<const P*>(static_cast<const T*>(eo.ptr[owner]) +
                                              ((size_t)(my_rank * LE + le) * C + loc) * M);
       }
-      g[j] = gates[il_index_p2p((int)s, Sp, K, j)];
+      g[j] = gates ? gates[il_index_p2p((int)s, Sp, K, j)] : 1.0f;
     }
     P* dst = reinterpret_cast<P*>(out + (size_t)s * M);
     for (int base = 0; base < row_vecs; base += 32 * U) {
@@ -159,6 +159,67 @@ combine_rows_peer_kernel(const float* __restrict__ gates, const int32_t* __restr
         for (int i = 0; i < N; ++i) o.v[i] = Num<T>::from_f(acc[i]);
         dst[v] = o;
       }
+    }
+  }
+}
+
+
+// Backward of combine, fused with the exchange.  Per token s and choice j kept at (owner, row):
+//   d_expert_out[owner][row] = gates[j,s] * dout[s]      (peer store: the transpose of the forward gather)
+//   dgates[j,s]             = <expert_out[owner][row], dout[s]>   (peer load, fp32 accumulation)
+// One warp per token; the row of dout is read once and used for both.
+template <typename T, int N, int K>
+__global__ void __launch_bounds__(kP2PThreads)
+combine_bwd_peer_kernel(const float* __restrict__ gates, const int32_t* __restrict__ idx_loc, const T* __restrict__ dout,
+                        PeerTable d_eo, PeerTable eo, float* __restrict__ dgates, int S, int Sp, int M, int C, int E, int LE,
+                        int my_rank) {
+  using P = PackP<T, N>;
+  const int lane = threadIdx.x & 31;
+  const int row_vecs = M / N;
+  const long long gw = (long long)blockIdx.x * kP2PWarps + (threadIdx.x >> 5);
+  const long long nwarps = (long long)gridDim.x * kP2PWarps;
+  for (long long s = gw; s < S; s += nwarps) {
+    P* drow[K];
+    const P* erow[K];
+    float g[K], dot[K];
+#pragma unroll
+    for (int j = 0; j < K; ++j) {
+      const int idx = idx_loc[il_index_p2p((int)s, Sp, 2 * K, 2 * j)];
+      const int loc = idx_loc[il_index_p2p((int)s, Sp, 2 * K, 2 * j + 1)];
+      drow[j] = nullptr;
+      erow[j] = nullptr;
+      dot[j] = 0.f;
+      if (idx >= 0 && idx < E && loc >= 0 && loc < C) {
+        const int owner = idx / LE, le = idx - owner * LE;
+        const size_t off = ((size_t)(my_rank * LE + le) * C + loc) * M;
+        drow[j] = reinterpret_cast<P*>(static_cast<T*>(d_eo.ptr[owner]) + off);
+        erow[j] = reinterpret_cast<const P*>(static_cast<const T*>(eo.ptr[owner]) + off);
+      }
+      g[j] = gates[il_index_p2p((int)s, Sp, K, j)];
+    }
+    const P* src = reinterpret_cast<const P*>(dout + (size_t)s * M);
+    for (int v = lane; v < row_vecs; v += 32) {
+      const P d = src[v];
+#pragma unroll
+      for (int j = 0; j < K; ++j) {
+        if (!drow[j]) continue;
+        const P e = erow[j][v];
+        P o;
+#pragma unroll
+        for (int i = 0; i < N; ++i) {
+          const float dv = Num<T>::to_f(d.v[i]);
+          o.v[i] = Num<T>::from_f(__fmul_rn(g[j], dv));
+          dot[j] = fmaf(Num<T>::to_f(e.v[i]), dv, dot[j]);
+        }
+        drow[j][v] = o;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < K; ++j) {
+      float t = dot[j];
+#pragma unroll
+      for (int d = 16; d > 0; d >>= 1) t += __shfl_xor_sync(0xffffffffu, t, d);
+      if (lane == 0) dgates[il_index_p2p((int)s, Sp, K, j)] = t;
     }
   }
 }
@@ -215,6 +276,21 @@ static int combine_p2p_t(const float* gates, const int32_t* idx_loc, const PeerT
   return launch_status("combine_rows_peer_kernel");
 }
 
+
+template <typename T>
+static int combine_bwd_p2p_t(const float* gates, const int32_t* idx_loc, const void* dout, const PeerTable& td,
+                             const PeerTable& te, float* dgates, int S, int Sp, int M, int C, int E, int LE, int rank, int k,
+                             cudaStream_t st) {
+  constexpr int N = 16 / sizeof(T);
+  ProfScope prof("combine_bwd_peer_kernel", st);
+  if (k == 1)
+    combine_bwd_peer_kernel<T, N, 1><<<p2p_grid(S), kP2PThreads, 0, st>>>(gates, idx_loc, static_cast<const T*>(dout), td, te,
+                                                                        dgates, S, Sp, M, C, E, LE, rank);
+  else
+    combine_bwd_peer_kernel<T, N, 2><<<p2p_grid(S), kP2PThreads, 0, st>>>(gates, idx_loc, static_cast<const T*>(dout), td, te,
+                                                                        dgates, S, Sp, M, C, E, LE, rank);
+  return launch_status("combine_bwd_peer_kernel");
+}
 }  // namespace lancet
 
 extern "C" {
@@ -343,8 +419,7 @@ int lancet_moe_combine_chunked_p2p(void* const* peer_expert_out, const void* gat
   LANCET_REQUIRE((k == 1 || k == 2) && M >= 0 && C >= 0 && valid_dtype(dtype), LANCET_ERR_INVALID,
                  "lancet_moe_combine_chunked_p2p: bad k=%d, M=%d, C=%d or dtype", k, M, C);
   if (S == 0 || M == 0) return LANCET_OK;
-  LANCET_REQUIRE(peer_expert_out && gates_s && idx_loc && out, LANCET_ERR_NULL,
-                 "lancet_moe_combine_chunked_p2p: null pointer argument");
+  LANCET_REQUIRE(peer_expert_out && idx_loc && out, LANCET_ERR_NULL, "lancet_moe_combine_chunked_p2p: null pointer argument");
   LANCET_REQUIRE(((size_t)M * dtype_bytes(dtype)) % 16 == 0 && aligned(out, 16), LANCET_ERR_INVALID,
                  "lancet_moe_combine_chunked_p2p: rows must be a multiple of 16 bytes and 16-byte aligned");
   PeerTable t;
@@ -357,5 +432,36 @@ int lancet_moe_combine_chunked_p2p(void* const* peer_expert_out, const void* gat
   if (dtype == LANCET_F32) return combine_p2p_t<float>(g, idx_loc, t, out, S, Sp, M, C, E, LE, rank, k, st);
   if (dtype == LANCET_F16) return combine_p2p_t<__half>(g, idx_loc, t, out, S, Sp, M, C, E, LE, rank, k, st);
   return combine_p2p_t<__nv_bfloat16>(g, idx_loc, t, out, S, Sp, M, C, E, LE, rank, k, st);
+}
+
+int lancet_moe_combine_bwd_p2p(const void* dout, const void* gates_s, const int32_t* idx_loc, void* const* peer_d_expert_out,
+                               void* const* peer_expert_out, void* dgates_s, int S, int M, int C, int LE, int W, int rank, int k,
+                               int n_chunks, int dtype, lancet_stream_t stream) {
+  LANCET_REQUIRE(W >= 1 && W <= kMaxPeers && rank >= 0 && rank < W && LE >= 1, LANCET_ERR_INVALID,
+                 "lancet_moe_combine_bwd_p2p: bad world %d / rank %d / local experts %d", W, rank, LE);
+  LANCET_REQUIRE(n_chunks >= 1 && S >= 0 && S % n_chunks == 0, LANCET_ERR_INVALID,
+                 "lancet_moe_combine_bwd_p2p: S=%d is not divisible into %d chunks", S, n_chunks);
+  LANCET_REQUIRE((k == 1 || k == 2) && M >= 0 && C >= 0 && valid_dtype(dtype), LANCET_ERR_INVALID,
+                 "lancet_moe_combine_bwd_p2p: bad k=%d, M=%d, C=%d or dtype", k, M, C);
+  if (S == 0 || M == 0) return LANCET_OK;
+  LANCET_REQUIRE(dout && gates_s && idx_loc && peer_d_expert_out && peer_expert_out && dgates_s, LANCET_ERR_NULL,
+                 "lancet_moe_combine_bwd_p2p: null pointer argument");
+  LANCET_REQUIRE(((size_t)M * dtype_bytes(dtype)) % 16 == 0 && aligned(dout, 16), LANCET_ERR_INVALID,
+                 "lancet_moe_combine_bwd_p2p: rows must be a multiple of 16 bytes and 16-byte aligned");
+  PeerTable td, te;
+  for (int i = 0; i < kMaxPeers; ++i) {
+    td.ptr[i] = i < W ? peer_d_expert_out[i] : nullptr;
+    te.ptr[i] = i < W ? peer_expert_out[i] : nullptr;
+  }
+  for (int i = 0; i < W; ++i)
+    LANCET_REQUIRE(td.ptr[i] && te.ptr[i] && aligned(td.ptr[i], 16) && aligned(te.ptr[i], 16), LANCET_ERR_NULL,
+                   "lancet_moe_combine_bwd_p2p: peer buffer %d is null or unaligned", i);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int E = LE * W, Sp = S / n_chunks;
+  const float* g = static_cast<const float*>(gates_s);
+  float* dg = static_cast<float*>(dgates_s);
+  if (dtype == LANCET_F32) return combine_bwd_p2p_t<float>(g, idx_loc, dout, td, te, dg, S, Sp, M, C, E, LE, rank, k, st);
+  if (dtype == LANCET_F16) return combine_bwd_p2p_t<__half>(g, idx_loc, dout, td, te, dg, S, Sp, M, C, E, LE, rank, k, st);
+  return combine_bwd_p2p_t<__nv_bfloat16>(g, idx_loc, dout, td, te, dg, S, Sp, M, C, E, LE, rank, k, st);
 }
 }

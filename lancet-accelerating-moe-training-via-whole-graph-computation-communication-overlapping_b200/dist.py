@@ -105,7 +105,7 @@ class DistChunkedMoE:
     """Chunk-chained top-k dispatch and combine with the all-to-all fused into the kernels."""
 
     def __init__(self, S, M, k=2, capacity_factor=1.25, n_chunks=4, dtype=torch.float16, device="cuda",
-                 local_experts=2, fabric=None, group=None, timeout_s=5.0, remote_zero=False):
+                 local_experts=2, fabric=None, group=None, timeout_s=5.0, remote_zero=False, train=False):
         self.device = torch.device(device)
         self.fabric = fabric if fabric is not None else ProcessFabric(self.device, group)
         self.W, self.rank = self.fabric.world, self.fabric.rank
@@ -124,13 +124,17 @@ class DistChunkedMoE:
         self.recv_bytes = _up(self.W * self.LE * self.C * M * item)
         flag_bytes = _up(16 * 4)
         cnt_bytes = _up(self.W * self.LE * 4)
-        total = 3 * self.recv_bytes + flag_bytes + 2 * cnt_bytes
+        self.train = train
+        n_regions = 5 if train else 3            # recv x2, expert_out, and for training d_expert_out, d_expert_in
+        total = n_regions * self.recv_bytes + flag_bytes + 2 * cnt_bytes
         bases = self.fabric.alloc(total)
         mk = lambda off: (ctypes.c_void_p * 16)(*[b + off for b in bases])
         self.peer_recv = [mk(0), mk(self.recv_bytes)]
         self.peer_eo = mk(2 * self.recv_bytes)
-        self.peer_flags = mk(3 * self.recv_bytes)
-        cnt_off = 3 * self.recv_bytes + flag_bytes
+        self.peer_deo = mk(3 * self.recv_bytes) if train else None
+        self.peer_dxe = mk(4 * self.recv_bytes) if train else None
+        self.peer_flags = mk(n_regions * self.recv_bytes)
+        cnt_off = n_regions * self.recv_bytes + flag_bytes
         self.peer_counts = [mk(cnt_off), mk(cnt_off + cnt_bytes)]
         self.base = bases[self.rank]
         d = self.device
@@ -149,6 +153,11 @@ class DistChunkedMoE:
         shape = (self.W, self.LE, self.C, M)
         self.recv = [tensor_from_ptr(self.base + i * self.recv_bytes, shape, dtype, d) for i in range(2)]
         self.expert_out = tensor_from_ptr(self.base + 2 * self.recv_bytes, shape, dtype, d)
+        if train:
+            self.d_expert_out = tensor_from_ptr(self.base + 3 * self.recv_bytes, shape, dtype, d)
+            self.d_expert_in = tensor_from_ptr(self.base + 4 * self.recv_bytes, shape, dtype, d)
+            self.dgates = torch.empty((n_chunks, k, self.Sp), dtype=torch.float32, device=d)
+            self.dx = torch.empty((S, M), dtype=dtype, device=d)
         self.counts = [tensor_from_ptr(self.base + cnt_off + i * cnt_bytes, (self.W * self.LE,), torch.int32, d)
                        for i in range(2)]
         if self.fabric.real and self.W > 1:
@@ -202,6 +211,30 @@ class DistChunkedMoE:
             self.n, _DT[self.dtype], _ptr(out), _stream(out)))
         return out
 
+    # -- backward ------------------------------------------------------------------------------
+    def combine_backward_send(self, dout):
+        """Backward of combine, fused with the exchange: gate-weighted rows of dout go to the owners'
+        d_expert_out buffers, dgates = <expert output row, dout row>."""
+        check(_capi.lib().lancet_moe_combine_bwd_p2p(
+            _ptr(dout), _ptr(self.gates_s), _ptr(self.idx_loc), self.peer_deo, self.peer_eo, _ptr(self.dgates), self.S,
+            self.M, self.C, self.LE, self.W, self.rank, self.k, self.n, _DT[self.dtype], _stream(dout)))
+
+    def combine_backward_finish(self):
+        """Meet the peers, zero the rows of d_expert_out that no token owns; returns (d_expert_out, dgates)."""
+        self.barrier()
+        check(_capi.lib().lancet_moe_zero_tail(_ptr(self.d_expert_out), _ptr(self.counts[self.parity]), self.M, self.C,
+                                               self.W * self.LE, _DT[self.dtype], _stream(self.out)))
+        return self.d_expert_out, self.dgates
+
+    def dispatch_backward(self):
+        """Backward of dispatch, fused with the exchange: dx[s] = sum of the d_expert_in rows of token s,
+        gathered from their owners (the experts have written `self.d_expert_in`)."""
+        self.barrier()
+        check(_capi.lib().lancet_moe_combine_chunked_p2p(
+            self.peer_dxe, None, _ptr(self.idx_loc), self.S, self.M, self.C, self.LE, self.W, self.rank, self.k,
+            self.n, _DT[self.dtype], _ptr(self.dx), _stream(self.dx)))
+        return self.dx
+
     def check(self):
         """Raises LancetError(LANCET_ERR_TIMEOUT) if a bounded wait ran out since construction."""
         check(_capi.lib().lancet_p2p_status(_ptr(self.status), _stream(self.status)))
@@ -209,4 +242,5 @@ class DistChunkedMoE:
     def close(self):
         torch.cuda.synchronize(self.device)
         self.recv, self.expert_out, self.counts = None, None, None
+        self.d_expert_out, self.d_expert_in = None, None
         self.fabric.close()

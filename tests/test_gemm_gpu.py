@@ -128,6 +128,8 @@ def test_data_gradient_gemm(groups, LE, C, N, K, dt, act, ragged):
     (4, 2, 256, 256, 512, torch.bfloat16, False),
     (8, 2, 200, 128, 256, torch.float16, True),
     (6, 2, 1280, 1024, 512, torch.bfloat16, True),
+    (4, 2, 160, 128, 256, torch.bfloat16, False),      # C not a multiple of the 64-row reduction block
+    (4, 2, 100, 128, 256, torch.bfloat16, True),
 ])
 def test_weight_gradient_gemm(groups, LE, C, Mout, N, dt, ragged):
     g = torch.Generator(device=DEV).manual_seed(groups * 55 + C + Mout + N)
