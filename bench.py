@@ -539,6 +539,86 @@ def run_ffn(args):
     })
 
 
+def run_layer(args):
+    """Whole MoE layer, forward + backward: gate probabilities in, dispatch (+exchange), expert FFN (M=2048,
+    H=8192, GELU, 2 local experts), combine (+exchange); backward with the weight-gradient GEMMs on a side stream
+    under the returning exchange.  S=16384 tokens per GPU, top-2, capacity factor 1.25, bf16."""
+    import lancet_b200 as LB
+    from lancet_b200 import _capi
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit("bench.py: --gpus %d but WORLD_SIZE=%d" % (args.gpus, world))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    fabric = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    else:
+        fabric = LB.LocalFabric(1, 0, {})
+    H = 8192
+    xs_h, gates_h = synth_inputs(rank, world, S_TOKENS, M_DIM, torch.bfloat16)
+    xs = [x.to(dev) for x in xs_h]
+    gates = [g.to(dev) for g in gates_h]
+    dout = torch.randn((S_TOKENS, M_DIM), device=dev).bfloat16()
+    layer = LB.MoELayer(S_TOKENS, M_DIM, H, TOP_K, CAP_FACTOR, N_CHUNKS, torch.bfloat16, dev, 2, fabric=fabric, overlap_dw=True)
+    side = layer.side
+    results = {}
+
+    def step(i):
+        layer.forward(xs[i % 2], gates[i % 2])
+        layer.backward(dout)
+
+    for overlap in (True, False):
+        layer.side = side if overlap else None
+        for i in range(max(args.warmup, 3)):
+            step(i)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        for i in range(args.steps):
+            step(i)
+        ev1.record()
+        torch.cuda.synchronize()
+        ms = ev0.elapsed_time(ev1) / args.steps
+        if world > 1:
+            t = torch.tensor([ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        results[overlap] = ms
+    layer_first = layer
+    if world > 1:
+        layer.moe.check()
+    live = int(layer_first.moe.capused[-1].sum().item())
+    st = LB.gemm_status(dev)
+    _capi.check(_capi.lib().lancet_p2p_status(ctypes.c_void_p(st.data_ptr()),
+                                              ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    if world > 1:
+        dist.barrier()
+        layer_first.moe.close()
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+    ms = results[True]
+    flops = 6.0 * 2.0 * live * M_DIM * H            # per GPU: 2 GEMMs forward, 4 backward, live rows only
+    peaks, peak_kind = load_peaks()
+    sustained = float(peaks.get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops"]))
+    emit({
+        "metric": "moe_layer_tokens_per_s", "value": S_TOKENS * world / (ms / 1e3), "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "moe_layer_fwd_bwd: S=%d tokens/GPU, M=%d, H=%d, E=%d, top-%d, cf=%.2f, %d chunks" % (
+            S_TOKENS, M_DIM, H, 2 * world, TOP_K, CAP_FACTOR, N_CHUNKS), "l2": "GBs touched per step exceed the 126 MB L2"},
+        "tflops_per_gpu": flops / (ms / 1e3) / 1e12, "tensor_frac": flops / (ms / 1e3) / 1e12 / sustained,
+        "peak_kind": peak_kind + " (sustained cuBLAS bf16)", "live_rows_rank0": live,
+        "dw_overlap": {"ms_with_side_stream": results[True], "ms_single_stream": results[False]},
+    })
+
+
 def main():
     # libraries (NCCL, torchrun) may write to stdout; keep it clean for the one JSON line
     saved_stdout = os.dup(1)
@@ -565,7 +645,7 @@ def _main():
     ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="moe", choices=["moe", "lans", "ffn"])
+    ap.add_argument("--workload", default="moe", choices=["moe", "lans", "ffn", "layer"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-graph", action="store_true", help="launch every step eagerly instead of replaying a CUDA graph")
     ap.add_argument("--lans-layers", type=int, default=24, help="transformer layers in the LANS tensor list (24 = 196 tensors)")
@@ -579,6 +659,8 @@ def _main():
         run_lans(args)
     elif args.workload == "ffn":
         run_ffn(args)
+    elif args.workload == "layer":
+        run_layer(args)
     else:
         run_moe(args)
 
