@@ -15,7 +15,7 @@
 // One persistent CTA per SM walks a static list of 128 x 256 output tiles.  Warp 0 is the TMA
 // producer (cp.async.bulk.tensor into 128-byte-swizzled shared memory, 4 stages of 64-wide K
 // blocks), warp 1 issues tcgen05.mma (one thread) into one of two 256-column TMEM accumulators,
-// warps 2-5 are the epilogue (tcgen05.ld, bias + activation, 16-byte stores), so the epilogue of
+// warps 2-9 are the epilogue (tcgen05.ld, bias + activation, 16-byte stores; two warps per TMEM lane quadrant), so the epilogue of
 // tile i overlaps the main loop of tile i+1.  Every mbarrier wait is bounded: when a limit runs
 // out the CTA raises an abort flag, records the site in *status, lets copies in flight land, frees
 // its TMEM and returns.
@@ -32,7 +32,8 @@ constexpr int A_STAGE_BYTES = BM * BK * 2;   // 16 KB
 constexpr int B_STAGE_BYTES = BN * BK * 2;   // 32 KB
 constexpr int SMEM_DATA = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES);
 constexpr int SMEM_BYTES = SMEM_DATA + 1024 /*alignment slack*/ + 256 /*barriers*/;
-constexpr int THREADS = 192;                 // warps: 0 TMA, 1 MMA, 2..5 epilogue
+constexpr int EPI_WARPS = 8;                 // two warps per TMEM lane quadrant, each takes half of the columns
+constexpr int THREADS = 64 + 32 * EPI_WARPS; // warps: 0 TMA, 1 MMA, 2.. epilogue
 constexpr int TMEM_COLS = 512;               // two accumulators of BN fp32 columns
 constexpr int BAND = 16;                     // m-tiles per band (L2 reuse of A against a sweep of B)
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
@@ -262,7 +263,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar_tfull + 8 * b, 1);
-      mbar_init(bar_tempty + 8 * b, 4);
+      mbar_init(bar_tempty + 8 * b, EPI_WARPS);
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -364,8 +365,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
     }
   } else {
-    // ---------------- epilogue: warps 2..5, TMEM lane quadrant = warp % 4 ----------------
+    // ---------------- epilogue: warps 2.., TMEM lane quadrant = warp % 4, column half = (warp - 2) / 4 ----------------
     const int quad = warp & 3;
+    const int c_begin = ((warp - 2) >> 2) * (BN / 32 / (EPI_WARPS / 4));
+    const int c_end = c_begin + BN / 32 / (EPI_WARPS / 4);
     int buf = 0;
     uint32_t tphase[2] = {0, 0};
     bool ok = true;
@@ -399,7 +402,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         e = tl.group;
       }
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = c_begin; c < c_end; ++c) {
         uint32_t r[32];
         tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(buf * BN + c * 32), r);
         if (MODE == MODE_REDUCE) {
