@@ -590,16 +590,15 @@ def run_layer(args):
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms = float(t.item())
         results[overlap] = ms
-    layer_first = layer
     if world > 1:
         layer.moe.check()
-    live = int(layer_first.moe.capused[-1].sum().item())
+    live = int(layer.moe.capused[-1].sum().item())
     st = LB.gemm_status(dev)
     _capi.check(_capi.lib().lancet_p2p_status(ctypes.c_void_p(st.data_ptr()),
                                               ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
     if world > 1:
         dist.barrier()
-        layer_first.moe.close()
+        layer.moe.close()
         dist.destroy_process_group()
     if rank != 0:
         return
