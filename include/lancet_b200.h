@@ -265,6 +265,11 @@ int lancet_all_to_all(const void* send, void* recv, size_t bytes_per_rank, lance
  * the reference's message when it does not divide (nccl.cc:213). */
 int lancet_all_to_all_evenly(const void* send, void* recv, size_t total_bytes, lancet_comm_t comm,
                              lancet_stream_t stream);
+/* Tuple form of `_all_to_all` (nccl.cc:228-277): n_tensors (at most 16) tensors of nbytes[i] bytes are
+ * exchanged in ONE grouped all-to-all: a kernel packs the per-rank slices into in_ws, the result lands in
+ * out_ws and a kernel unpacks it into recvs[i].  in_ws and out_ws: sum(nbytes) bytes each. */
+int lancet_all_to_all_tuple(const void* const* sends, void* const* recvs, const size_t* nbytes, int n_tensors,
+                            void* in_ws, void* out_ws, size_t ws_bytes, lancet_comm_t comm, lancet_stream_t stream);
 /* Peer-memory transport for receive buffers in symmetric memory: one kernel stores chunk i of
  * `send` into block `rank` of peer_recv[i].  Follow with lancet_p2p_barrier before reading. */
 int lancet_all_to_all_p2p(const void* send, void* const* peer_recv, size_t bytes_per_rank, int W, int rank,

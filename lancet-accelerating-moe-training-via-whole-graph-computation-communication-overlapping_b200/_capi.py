@@ -93,6 +93,8 @@ SIGNATURES = {
                                        c_int, c_int, c_void_p, c_void_p]),
     "lancet_grouped_gemm_tn": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int,
                                        c_void_p, c_void_p]),
+    "lancet_all_to_all_tuple": (c_int, [ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), ctypes.POINTER(c_size_t), c_int,
+                                        c_void_p, c_void_p, c_size_t, c_void_p, c_void_p]),
     "lancet_all_to_all_evenly": (c_int, [c_void_p, c_void_p, c_size_t, c_void_p, c_void_p]),
     "lancet_raf_last_error": (ctypes.c_char_p, []),
     "lancet_raf_declare": (c_int, [ctypes.c_char_p, ctypes.POINTER(RafValue), c_int, ctypes.POINTER(RafValue), c_int,

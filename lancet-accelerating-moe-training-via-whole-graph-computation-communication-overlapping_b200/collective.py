@@ -41,6 +41,20 @@ class Communicator:
         check(_capi.lib().lancet_all_to_all(_ptr(x), _ptr(out), nbytes // self.world, self.handle, _stream(x)))
         return out
 
+    def all_to_all_tuple(self, xs):
+        """`_all_to_all` of a tuple of tensors in one grouped exchange; returns the list of outputs."""
+        outs = [torch.empty_like(x) for x in xs]
+        n = len(xs)
+        sizes = [x.numel() * x.element_size() for x in xs]
+        total = sum(sizes)
+        ws = torch.empty(2 * max(total, 1), dtype=torch.uint8, device=xs[0].device)
+        send = (ctypes.c_void_p * n)(*[x.data_ptr() for x in xs])
+        recv = (ctypes.c_void_p * n)(*[o.data_ptr() for o in outs])
+        nb = (ctypes.c_size_t * n)(*sizes)
+        check(_capi.lib().lancet_all_to_all_tuple(send, recv, nb, n, _ptr(ws), ctypes.c_void_p(ws.data_ptr() + total),
+                                                  total, self.handle, _stream(xs[0])))
+        return outs
+
     def close(self):
         if self.handle:
             _capi.lib().lancet_comm_destroy(self.handle)

@@ -198,6 +198,73 @@ int lancet_all_to_all_evenly(const void* send, void* recv, size_t total_bytes, l
   return lancet_all_to_all(send, recv, total_bytes / W, comm, stream);
 }
 
+// Tuple form (nccl.cc:228-277 of the reference): the per-rank slices of all tensors are packed next to each
+// other into `in_ws`, exchanged in one grouped all-to-all into `out_ws` and unpacked.  The reference issues
+// 2*W*n_tensors cudaMemcpyAsync calls for the packing; here one kernel launch packs and one unpacks.
+struct TupleTable {
+  const void* src[16];
+  void* dst[16];
+  unsigned long long bytes_per_rank[16];
+  unsigned long long offset[16];  // offset of tensor t inside a rank's packed block
+  unsigned long long block;       // packed bytes per rank
+};
+
+__global__ void __launch_bounds__(256) a2a_pack_kernel(TupleTable t, unsigned char* __restrict__ ws, int pack) {
+  const int tensor = blockIdx.y, rank = blockIdx.z;
+  const unsigned long long n = t.bytes_per_rank[tensor];
+  unsigned char* packed = ws + (unsigned long long)rank * t.block + t.offset[tensor];
+  const unsigned long long stride = (unsigned long long)gridDim.x * blockDim.x;
+  const unsigned long long tid = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (pack) {
+    const unsigned char* s = static_cast<const unsigned char*>(t.src[tensor]) + (unsigned long long)rank * n;
+    if ((n & 15) == 0 && ((reinterpret_cast<uintptr_t>(s) | reinterpret_cast<uintptr_t>(packed)) & 15) == 0) {
+      for (unsigned long long i = tid; i < n / 16; i += stride) reinterpret_cast<uint4*>(packed)[i] = reinterpret_cast<const uint4*>(s)[i];
+    } else {
+      for (unsigned long long i = tid; i < n; i += stride) packed[i] = s[i];
+    }
+  } else {
+    unsigned char* d = static_cast<unsigned char*>(t.dst[tensor]) + (unsigned long long)rank * n;
+    if ((n & 15) == 0 && ((reinterpret_cast<uintptr_t>(d) | reinterpret_cast<uintptr_t>(packed)) & 15) == 0) {
+      for (unsigned long long i = tid; i < n / 16; i += stride) reinterpret_cast<uint4*>(d)[i] = reinterpret_cast<const uint4*>(packed)[i];
+    } else {
+      for (unsigned long long i = tid; i < n; i += stride) d[i] = packed[i];
+    }
+  }
+}
+
+int lancet_all_to_all_tuple(const void* const* sends, void* const* recvs, const size_t* nbytes, int n_tensors, void* in_ws,
+                            void* out_ws, size_t ws_bytes, lancet_comm_t comm, lancet_stream_t stream) {
+  LANCET_REQUIRE(n_tensors >= 1 && n_tensors <= 16, LANCET_ERR_INVALID, "lancet_all_to_all_tuple: 1 to 16 tensors, got %d", n_tensors);
+  LANCET_REQUIRE(sends && recvs && nbytes && in_ws && out_ws && comm, LANCET_ERR_NULL, "lancet_all_to_all_tuple: null argument");
+  LANCET_REQUIRE(nccl().ok, LANCET_ERR_COMM, "NCCL (libnccl.so.2) could not be loaded");
+  int W = 0;
+  LANCET_NCCL(nccl().CommCount(static_cast<ncclComm_t>(comm), &W));
+  TupleTable t;
+  size_t total = 0, block = 0;
+  for (int i = 0; i < n_tensors; ++i) {
+    LANCET_REQUIRE(sends[i] && recvs[i], LANCET_ERR_NULL, "lancet_all_to_all_tuple: tensor %d is null", i);
+    LANCET_REQUIRE(nbytes[i] % (size_t)W == 0, LANCET_ERR_INVALID,
+                   "Cannot evenly distribute input tensor to all ranks (tensor %d: %zu bytes over %d ranks).", i, nbytes[i], W);
+    t.src[i] = sends[i];
+    t.dst[i] = recvs[i];
+    t.bytes_per_rank[i] = nbytes[i] / W;
+    t.offset[i] = block;
+    block += nbytes[i] / W;
+    total += nbytes[i];
+  }
+  t.block = block;
+  LANCET_REQUIRE(ws_bytes >= total, LANCET_ERR_INVALID, "lancet_all_to_all_tuple: workspaces of %zu bytes are smaller than the %zu needed",
+                 ws_bytes, total);
+  if (total == 0) return LANCET_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int bx = sm_count() * 4 / (n_tensors * W) + 1;
+  a2a_pack_kernel<<<dim3(bx, n_tensors, W), 256, 0, st>>>(t, static_cast<unsigned char*>(in_ws), 1);
+  if (int rc = launch_status("a2a_pack_kernel")) return rc;
+  if (int rc = lancet_all_to_all(in_ws, out_ws, block, comm, stream)) return rc;
+  a2a_pack_kernel<<<dim3(bx, n_tensors, W), 256, 0, st>>>(t, static_cast<unsigned char*>(out_ws), 0);
+  return launch_status("a2a_pack_kernel");
+}
+
 int lancet_all_to_all_p2p(const void* send, void* const* peer_recv, size_t bytes_per_rank, int W, int rank,
                           lancet_stream_t stream) {
   LANCET_REQUIRE(W >= 1 && W <= kMaxPeersA2A && rank >= 0 && rank < W, LANCET_ERR_INVALID,

@@ -533,30 +533,50 @@ class LansImpl : public OpEnv {
 RAF_REGISTER_DIALECT_OP(cuda, lans, 20);
 RAF_OP_ENV_MAKER("raf.op.cuda.lans", LansImpl::make);
 
-// _all_to_all over NCCL, single tensor (the tuple form of nccl.cc:228-277 is declined)
+// _all_to_all over NCCL: one tensor directly, a tuple through pack / one exchange / unpack (nccl.cc:195-277)
 class NCCLAllToAll : public OpEnv {
  public:
   explicit NCCLAllToAll(const CallValues& cv) {
     arg_indices = {0};
     RequestStream(&stream_, cv.device, kCudaCommunicate);
     RequestDistributed(&communicator_);
-    total_bytes_ = (size_t)cv.args[0].fields[0].tensor.nbytes();
+    for (const Value& v : cv.args[0].fields) {
+      sizes_.push_back((size_t)v.tensor.nbytes());
+      total_bytes_ += (size_t)v.tensor.nbytes();
+    }
+    if (sizes_.size() > 1) {
+      RequestWorkspace(&in_ws_, cv.device, (int64_t)total_bytes_);
+      RequestWorkspace(&out_ws_, cv.device, (int64_t)total_bytes_);
+    }
   }
   std::string name() const override { return "raf.op.nccl._all_to_all"; }
   void Execute(const CallValues& cv) override { Execute({cv.args[0]}, cv.out); }
   void Execute(const std::vector<Value>& in, Value out) override {
     RAF_SHIM_CHECK(communicator_ != nullptr, "_all_to_all: no communicator (RequestDistributed was not satisfied)");
-    // the world size is the communicator's; the split must be even (nccl.cc:213)
-    Ok(lancet_all_to_all_evenly(in[0].fields[0].tensor.data, out.tensor.data, total_bytes_, communicator_, stream_));
+    if (sizes_.size() == 1) {
+      // the world size is the communicator's; the split must be even (nccl.cc:213)
+      Ok(lancet_all_to_all_evenly(in[0].fields[0].tensor.data, out.tensor.data, total_bytes_, communicator_, stream_));
+      return;
+    }
+    std::vector<const void*> s;
+    std::vector<void*> r;
+    for (const Value& v : in[0].fields) s.push_back(v.tensor.data);
+    for (const Value& v : out.fields) r.push_back(v.tensor.data);
+    Ok(lancet_all_to_all_tuple(s.data(), r.data(), sizes_.data(), (int)sizes_.size(), in_ws_, out_ws_, total_bytes_, communicator_,
+                               stream_));
   }
   static OpEnv* make(const CallValues& cv) {
-    if (cv.args.empty() || cv.args[0].kind != Value::kTuple || cv.args[0].fields.size() != 1) return nullptr;
+    if (cv.args.empty() || cv.args[0].kind != Value::kTuple || cv.args[0].fields.empty() || cv.args[0].fields.size() > 16)
+      return nullptr;
     return new NCCLAllToAll(cv);
   }
 
  private:
   void* stream_ = nullptr;
   void* communicator_ = nullptr;
+  void* in_ws_ = nullptr;
+  void* out_ws_ = nullptr;
+  std::vector<size_t> sizes_;
   size_t total_bytes_ = 0;
 };
 RAF_REGISTER_DIALECT_OP(nccl, _all_to_all, 10);

@@ -50,6 +50,13 @@ def main():
     back = comm.all_to_all(comm.all_to_all(big))
     torch.cuda.synchronize()
     assert torch.equal(back, big)
+    # tuple form: three tensors of different types in one grouped exchange == three single exchanges
+    tup = [big, torch.arange(world * 6, device=dev, dtype=torch.int32).view(world, 6) + 100 * rank,
+           torch.randn(world * 10, device=dev).half()]
+    got_t = comm.all_to_all_tuple(tup)
+    torch.cuda.synchronize()
+    for a, x in zip(got_t, tup):
+        assert torch.equal(a, comm.all_to_all(x))
     # the same exchange over peer memory, and the count-aware variant
     sa = LB.SymmAllToAll(big.numel() * 4, dev, n_chunks=2)
     got = sa.all_to_all(big)
