@@ -618,6 +618,68 @@ def run_layer(args):
     })
 
 
+def run_a2a(args):
+    """Stand-alone `_all_to_all` of the [E,C,M] expert buffer of the MoE workload (160 MiB per GPU): NCCL grouped
+    send/recv exactly as the reference issues it, and the peer-memory store kernel + flag barrier."""
+    import lancet_b200 as LB
+    import torch.distributed as dist
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus or world < 2:
+        raise SystemExit("bench.py --workload a2a needs --gpus N >= 2 under torch.distributed.run")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist.init_process_group("nccl", device_id=dev)
+    E = 2 * world
+    C = LB.moe_capacity(S_TOKENS // N_CHUNKS, E, CAP_FACTOR * N_CHUNKS, TOP_K)
+    x = torch.randn((E, C, M_DIM), device=dev).half()
+    nbytes = x.numel() * 2
+    comm = LB.Communicator(dev)
+    sa = LB.SymmAllToAll(nbytes, dev)
+    res = {}
+
+    def timed(fn):
+        for _ in range(max(args.warmup, 3)):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        for _ in range(args.steps):
+            fn()
+        ev1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([ev0.elapsed_time(ev1) / args.steps], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    out = torch.empty_like(x)
+    res["nccl"] = timed(lambda: comm.all_to_all(x, out=out))
+    res["peer"] = timed(lambda: sa.all_to_all(x))
+    ok = bool(torch.equal(sa.recv_view(x), comm.all_to_all(x)))
+    sa.check()
+    comm.close()
+    dist.barrier()
+    sa.close()
+    dist.destroy_process_group()
+    if rank != 0:
+        return
+    link_bytes = nbytes * (world - 1) / world          # bytes that leave each GPU per call
+    emit({
+        "metric": "all_to_all_bus_gb_per_s", "value": link_bytes / (res["peer"] / 1e3) / 1e9, "unit": "GB/s per direction per GPU",
+        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": res["peer"],
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
+        "config": {"workload": "all_to_all of the [E,C,M] fp16 expert buffer, %d bytes per GPU" % nbytes},
+        "peer_memory": {"ms": res["peer"], "gb_per_s": link_bytes / (res["peer"] / 1e3) / 1e9},
+        "nccl_grouped_send_recv": {"ms": res["nccl"], "gb_per_s": link_bytes / (res["nccl"] / 1e3) / 1e9},
+        "results_identical": ok,
+        "roofline": {"bound": "nvlink", "kernel": "a2a_store_kernel", "achieved": link_bytes / (res["peer"] / 1e3) / 1e9,
+                     "peak": 770.0, "unit": "GB/s", "frac": link_bytes / (res["peer"] / 1e3) / 1e9 / 770.0,
+                     "peak_kind": "measured peer copy, per direction", "traffic": None},
+    })
+
+
 def main():
     # libraries (NCCL, torchrun) may write to stdout; keep it clean for the one JSON line
     saved_stdout = os.dup(1)
@@ -644,7 +706,7 @@ def _main():
     ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="moe", choices=["moe", "lans", "ffn", "layer"])
+    ap.add_argument("--workload", default="moe", choices=["moe", "lans", "ffn", "layer", "a2a"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-graph", action="store_true", help="launch every step eagerly instead of replaying a CUDA graph")
     ap.add_argument("--lans-layers", type=int, default=24, help="transformer layers in the LANS tensor list (24 = 196 tensors)")
@@ -660,6 +722,8 @@ def _main():
         run_ffn(args)
     elif args.workload == "layer":
         run_layer(args)
+    elif args.workload == "a2a":
+        run_a2a(args)
     else:
         run_moe(args)
 
