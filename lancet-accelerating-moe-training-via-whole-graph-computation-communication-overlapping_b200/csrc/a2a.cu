@@ -75,20 +75,34 @@ struct PeerTableA {
   void* ptr[kMaxPeersA2A];
 };
 
-// Copy chunk `dst` of my send buffer into block `my_rank` of rank dst's receive buffer.
-// grid.y = destination rank; 16-byte accesses.
+// Copy chunk `dst` of my send buffer into block `my_rank` of rank dst's receive buffer.  A warp moves 4 KB
+// pieces (8 independent 16-byte loads per lane, then 8 stores, like the fused dispatch kernel); consecutive
+// pieces go to different destinations so that all links are busy all the time.
 __global__ void __launch_bounds__(256)
-a2a_store_kernel(const uint4* __restrict__ send, PeerTableA recv, size_t vecs_per_rank, int my_rank) {
-  const int dst = blockIdx.y;
-  const uint4* s = send + (size_t)dst * vecs_per_rank;
-  uint4* d = static_cast<uint4*>(recv.ptr[dst]) + (size_t)my_rank * vecs_per_rank;
-  const size_t stride = (size_t)gridDim.x * blockDim.x;
-  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  for (; i + 3 * stride < vecs_per_rank; i += 4 * stride) {
-    const uint4 a = __ldcs(s + i), b = __ldcs(s + i + stride), c = __ldcs(s + i + 2 * stride), e = __ldcs(s + i + 3 * stride);
-    d[i] = a; d[i + stride] = b; d[i + 2 * stride] = c; d[i + 3 * stride] = e;
+a2a_store_kernel(const uint4* __restrict__ send, PeerTableA recv, size_t vecs_per_rank, int W, int my_rank) {
+  constexpr int U = 8;
+  const int lane = threadIdx.x & 31;
+  const size_t pieces_per_rank = (vecs_per_rank + 32 * U - 1) / (32 * U);
+  const size_t tasks = pieces_per_rank * W;
+  const size_t gw = (size_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const size_t nw = (size_t)gridDim.x * 8;
+  for (size_t t = gw; t < tasks; t += nw) {
+    const int dst = (int)((t + my_rank) % W);          // start at a different peer on every rank
+    const size_t base = (t / W) * (32 * U);
+    const uint4* s = send + (size_t)dst * vecs_per_rank + base;
+    uint4* d = static_cast<uint4*>(recv.ptr[dst]) + (size_t)my_rank * vecs_per_rank + base;
+    uint4 r[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const size_t v = (size_t)u * 32 + lane;
+      if (base + v < vecs_per_rank) r[u] = __ldcs(s + v);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const size_t v = (size_t)u * 32 + lane;
+      if (base + v < vecs_per_rank) d[v] = r[u];
+    }
   }
-  for (; i < vecs_per_rank; i += stride) d[i] = __ldcs(s + i);
 }
 
 // Count-aware variant: for destination dst and chunk j only the first send_counts[dst*n_chunks+j]
@@ -278,13 +292,13 @@ int lancet_all_to_all_p2p(const void* send, void* const* peer_recv, size_t bytes
   for (int i = 0; i < W; ++i)
     LANCET_REQUIRE(t.ptr[i] && aligned(t.ptr[i], 16), LANCET_ERR_NULL, "lancet_all_to_all_p2p: peer buffer %d is null or unaligned", i);
   const size_t vecs = bytes_per_rank / 16;
-  long long bx = (long long)((vecs + 256 * 4 - 1) / (256 * 4));
-  const long long cap = (long long)sm_count() * 8 / W + 1;
+  long long bx = (long long)(((vecs + 255) / 256 * W + 7) / 8);
+  const long long cap = (long long)sm_count() * 8;
   if (bx > cap) bx = cap;
   if (bx < 1) bx = 1;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   ProfScope prof("a2a_store_kernel", st);
-  a2a_store_kernel<<<dim3((unsigned)bx, W), 256, 0, st>>>(static_cast<const uint4*>(send), t, vecs, rank);
+  a2a_store_kernel<<<(unsigned)bx, 256, 0, st>>>(static_cast<const uint4*>(send), t, vecs, W, rank);
   return launch_status("a2a_store_kernel");
 }
 
