@@ -321,6 +321,12 @@ int lancet_moe_combine_bwd_p2p(const void* dout, const void* gates_s, const int3
                                void* const* peer_d_expert_out, void* const* peer_expert_out, void* dgates_s, int S,
                                int M, int C, int LE, int W, int rank, int k, int n_chunks, int dtype,
                                lancet_stream_t stream);
+/* Bias gradient of an expert layer: db[e][:] = sum over the groups of expert e and their live rows of
+ * dY[g][r][:]  (dY [groups][C][N], db [LE][N]); the reference gets it from the autodiff of nn.Linear's
+ * bias add (a `sum` over rows).  ws: lancet_grouped_bias_grad_workspace_bytes(LE, N) bytes. */
+size_t lancet_grouped_bias_grad_workspace_bytes(int LE, int N);
+int lancet_grouped_bias_grad(const void* dY, void* db, int groups, int LE, int C, int N, const int32_t* counts,
+                             int dtype, void* ws, size_t ws_bytes, lancet_stream_t stream);
 
 /* ---- LANS optimizer ---------------------------------------------------------------------------
  * Replaces multi_tensor_lans_cuda (kernel_util.cuh:26-34; multi_tensor_lans.cu:401-450) and the

@@ -117,6 +117,9 @@ SIGNATURES = {
     "lancet_moe_combine_bwd_p2p": (c_int, [c_void_p, c_void_p, c_void_p, ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p),
                                            c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                            c_void_p]),
+    "lancet_grouped_bias_grad_workspace_bytes": (c_size_t, [c_int, c_int]),
+    "lancet_grouped_bias_grad": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_size_t,
+                                         c_void_p]),
     "lancet_lans_workspace_bytes": (c_size_t, [c_int, ctypes.POINTER(c_i64)]),
     "lancet_lans": (c_int, [c_void_p, c_size_t, c_int, ctypes.POINTER(c_i64), ctypes.POINTER(c_void_p),
                             ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), c_int, c_int,

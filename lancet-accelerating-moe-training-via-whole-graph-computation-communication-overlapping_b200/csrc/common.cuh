@@ -100,7 +100,7 @@ __device__ __forceinline__ void store_from_float(void* p, int dtype, size_t i, f
 size_t gate_workspace_bytes(int S, int E, int k, int n_chunks);
 int gate_launch(const void* gate, int gate_dtype, int S, int E, int k, int n_chunks, const int32_t* in_capused, int C,
                 int M, void* out_gates_s, int gates_dtype, int32_t* out_idx_loc, int32_t* out_capused,
-                uint64_t* out_elems, void* ws, int global_loc, cudaStream_t stream);
+                uint64_t* out_elems, void* ws, int global_loc, cudaStream_t stream, int32_t* chain_row0 = nullptr);
 int dispatch_launch(const int32_t* idx_loc, int k, const int32_t* in_cap, const int32_t* rows_hi, const int32_t* rows_lo,
                     const void* x, void* out, int S, int Sp, int M, int C, int E, int dtype, int flags,
                     cudaStream_t stream);

@@ -481,6 +481,43 @@ zero_dead_rows_kernel(T* __restrict__ D, const int32_t* __restrict__ counts, int
     base[i] = make_uint4(0, 0, 0, 0);
 }
 
+// Bias gradient of an expert layer: db[e][n] = sum over the groups g of expert e and their live rows r of dY[g][r][n].
+// Two deterministic stages: partial sums over row slices, then a sum over the slices in fixed order.
+constexpr int kColsumSplits = 64;
+template <typename T>
+__global__ void __launch_bounds__(256)
+colsum_partial_kernel(const T* __restrict__ dY, const int32_t* __restrict__ counts, int groups, int LE, int C, int N,
+                      float* __restrict__ partial) {
+  __shared__ float red[4][64];
+  const int col = blockIdx.x * 64 + (threadIdx.x & 63);
+  const int lane_r = threadIdx.x >> 6;            // 4 row lanes
+  const int split = blockIdx.y, e = blockIdx.z;
+  float acc = 0.f;
+  if (col < N) {
+    for (int g = e; g < groups; g += LE) {
+      int rows = counts ? counts[g] : C;
+      rows = rows < 0 ? 0 : (rows > C ? C : rows);
+      const T* base = dY + (size_t)g * C * N + col;
+      for (int r = split * 4 + lane_r; r < rows; r += kColsumSplits * 4) acc += Num<T>::to_f(base[(size_t)r * N]);
+    }
+  }
+  red[lane_r][threadIdx.x & 63] = acc;
+  __syncthreads();
+  if (lane_r == 0 && col < N)
+    partial[((size_t)e * kColsumSplits + split) * N + col] = (red[0][threadIdx.x] + red[1][threadIdx.x]) + (red[2][threadIdx.x] + red[3][threadIdx.x]);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+colsum_final_kernel(const float* __restrict__ partial, int LE, int N, T* __restrict__ db) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= LE * N) return;
+  const int e = i / N, col = i - e * N;
+  float acc = 0.f;
+  for (int s = 0; s < kColsumSplits; ++s) acc += partial[((size_t)e * kColsumSplits + s) * N + col];
+  db[i] = Num<T>::from_f(acc);
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -649,5 +686,36 @@ int lancet_grouped_gemm_tn(const void* A, const void* B, void* D, int groups, in
   if (int rc = make_map3(&tmA, A, (uint64_t)groups, (uint64_t)C, (uint64_t)Mout, dtype)) return rc;
   if (int rc = make_map3(&tmB, B, (uint64_t)groups, (uint64_t)C, (uint64_t)N, dtype)) return rc;
   return launch<MODE_REDUCE, true, EPI_ACT>(tmA, tmB, p, dtype, "grouped_gemm_tn_kernel", static_cast<cudaStream_t>(stream));
+}
+
+size_t lancet_grouped_bias_grad_workspace_bytes(int LE, int N) {
+  if (LE < 1 || N < 1) return 0;
+  return (size_t)LE * lancet::gemm::kColsumSplits * N * sizeof(float);
+}
+
+int lancet_grouped_bias_grad(const void* dY, void* db, int groups, int LE, int C, int N, const int32_t* counts, int dtype,
+                             void* ws, size_t ws_bytes, lancet_stream_t stream) {
+  using namespace lancet::gemm;
+  LANCET_REQUIRE(dtype == LANCET_BF16 || dtype == LANCET_F16, LANCET_ERR_UNSUPPORTED,
+                 "lancet_grouped_bias_grad: inputs must be bfloat16 or float16 (dtype code %d)", dtype);
+  LANCET_REQUIRE(groups >= 1 && LE >= 1 && groups % LE == 0 && C >= 0 && N >= 1, LANCET_ERR_INVALID,
+                 "lancet_grouped_bias_grad: bad sizes groups=%d LE=%d C=%d N=%d", groups, LE, C, N);
+  LANCET_REQUIRE(dY && db && ws, LANCET_ERR_NULL, "lancet_grouped_bias_grad: null pointer argument");
+  LANCET_REQUIRE(ws_bytes >= lancet_grouped_bias_grad_workspace_bytes(LE, N), LANCET_ERR_INVALID,
+                 "lancet_grouped_bias_grad: workspace too small");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  float* partial = static_cast<float*>(ws);
+  const dim3 grid1((N + 63) / 64, kColsumSplits, LE);
+  const int grid2 = (LE * N + 255) / 256;
+  if (dtype == LANCET_BF16) {
+    colsum_partial_kernel<__nv_bfloat16><<<grid1, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(dY), counts, groups, LE, C, N, partial);
+    if (int rc = launch_status("colsum_partial_kernel")) return rc;
+    colsum_final_kernel<__nv_bfloat16><<<grid2, 256, 0, st>>>(partial, LE, N, static_cast<__nv_bfloat16*>(db));
+  } else {
+    colsum_partial_kernel<__half><<<grid1, 256, 0, st>>>(static_cast<const __half*>(dY), counts, groups, LE, C, N, partial);
+    if (int rc = launch_status("colsum_partial_kernel")) return rc;
+    colsum_final_kernel<__half><<<grid2, 256, 0, st>>>(partial, LE, N, static_cast<__half*>(db));
+  }
+  return launch_status("colsum_final_kernel");
 }
 }

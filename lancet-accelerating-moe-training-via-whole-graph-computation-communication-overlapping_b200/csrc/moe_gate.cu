@@ -160,7 +160,7 @@ gate_assign_kernel(int Sp, int E, int C, int M, int n_chunks, int tiles_per_chun
                    const int* __restrict__ hist, const int* __restrict__ total_in,
                    const int32_t* __restrict__ in_capused, const float* __restrict__ raw_gates,
                    int32_t* __restrict__ idx_loc, void* __restrict__ gates_out, int gates_dtype,
-                   int32_t* __restrict__ out_capused, uint64_t* __restrict__ out_elems) {
+                   int32_t* __restrict__ out_capused, uint64_t* __restrict__ out_elems, int32_t* __restrict__ chain_row0) {
   extern __shared__ int sm[];  // pre[KE], used[E], tot[n_chunks][KE]
   const int KE = K * E;
   int* pre = sm;
@@ -201,6 +201,7 @@ gate_assign_kernel(int Sp, int E, int C, int M, int n_chunks, int tiles_per_chun
   // capacity used before this chunk: the chain min(used + n, C) over the earlier chunks
   for (int ex = tid; ex < E; ex += kGateTile) {
     int used = in_capused ? in_capused[ex] : 0;
+    if (writes_chain && chain_row0) chain_row0[ex] = used;  // row 0 of a [n+1][E] capacity chain
     for (int c = 0; c < chunk; ++c) {
       int n = 0;
 #pragma unroll
@@ -282,7 +283,7 @@ size_t gate_workspace_bytes(int S, int E, int k, int n_chunks) { return gate_lay
 
 int gate_launch(const void* gate, int gate_dtype, int S, int E, int k, int n_chunks, const int32_t* in_capused, int C,
                 int M, void* out_gates_s, int gates_dtype, int32_t* out_idx_loc, int32_t* out_capused,
-                uint64_t* out_elems, void* ws, int global_loc, cudaStream_t stream) {
+                uint64_t* out_elems, void* ws, int global_loc, cudaStream_t stream, int32_t* chain_row0) {
   const GateLayout L = gate_layout(S, E, k, n_chunks);
   char* w = static_cast<char*>(ws);
   float* raw = reinterpret_cast<float*>(w + L.raw_off);
@@ -307,11 +308,11 @@ int gate_launch(const void* gate, int gate_dtype, int S, int E, int k, int n_chu
   if (k == 1)
     gate_assign_kernel<1><<<L.tiles, kGateTile, smem2, stream>>>(L.Sp, E, C, M, n_chunks, L.tiles_per_chunk, prescanned,
                                                                  global_loc, hist, total, in_capused, raw, out_idx_loc,
-                                                                 out_gates_s, gates_dtype, out_capused, out_elems);
+                                                                 out_gates_s, gates_dtype, out_capused, out_elems, chain_row0);
   else
     gate_assign_kernel<2><<<L.tiles, kGateTile, smem2, stream>>>(L.Sp, E, C, M, n_chunks, L.tiles_per_chunk, prescanned,
                                                                  global_loc, hist, total, in_capused, raw, out_idx_loc,
-                                                                 out_gates_s, gates_dtype, out_capused, out_elems);
+                                                                 out_gates_s, gates_dtype, out_capused, out_elems, chain_row0);
   return launch_status("gate_assign_kernel");
 }
 
@@ -353,7 +354,7 @@ int lancet_moe_gate_chained(const void* gate, int gate_dtype, int S, int E, int 
                  "lancet_moe_gate: workspace must be 16-byte aligned");
   return gate_launch(gate, gate_dtype, S, E, k, n_chunks, in_capused, C, M, out_gates_s, gates_dtype, out_idx_loc,
                      out_capused, out_elems, ws, (flags & LANCET_GATE_GLOBAL_LOC) ? 1 : 0,
-                     static_cast<cudaStream_t>(stream));
+                     static_cast<cudaStream_t>(stream), nullptr);
 }
 
 int lancet_moe_gate(const void* gate, int gate_dtype, int S, int E, int k, const int32_t* in_capused, int C, int M,

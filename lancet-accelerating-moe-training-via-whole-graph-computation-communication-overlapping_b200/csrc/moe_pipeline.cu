@@ -21,8 +21,8 @@ int lancet_moe_dispatch_chunked(const void* x, const void* gate, int gate_dtype,
                                 lancet_stream_t stream) {
   LANCET_REQUIRE(n_chunks >= 1 && S >= 0 && S % n_chunks == 0, LANCET_ERR_INVALID,
                  "lancet_moe_dispatch_chunked: S=%d is not divisible into %d chunks", S, n_chunks);
-  LANCET_REQUIRE(E > 0 && (k == 1 || k == 2) && M >= 0, LANCET_ERR_INVALID,
-                 "lancet_moe_dispatch_chunked: bad sizes E=%d k=%d M=%d", E, k, M);
+  LANCET_REQUIRE((k == 1 || k == 2) && E >= k && M >= 0, LANCET_ERR_INVALID,
+                 "lancet_moe_dispatch_chunked: bad sizes E=%d k=%d M=%d (need k in {1,2}, E >= k)", E, k, M);
   LANCET_REQUIRE(valid_dtype(dtype) && valid_dtype(gate_dtype) && valid_dtype(gates_dtype), LANCET_ERR_INVALID,
                  "lancet_moe_dispatch_chunked: unknown dtype code");
   LANCET_REQUIRE(capused_chain && elems && ws && (S == 0 || (x && gate && gates_s && idx_loc)), LANCET_ERR_NULL,
@@ -35,10 +35,14 @@ int lancet_moe_dispatch_chunked(const void* x, const void* gate, int gate_dtype,
   LANCET_REQUIRE(aligned(x, dtype_bytes(dtype)) && aligned(dispatched, dtype_bytes(dtype)), LANCET_ERR_INVALID,
                  "lancet_moe_dispatch_chunked: data pointers are not aligned to the element size");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  LANCET_CUDA(cudaMemsetAsync(capused_chain, 0, (size_t)E * sizeof(int32_t), st));
-  // one gating pass over all chunks (chain of used capacities), locations = rows of the shared buffer
-  int rc = lancet_moe_gate_chained(gate, gate_dtype, S, E, k, n_chunks, capused_chain, C, M, gates_s, gates_dtype, idx_loc,
-                                   capused_chain + E, elems, ws, ws_bytes, LANCET_GATE_GLOBAL_LOC, stream);
+  LANCET_REQUIRE(k * E <= 1024 && (long long)n_chunks * k * E <= 8192, LANCET_ERR_INVALID,
+                 "lancet_moe_dispatch_chunked: k*E=%d or n_chunks*k*E too large", k * E);
+  LANCET_REQUIRE(ws_bytes >= gate_workspace_bytes(S, E, k, n_chunks) && aligned(ws, 16), LANCET_ERR_INVALID,
+                 "lancet_moe_dispatch_chunked: workspace too small or unaligned");
+  // one gating pass over all chunks (chain of used capacities starting from zero; the pass also writes row 0
+  // of the chain), locations = rows of the shared buffer
+  int rc = gate_launch(gate, gate_dtype, S, E, k, n_chunks, nullptr, C, M, gates_s, gates_dtype, idx_loc, capused_chain + E,
+                       elems, ws, 1, st, capused_chain);
   if (rc != LANCET_OK) return rc;
   if ((size_t)E * C * M == 0) return LANCET_OK;
   // one scatter over all tokens; rows past the final used capacity are zero-filled by the same launch

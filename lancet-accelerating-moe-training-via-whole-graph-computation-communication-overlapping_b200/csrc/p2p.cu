@@ -390,9 +390,12 @@ int lancet_moe_dispatch_chunked_p2p(const void* x, const void* gate, int gate_dt
     for (int i = 0; i < W; ++i)
       LANCET_REQUIRE(tc.ptr[i], LANCET_ERR_NULL, "lancet_moe_dispatch_chunked_p2p: LANCET_P2P_NO_REMOTE_ZERO needs peer_counts (entry %d is null)", i);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  LANCET_CUDA(cudaMemsetAsync(capused_chain, 0, (size_t)E * sizeof(int32_t), st));
-  int rc = lancet_moe_gate_chained(gate, gate_dtype, S, E, k, n_chunks, capused_chain, C, M, gates_s, LANCET_F32, idx_loc,
-                                   capused_chain + E, elems, ws, ws_bytes, LANCET_GATE_GLOBAL_LOC, stream);
+  LANCET_REQUIRE(E >= k && k * E <= 1024 && (long long)n_chunks * k * E <= 8192, LANCET_ERR_INVALID,
+                 "lancet_moe_dispatch_chunked_p2p: k*E=%d or n_chunks*k*E too large", k * E);
+  LANCET_REQUIRE(ws_bytes >= gate_workspace_bytes(S, E, k, n_chunks) && aligned(ws, 16), LANCET_ERR_INVALID,
+                 "lancet_moe_dispatch_chunked_p2p: workspace too small or unaligned");
+  int rc = gate_launch(gate, gate_dtype, S, E, k, n_chunks, nullptr, C, M, gates_s, LANCET_F32, idx_loc, capused_chain + E,
+                       elems, ws, 1, st, capused_chain);
   if (rc != LANCET_OK) return rc;
   if ((size_t)E * C * M == 0) return LANCET_OK;
   const int zero_tail = (flags & LANCET_P2P_NO_REMOTE_ZERO) ? 0 : 1;

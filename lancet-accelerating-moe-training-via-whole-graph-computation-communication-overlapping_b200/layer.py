@@ -30,6 +30,8 @@ class MoELayer:
         self.dh = torch.empty((G, C, H), dtype=dtype, device=d)
         self.dw1 = torch.empty_like(self.w1)
         self.dw2 = torch.empty_like(self.w2)
+        self.db1 = torch.empty_like(self.b1)
+        self.db2 = torch.empty_like(self.b2)
         self.side = torch.cuda.Stream(device=d) if overlap_dw else None
         self.G, self.C = G, C
 
@@ -71,6 +73,8 @@ class MoELayer:
         with torch.cuda.stream(self.side if self.side is not None else main):
             ops.grouped_gemm_tn(dy, self.h, self.LE, counts=self.cnt, out=self.dw2)
             ops.grouped_gemm_tn(self.dh, self.x_e, self.LE, counts=self.cnt, out=self.dw1)
+            ops.grouped_bias_grad(dy, self.LE, counts=self.cnt, out=self.db2)
+            ops.grouped_bias_grad(self.dh, self.LE, counts=self.cnt, out=self.db1)
 
     def bwd_dispatch(self):
         dx = self.moe.dispatch_backward()

@@ -371,3 +371,15 @@ def moe_encode_batch_prioritized(data, gate, n_partitions=1, partition_id=0, cap
                                   E, _dt(data), _ptr(gates_s), _capi.F32, _ptr(idx_loc), _ptr(capused), _ptr(elems),
                                   _ptr(disp), _ptr(ws), ws.numel(), _stream(data)))
     return gates_s, idx_loc, capused, elems, disp
+
+
+def grouped_bias_grad(dy, n_local_experts, counts=None, out=None):
+    """Bias gradient of an expert layer: out[e] = sum of the live rows of dy[g] over the groups g of expert e."""
+    _require_cuda(dy, counts, out)
+    groups, C, N = dy.shape
+    out = torch.empty((n_local_experts, N), dtype=dy.dtype, device=dy.device) if out is None else out
+    L = _capi.lib()
+    ws = workspace(dy.device, L.lancet_grouped_bias_grad_workspace_bytes(n_local_experts, N), "bias_grad")
+    check(L.lancet_grouped_bias_grad(_ptr(dy), _ptr(out), groups, n_local_experts, C, N, _ptr(counts), _dt(dy), _ptr(ws),
+                                     ws.numel(), _stream(dy)))
+    return out

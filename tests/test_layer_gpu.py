@@ -43,8 +43,8 @@ def test_layer_forward_backward(W, k, n):
     xr = [x.float().requires_grad_(True) for x in xs]
     w1 = [l.w1.float().requires_grad_(True) for l in layers]
     w2 = [l.w2.float().requires_grad_(True) for l in layers]
-    b1 = [l.b1.float() for l in layers]
-    b2 = [l.b2.float() for l in layers]
+    b1 = [l.b1.float().requires_grad_(True) for l in layers]
+    b2 = [l.b2.float().requires_grad_(True) for l in layers]
     gs = [l.moe.gates_s.clone().requires_grad_(True) for l in layers]        # [n, k, Sp]
     loss = 0
     ref_out = []
@@ -74,5 +74,7 @@ def test_layer_forward_backward(W, k, n):
         close(dgates, gs[r].grad, "dgates[%d]" % r)
         close(l.dw1, w1[r].grad, "dw1[%d]" % r)
         close(l.dw2, w2[r].grad, "dw2[%d]" % r)
+        close(l.db1, b1[r].grad, "db1[%d]" % r)
+        close(l.db2, b2[r].grad, "db2[%d]" % r)
     st = LB.gemm_status(torch.device(DEV))
     assert int(st.item()) == 0
