@@ -96,7 +96,7 @@ def test_training_steps_match_torch_reference_and_loss_falls():
     model["blocks"][1].ffn = ref_block
     loss_ref = run(model, ids)
     loss_ref.backward()
-    assert abs(float(loss) - float(loss_ref)) < 2e-2 * abs(float(loss_ref))
+    assert abs(float(loss.detach()) - float(loss_ref.detach())) < 2e-2 * abs(float(loss_ref.detach()))
     for n, p in model.named_parameters():
         n_lib = n.replace("ffn.moe.", "ffn.")
         g, r = got[n_lib], p.grad
@@ -123,5 +123,5 @@ def test_training_steps_match_torch_reference_and_loss_falls():
             for p, wp in zip(params, w[0]):
                 np.testing.assert_allclose(p.detach().cpu().numpy(), wp, rtol=1e-4, atol=1e-6)
         model.zero_grad()
-        losses.append(float(loss))
+        losses.append(float(loss.detach()))
     assert losses[-1] < losses[0] - 0.05, losses
