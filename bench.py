@@ -124,7 +124,7 @@ def cpu_reference_sample(max_seconds, world=1, tokens=None):
         tokens = max(256, tokens // 256 * 256)
     dt, _ = run(tokens)
     return tokens / dt, cores, "%d of %d tokens/GPU, M=%d, E=%d, top-%d, encode+decode with per-token loops" % (
-        tokens, S_TOKENS, M_DIM, E, TOP_K), dt, tokens
+        tokens, S_TOKENS, M_DIM, E, TOP_K) + " (torch CPU ops on %d threads, the loops are single-threaded Python)" % cores, dt, tokens
 
 
 def run_reference_arm(args):
@@ -680,6 +680,63 @@ def run_a2a(args):
     })
 
 
+def run_gpt(args):
+    """Full GPT-MoE training step (nl=12, m=1024, nh=16, sl=512, b=16 per GPU, vocab 50257, every other layer MoE with
+    2N experts of FFN 4096, top-2, capacity factor 1.25, bf16 autocast, LANS).  Token ids are uniform random from a seed."""
+    import lancet_b200 as LB
+    from lancet_b200.gpt_moe import GPTMoE, LansTrainer
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit("bench.py: --gpus %d but WORLD_SIZE=%d" % (args.gpus, world))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    fabric = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    else:
+        fabric = LB.LocalFabric(1, 0, {})
+    vocab, m, nh, nl, seq, batch, ffn = 50257, 1024, 16, 12, 512, 16, 4096
+    model = GPTMoE(vocab, m, nh, nl, seq, batch, ffn, 2 * world, TOP_K, CAP_FACTOR, N_CHUNKS, dev, fabric=fabric, seed=0)
+    trainer = LansTrainer(model, lr=1e-3)
+    g = torch.Generator(device=dev).manual_seed(1000 + rank)
+    ids = [torch.randint(0, vocab, (batch, seq), device=dev, generator=g) for _ in range(2)]
+    losses = []
+    for i in range(max(args.warmup, 3)):
+        losses.append(float(trainer.step(ids[i % 2])))
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for i in range(args.steps):
+        loss = trainer.step(ids[i % 2])
+    ev1.record()
+    torch.cuda.synchronize()
+    losses.append(float(loss))
+    ms = ev0.elapsed_time(ev1) / args.steps
+    if world > 1:
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        dist.barrier()
+        model.close()
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+    n_params = sum(p.numel() for p in model.parameters())
+    emit({
+        "metric": "gpt_moe_tokens_per_s", "value": batch * seq * world / (ms / 1e3), "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "gpt2_moe_nl12_m1024_nh16_sl512_b16 training step, %d experts, top-2, cf 1.25, LANS" % (2 * world),
+                   "params_per_rank": n_params},
+        "loss_first": losses[0], "loss_last": losses[-1],
+    })
+
+
 def main():
     # libraries (NCCL, torchrun) may write to stdout; keep it clean for the one JSON line
     saved_stdout = os.dup(1)
@@ -706,7 +763,7 @@ def _main():
     ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="moe", choices=["moe", "lans", "ffn", "layer", "a2a"])
+    ap.add_argument("--workload", default="moe", choices=["moe", "lans", "ffn", "layer", "a2a", "gpt"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-graph", action="store_true", help="launch every step eagerly instead of replaying a CUDA graph")
     ap.add_argument("--lans-layers", type=int, default=24, help="transformer layers in the LANS tensor list (24 = 196 tensors)")
@@ -724,6 +781,8 @@ def _main():
         run_layer(args)
     elif args.workload == "a2a":
         run_a2a(args)
+    elif args.workload == "gpt":
+        run_gpt(args)
     else:
         run_moe(args)
 

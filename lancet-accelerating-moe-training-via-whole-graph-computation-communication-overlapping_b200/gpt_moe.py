@@ -1,0 +1,116 @@
+"""GPT-2-style decoder with an expert-parallel MoE block in every other layer: the model family of the
+reference's benchmark (gpt2_moe_nl12_m1024_nh16_sl512, models/benchmark/pytorch/nlp.py:303-316,
+`moe_expert_interval=2`, `num_experts = 2 * world_size`, models/benchmark_raf.py:53).  Attention, layer norm,
+embeddings and the loss are plain torch modules (outside the hot path this library implements); the MoE
+blocks run on the library's fused layer, the optimizer step on its LANS op."""
+import torch
+import torch.nn.functional as F
+
+from .autograd import MoE
+from .ops import LansState, lans
+
+
+class Attention(torch.nn.Module):
+    def __init__(self, m, nh):
+        super().__init__()
+        self.nh = nh
+        self.qkv = torch.nn.Linear(m, 3 * m)
+        self.proj = torch.nn.Linear(m, m)
+
+    def forward(self, x):
+        B, T, M = x.shape
+        q, k, v = self.qkv(x).view(B, T, 3, self.nh, M // self.nh).permute(2, 0, 3, 1, 4)
+        y = F.scaled_dot_product_attention(q, k, v, is_causal=True)
+        return self.proj(y.transpose(1, 2).reshape(B, T, M))
+
+
+class Block(torch.nn.Module):
+    def __init__(self, m, nh, ffn):
+        super().__init__()
+        self.ln1, self.ln2 = torch.nn.LayerNorm(m), torch.nn.LayerNorm(m)
+        self.attn = Attention(m, nh)
+        self.ffn = ffn
+
+    def forward(self, x):
+        x = x + self.attn(self.ln1(x))
+        return x + self.ffn(self.ln2(x))
+
+
+class GPTMoE(torch.nn.Module):
+    def __init__(self, vocab, m, nh, nl, seq, batch, ffn_dim, world_experts, k=2, capacity_factor=1.25, n_chunks=4,
+                 device="cuda", fabric=None, group=None, seed=0):
+        super().__init__()
+        torch.manual_seed(seed)
+        self.emb = torch.nn.Embedding(vocab, m)
+        self.pos = torch.nn.Embedding(seq, m)
+        blocks = []
+        for i in range(nl):
+            if i % 2 == 1:
+                ffn = MoE(seq * batch, m, ffn_dim, world_experts, k, capacity_factor, n_chunks, torch.bfloat16, device, 2,
+                          fabric=fabric, group=group, seed=seed + i)
+            else:
+                ffn = torch.nn.Sequential(torch.nn.Linear(m, ffn_dim), torch.nn.GELU(), torch.nn.Linear(ffn_dim, m))
+            blocks.append(Block(m, nh, ffn))
+        self.blocks = torch.nn.ModuleList(blocks)
+        self.ln = torch.nn.LayerNorm(m)
+        torch.nn.init.normal_(self.emb.weight, std=0.02)
+        torch.nn.init.normal_(self.pos.weight, std=0.01)
+        self.to(device)
+
+    def expert_parameters(self):
+        out = []
+        for b in self.blocks:
+            if isinstance(b.ffn, MoE):
+                out += [b.ffn.w1, b.ffn.b1, b.ffn.w2, b.ffn.b2]
+        return out
+
+    def forward(self, ids):
+        x = self.emb(ids) + self.pos(torch.arange(ids.shape[1], device=ids.device))[None]
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            for b in self.blocks:
+                x = b(x)
+            logits = F.linear(self.ln(x), self.emb.weight)         # tied output embedding
+        return F.cross_entropy(logits[:, :-1].reshape(-1, logits.shape[-1]).float(), ids[:, 1:].reshape(-1))
+
+    def close(self):
+        for b in self.blocks:
+            if isinstance(b.ffn, MoE):
+                b.ffn.layer.moe.close()
+
+
+class LansTrainer:
+    """One training step: forward, backward, gradient average of the replicated parameters across ranks
+    (torch.distributed, outside this library's scope), LANS update through the library."""
+
+    def __init__(self, model, lr=1e-3, group=None):
+        self.model = model
+        self.params = [p for p in model.parameters()]
+        expert_ids = {id(p) for p in model.expert_parameters()}
+        self.shared = [p for p in self.params if id(p) not in expert_ids]
+        self.m = [torch.zeros_like(p) for p in self.params]
+        self.v = [torch.zeros_like(p) for p in self.params]
+        self.grads = [torch.zeros_like(p) for p in self.params]
+        for p, g in zip(self.params, self.grads):
+            p.grad = g
+        self.state = LansState(self.grads, [p.data for p in self.params], self.m, self.v)
+        self.lr = lr
+        self.step_no = 0
+        self.group = group
+        self.world = torch.distributed.get_world_size(group) if torch.distributed.is_initialized() else 1
+
+    def step(self, ids):
+        self.step_no += 1
+        loss = self.model(ids)
+        loss.backward()
+        if self.world > 1:
+            flat = torch._utils._flatten_dense_tensors([p.grad for p in self.shared])
+            torch.distributed.all_reduce(flat, group=self.group)
+            flat.div_(self.world)
+            for g, f in zip([p.grad for p in self.shared], torch._utils._unflatten_dense_tensors(flat, [p.grad for p in self.shared])):
+                g.copy_(f)
+        with torch.no_grad():
+            lans(self.grads + [p.data for p in self.params] + self.m + self.v, self.step_no, learning_rate=self.lr,
+                 state=self.state)
+        for g in self.grads:
+            g.zero_()
+        return loss.detach()

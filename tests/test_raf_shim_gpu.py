@@ -99,3 +99,21 @@ def test_partitioned_graph_ops_through_registry():
     assert name == "raf.op.cuda.moe_encode_batch_prioritized"
     for a, b in zip(got, want):
         np.testing.assert_array_equal(a.cpu().numpy() if a.dtype != torch.uint64 else a.cpu().view(torch.int64).numpy().astype(np.uint64), b)
+
+
+def test_cpp_host_through_registry(tmp_path):
+    """A C++ program (no Python, no torch) drives moe_encode / moe_decode through the registry."""
+    import shutil
+    import subprocess
+    import lancet_b200 as LB
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(nvcc):
+        pytest.skip("no nvcc on this box")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    shim = os.path.join(LB.build.CSRC, "raf_shim")
+    exe = str(tmp_path / "raf_host_example")
+    libdir = os.path.dirname(LB.build.LIB_PATH)
+    subprocess.run([nvcc, "-std=c++17", "-O1", "-I", shim, os.path.join(root, "tests", "cpp", "raf_host_example.cc"),
+                    "-L", libdir, "-llancet_b200", "-Xlinker", "-rpath", "-Xlinker", libdir, "-o", exe], check=True)
+    r = subprocess.run([exe], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0 and "raf host example ok" in r.stdout, r.stdout + r.stderr
