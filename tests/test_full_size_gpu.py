@@ -17,7 +17,8 @@ def test_moe_config3_properties(E):
     S, M, k, cf, n = 16384, 2048, 2, 1.25, 4
     g = torch.Generator(device=DEV).manual_seed(1000)
     x = torch.randn((S, M), device=DEV, generator=g).half()
-    gate = torch.softmax(torch.randn((S, E), device=DEV, generator=g) * 2.0, dim=1)     # skewed: forces drops
+    bias = torch.linspace(1.5, -1.5, E, device=DEV)                                      # popular and unpopular experts: forces drops
+    gate = torch.softmax(torch.randn((S, E), device=DEV, generator=g) + bias, dim=1)
     plan = LB.ChunkedMoE(S, M, E, k, cf, n, torch.float16, device=DEV)
     disp = plan.dispatch(x, gate)
     out = plan.combine()
@@ -28,7 +29,7 @@ def test_moe_config3_properties(E):
     idx = torch.stack([il[0], il[2]])
     loc = torch.stack([il[1], il[3]])
     kept = idx >= 0
-    assert int((~kept).sum()) > 0 or E == 2
+    assert int((~kept).sum()) > 0
     # round trip with identity experts
     want = torch.zeros((S, M), device=DEV, dtype=torch.float32)
     for j in range(k):
