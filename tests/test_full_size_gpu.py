@@ -29,7 +29,7 @@ def test_moe_config3_properties(E):
     idx = torch.stack([il[0], il[2]])
     loc = torch.stack([il[1], il[3]])
     kept = idx >= 0
-    assert int((~kept).sum()) > 0
+    assert E == 2 or int((~kept).sum()) > 0      # with E == k every expert receives exactly S rows: nothing can drop
     # round trip with identity experts
     want = torch.zeros((S, M), device=DEV, dtype=torch.float32)
     for j in range(k):
