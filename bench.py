@@ -207,9 +207,10 @@ def run_moe(args):
     sync_all()
     kname = b"dispatch_rows_kernel" if world == 1 else b"dispatch_rows_peer_kernel"
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    use_graph = world == 1 and not args.no_graph
+    use_graph = not args.no_graph
     if use_graph:
-        # the step is 5 short launches: replay it from a CUDA graph (one per input set) to cut launch gaps
+        # the step is a handful of short launches: replay it from a CUDA graph (one per input set; the receive
+        # buffers of the multi-GPU plan alternate with the same period) to cut launch gaps
         graphs = []
         side = torch.cuda.Stream(device=dev)
         side.wait_stream(torch.cuda.current_stream())

@@ -231,6 +231,10 @@ int lancet_symm_free(void* ptr);
  * healthy) and returns; lancet_p2p_status() turns a non-zero word into LANCET_ERR_TIMEOUT. */
 int lancet_p2p_barrier(void* const* peer_flags, int W, int rank, unsigned epoch, unsigned long long timeout_ns,
                        int32_t* status, lancet_stream_t stream);
+/* Same barrier with the epoch kept in device memory (*epoch_counter, zero-initialised, owned by this rank):
+ * every launch uses the stored value + 1 and writes it back, so the launch can be replayed from a CUDA graph. */
+int lancet_p2p_barrier_counted(void* const* peer_flags, int W, int rank, uint32_t* epoch_counter,
+                               unsigned long long timeout_ns, int32_t* status, lancet_stream_t stream);
 int lancet_p2p_status(const int32_t* status, lancet_stream_t stream);
 
 /* LANCET_P2P_NO_REMOTE_ZERO: do not send zero rows over NVLink; instead the row count of every

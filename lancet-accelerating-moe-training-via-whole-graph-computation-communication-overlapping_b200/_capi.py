@@ -73,6 +73,8 @@ SIGNATURES = {
     "lancet_symm_free": (c_int, [c_void_p]),
     "lancet_p2p_barrier": (c_int, [ctypes.POINTER(c_void_p), c_int, c_int, ctypes.c_uint, ctypes.c_ulonglong, c_void_p,
                                    c_void_p]),
+    "lancet_p2p_barrier_counted": (c_int, [ctypes.POINTER(c_void_p), c_int, c_int, c_void_p, ctypes.c_ulonglong, c_void_p,
+                                           c_void_p]),
     "lancet_p2p_status": (c_int, [c_void_p, c_void_p]),
     "lancet_moe_dispatch_chunked_p2p": (c_int, [c_void_p, c_void_p, c_int, c_float, c_int, c_int, c_int, c_int, c_int,
                                                 c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,

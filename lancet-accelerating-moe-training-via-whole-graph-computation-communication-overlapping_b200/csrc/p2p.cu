@@ -232,9 +232,14 @@ __device__ __forceinline__ unsigned long long globaltimer_ns() {
 
 // Thread i tells rank i that this rank has arrived (epoch) and waits until rank i has told us.
 // flags.ptr[r] is rank r's array of W words; word i of it is written by rank i only.
+// With epoch_counter != nullptr the epoch is kept in device memory (previous value + 1, written back by thread 0),
+// so that the same launch can be replayed from a CUDA graph.
 __global__ void p2p_barrier_kernel(PeerTable flags, int W, int my_rank, unsigned epoch, unsigned long long timeout_ns,
-                                   int* __restrict__ status) {
+                                   int* __restrict__ status, unsigned* __restrict__ epoch_counter) {
   const int i = threadIdx.x;
+  if (epoch_counter) epoch = *epoch_counter + 1;
+  __syncwarp();
+  if (i == 0 && epoch_counter) *epoch_counter = epoch;
   if (i >= W) return;
   __threadfence_system();
   unsigned* remote = static_cast<unsigned*>(flags.ptr[i]) + my_rank;
@@ -344,7 +349,21 @@ int lancet_p2p_barrier(void* const* peer_flags, int W, int rank, unsigned epoch,
   PeerTable t;
   for (int i = 0; i < kMaxPeers; ++i) t.ptr[i] = i < W ? peer_flags[i] : nullptr;
   for (int i = 0; i < W; ++i) LANCET_REQUIRE(t.ptr[i], LANCET_ERR_NULL, "lancet_p2p_barrier: flag pointer %d is null", i);
-  p2p_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(t, W, rank, epoch, timeout_ns, status);
+  p2p_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(t, W, rank, epoch, timeout_ns, status, nullptr);
+  return launch_status("p2p_barrier_kernel");
+}
+
+int lancet_p2p_barrier_counted(void* const* peer_flags, int W, int rank, uint32_t* epoch_counter, unsigned long long timeout_ns,
+                               int32_t* status, lancet_stream_t stream) {
+  LANCET_REQUIRE(W >= 1 && W <= kMaxPeers && rank >= 0 && rank < W, LANCET_ERR_INVALID,
+                 "lancet_p2p_barrier_counted: bad world %d / rank %d (at most %d ranks)", W, rank, kMaxPeers);
+  LANCET_REQUIRE(peer_flags && status && epoch_counter, LANCET_ERR_NULL, "lancet_p2p_barrier_counted: null argument");
+  LANCET_REQUIRE(timeout_ns > 0 && timeout_ns <= 60ull * 1000000000ull, LANCET_ERR_INVALID,
+                 "lancet_p2p_barrier_counted: the wait limit must be in (0, 60 s]");
+  PeerTable t;
+  for (int i = 0; i < kMaxPeers; ++i) t.ptr[i] = i < W ? peer_flags[i] : nullptr;
+  for (int i = 0; i < W; ++i) LANCET_REQUIRE(t.ptr[i], LANCET_ERR_NULL, "lancet_p2p_barrier_counted: flag pointer %d is null", i);
+  p2p_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(t, W, rank, 0u, timeout_ns, status, epoch_counter);
   return launch_status("p2p_barrier_kernel");
 }
 

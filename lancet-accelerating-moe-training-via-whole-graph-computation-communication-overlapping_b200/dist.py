@@ -144,6 +144,7 @@ class DistChunkedMoE:
         self.elems = torch.zeros((n_chunks, self.E), dtype=torch.uint64, device=d)
         self.out = torch.empty((S, M), dtype=dtype, device=d)
         self.status = torch.zeros(1, dtype=torch.int32, device=d)
+        self.epoch_dev = torch.zeros(1, dtype=torch.int32, device=d)   # barrier epoch, kept on the device (graph replay)
         nws = L.lancet_moe_dispatch_chunked_workspace_bytes(S, self.E, k, n_chunks)
         self.ws = torch.empty(max(nws, 256), dtype=torch.uint8, device=d)
         self.timeout_ns = int(timeout_s * 1e9)
@@ -169,9 +170,8 @@ class DistChunkedMoE:
         """All ranks' earlier kernels on this stream have finished when later kernels start."""
         if not self.fabric.real or self.W == 1:
             return
-        self.epoch += 1
-        check(_capi.lib().lancet_p2p_barrier(self.peer_flags, self.W, self.rank, self.epoch, self.timeout_ns,
-                                             _ptr(self.status), _stream(self.status)))
+        check(_capi.lib().lancet_p2p_barrier_counted(self.peer_flags, self.W, self.rank, _ptr(self.epoch_dev),
+                                                     self.timeout_ns, _ptr(self.status), _stream(self.status)))
 
     def dispatch(self, x, gate):
         """Gate all chunks, scatter rows into the owners' receive buffers, meet the peers.
