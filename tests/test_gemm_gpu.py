@@ -163,3 +163,20 @@ def test_weight_gradient_all_groups_empty():
     torch.cuda.synchronize()
     check_status()
     assert (out == 0).all()
+
+
+def test_gemm_empty_groups_and_zero_capacity():
+    a = torch.randn((4, 256, 64), device=DEV).bfloat16()
+    b = torch.randn((2, 256, 64), device=DEV).bfloat16()
+    out = torch.full((4, 256, 256), 7.0, dtype=torch.bfloat16, device=DEV)
+    counts = torch.zeros(4, dtype=torch.int32, device=DEV)
+    LB.grouped_gemm_nt(a, b, counts=counts, out=out)          # nothing is live: nothing may be written
+    torch.cuda.synchronize()
+    check_status()
+    assert (out.float() == 7.0).all()
+    empty = LB.grouped_gemm_nt(a[:, :0].contiguous(), b)      # C == 0
+    assert empty.shape == (4, 0, 256)
+    dw = LB.grouped_gemm_tn(torch.zeros((4, 0, 128), dtype=torch.bfloat16, device=DEV),
+                            torch.zeros((4, 0, 256), dtype=torch.bfloat16, device=DEV), 2)
+    torch.cuda.synchronize()
+    assert dw.shape == (2, 128, 256) and (dw == 0).all()     # an empty reduction is zero

@@ -159,3 +159,14 @@ def test_all_to_allv_peer_memory_virtual_ranks():
     for r in range(W):
         np.testing.assert_array_equal(ops[r].recv_view(xs[r]).cpu().numpy(), want[r])
         np.testing.assert_array_equal(ops[r].counts_view().cpu().numpy().astype(np.uint64), want_rc[r])
+
+
+def test_peer_dispatch_rejects_unaligned_rows():
+    """Rows that are not a multiple of 16 bytes cannot take the 16-byte peer stores: reported, not launched."""
+    plan = LB.DistChunkedMoE(64, 12, 1, 1.0, 1, torch.float16, DEV, 2, fabric=LB.LocalFabric(1, 0, {}))
+    x = torch.zeros((64, 12), dtype=torch.float16, device=DEV)
+    gate = torch.softmax(torch.randn((64, 2), device=DEV), dim=1)
+    with pytest.raises(LB.LancetError) as ei:
+        plan.dispatch(x, gate)
+    assert ei.value.code == 1 and "16 bytes" in str(ei.value)
+    torch.cuda.synchronize()
