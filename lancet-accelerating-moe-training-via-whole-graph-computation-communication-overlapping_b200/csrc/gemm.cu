@@ -667,7 +667,7 @@ int lancet_grouped_gemm_tn(const void* A, const void* B, void* D, int groups, in
                  "lancet_grouped_gemm_tn: bad sizes groups=%d LE=%d C=%d Mout=%d N=%d", groups, LE, C, Mout, N);
   LANCET_REQUIRE(Mout % BM == 0 && N % BN == 0, LANCET_ERR_INVALID,
                  "lancet_grouped_gemm_tn: Mout=%d must be a multiple of %d and N=%d of %d", Mout, BM, N, BN);
-  LANCET_REQUIRE(A && B && D && status, LANCET_ERR_NULL, "lancet_grouped_gemm_tn: null pointer argument");
+  LANCET_REQUIRE(D && status && (C == 0 || (A && B)), LANCET_ERR_NULL, "lancet_grouped_gemm_tn: null pointer argument");
   LANCET_REQUIRE(aligned(A, 16) && aligned(B, 16) && aligned(D, 16), LANCET_ERR_INVALID,
                  "lancet_grouped_gemm_tn: operands must be 16-byte aligned");
   LANCET_REQUIRE((long long)groups * C < (1ll << 31) && (long long)LE * Mout < (1ll << 31), LANCET_ERR_INVALID,
