@@ -248,6 +248,30 @@ int lancet_moe_dispatch_chunked_p2p(const void* x, const void* gate, int gate_dt
                                     int32_t* idx_loc, int32_t* capused_chain, uint64_t* elems,
                                     void* const* peer_recv, void* const* peer_counts, void* ws, size_t ws_bytes,
                                     int flags, lancet_stream_t stream);
+/* Staged form of the call above, for running the exchange of chunk c+1 under the expert GEMMs of chunk c
+ * (the reference's chunk pipeline: src/pass/dist_optimization/partition_exprs.cc:1745-1757 partitions
+ * moe_encode / _all_to_all / experts, lancet_optimization.cc schedules them on two streams).
+ * 1. lancet_moe_gate_chunked_p2p gates all chunks and writes the chained row counts capused_chain
+ *    [n+1][E] into every owner's table peer_chain[owner] = int32 [W][n+1][LE] (block `rank`), so that the
+ *    owner knows before any row arrives where each chunk's rows of every block will lie.
+ * 2. lancet_moe_dispatch_rows_p2p scatters the rows of chunks [chunk_begin, chunk_end) (x [S][M] and
+ *    idx_loc [n][2k][Sp] are the whole arrays); follow each stage with lancet_p2p_barrier.
+ * 3. lancet_moe_stage_windows (on the owner, after the first barrier) turns its chain table into the row
+ *    windows of every stage, row_begin / row_end int32 [n][W*LE], aligned to row_align rows (128 for the
+ *    grouped GEMM): stage c covers the whole row_align-row tiles that have fully arrived with chunks 0..c and
+ *    that earlier stages did not cover; the last stage ends at the total.  counts (nullable, int32 [W*LE])
+ *    receives the totals.
+ * Combine, its backward and the dispatch backward run per chunk through the existing calls on sub-arrays
+ * (gates_s + c*k*Sp, idx_loc + c*2k*Sp, out + c*Sp*M, S = Sp, n_chunks = 1). */
+int lancet_moe_gate_chunked_p2p(const void* gate, int gate_dtype, float capacity_factor, int S, int M, int LE, int W,
+                                int rank, int k, int n_chunks, void* gates_s, int32_t* idx_loc,
+                                int32_t* capused_chain, uint64_t* elems, void* const* peer_chain, void* ws,
+                                size_t ws_bytes, lancet_stream_t stream);
+int lancet_moe_dispatch_rows_p2p(const void* x, const int32_t* idx_loc, int S, int M, int C, int LE, int W, int rank,
+                                 int k, int n_chunks, int chunk_begin, int chunk_end, int dtype,
+                                 void* const* peer_recv, lancet_stream_t stream);
+int lancet_moe_stage_windows(const int32_t* chain, int W, int LE, int n_chunks, int row_align, int32_t* row_begin,
+                             int32_t* row_end, int32_t* counts, lancet_stream_t stream);
 /* As lancet_moe_combine_chunked, gathering rows from the owners' expert output buffers.  With
  * gates_s == NULL every kept row has weight 1: the data gradient of dispatch (moe_encode_dx,
  * src/op/dialect/cuda/moe.cc:1108-1133) fused with the returning all-to-all. */
@@ -309,6 +333,18 @@ int lancet_grouped_gemm_nt(const void* A, const void* B, void* D, const void* bi
 int lancet_grouped_gemm_nn(const void* A, const void* B, void* D, const void* preact, int groups, int LE, int C,
                            int N, int K, const int32_t* counts, int act, int dtype, int32_t* status,
                            lancet_stream_t stream);
+/* Row-window forms of the two calls above for a pipelined exchange: group g is computed on rows
+ * [row_begin[g] rounded down to a multiple of 128, row_end[g]) only (device int32 [groups] each, row_begin
+ * nullable = 0); rows outside the window are not touched, except that rows from row_end[g] to the end of its
+ * 128-row tile are written as zeros.  Row results do not depend on the windows they are computed in.
+ * No reference counterpart: the reference runs one cuBLAS call per partition
+ * (src/pass/dist_optimization/partition_exprs.cc:1745-1757 splits the expert matmuls with the tokens). */
+int lancet_grouped_gemm_nt_window(const void* A, const void* B, void* D, const void* bias, void* preact, int groups,
+                                  int LE, int C, int N, int K, const int32_t* row_begin, const int32_t* row_end,
+                                  int act, int dtype, int32_t* status, lancet_stream_t stream);
+int lancet_grouped_gemm_nn_window(const void* A, const void* B, void* D, const void* preact, int groups, int LE,
+                                  int C, int N, int K, const int32_t* row_begin, const int32_t* row_end, int act,
+                                  int dtype, int32_t* status, lancet_stream_t stream);
 /* Weight gradient (the reference's dW = matmul_tn(a, dy), src/op/grad/gemm.cc:31-36), summed over the
  * source ranks of an expert: D[e] = sum over groups g with g % LE == e of A[g][:counts[g]]^T * B[g][:counts[g]];
  * A [groups][C][Mout], B [groups][C][N], D [LE][Mout][N].  Rows from counts[g] to the next multiple

@@ -119,6 +119,16 @@ SIGNATURES = {
     "lancet_moe_combine_bwd_p2p": (c_int, [c_void_p, c_void_p, c_void_p, ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p),
                                            c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                            c_void_p]),
+    "lancet_grouped_gemm_nt_window": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                              c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
+    "lancet_grouped_gemm_nn_window": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                              c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
+    "lancet_moe_gate_chunked_p2p": (c_int, [c_void_p, c_int, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                            c_void_p, c_void_p, c_void_p, c_void_p, ctypes.POINTER(c_void_p), c_void_p,
+                                            c_size_t, c_void_p]),
+    "lancet_moe_dispatch_rows_p2p": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                             c_int, c_int, c_int, ctypes.POINTER(c_void_p), c_void_p]),
+    "lancet_moe_stage_windows": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "lancet_grouped_bias_grad_workspace_bytes": (c_size_t, [c_int, c_int]),
     "lancet_grouped_bias_grad": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_size_t,
                                          c_void_p]),

@@ -31,7 +31,9 @@ constexpr int UMMA_K = 16;
 constexpr int A_STAGE_BYTES = BM * BK * 2;   // 16 KB
 constexpr int B_STAGE_BYTES = BN * BK * 2;   // 32 KB
 constexpr int SMEM_DATA = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES);
-constexpr int SMEM_BYTES = SMEM_DATA + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int MAX_GROUPS = 1024;              // row-parallel forms keep a per-group tile table in shared memory
+constexpr int SCHED_BYTES = (2 * MAX_GROUPS + 1) * 4;
+constexpr int SMEM_BYTES = SMEM_DATA + 1024 /*alignment slack*/ + 256 /*barriers*/ + SCHED_BYTES;
 constexpr int EPI_WARPS = 8;                 // two warps per TMEM lane quadrant, each takes half of the columns
 constexpr int THREADS = 64 + 32 * EPI_WARPS; // warps: 0 TMA, 1 MMA, 2.. epilogue
 constexpr int TMEM_COLS = 512;               // two accumulators of BN fp32 columns
@@ -49,7 +51,8 @@ struct Params {
   int groups, LE, C, N, K;
   int Mout;               // MODE_REDUCE: output rows per expert
   int m_tiles, n_tiles, tiles_per_group, total_tiles;
-  const int32_t* counts;  // [groups] live rows, or null
+  const int32_t* counts;  // [groups] live rows (end of the row window), or null
+  const int32_t* row_lo;  // [groups] first row of the window (rounded down to a tile boundary), or null; MODE_ROWS only
   const void* bias;       // [LE][N] or null
   void* D;
   void* preact;           // EPI_ACT: optional copy of the pre-activation; EPI_DACT: the saved pre-activation (input)
@@ -181,7 +184,6 @@ __device__ __forceinline__ float dactivate(float x, int act) {
 
 struct Tile {
   int group, mt, nt, rows;  // rows = live rows of the group
-  bool live;
 };
 
 // Number of 64-row reduction blocks of group g (MODE_REDUCE).
@@ -194,8 +196,22 @@ __device__ __forceinline__ int group_row_blocks(const Params& p, int g) {
   return (rows + BK - 1) / BK;
 }
 
+// Row-parallel forms walk a compacted list of the live tiles only: group g contributes the m-tiles
+// [lo[g], lo[g] + (pref[g+1] - pref[g])) of its row window, each times n_tiles column tiles, ordered
+// (group, band of BAND m-tiles, n-tile, m-tile in band) so that a band of A stays in L2 against a sweep of B.
+struct Sched {
+  const int* pref;  // [groups + 1] exclusive prefix of live m-tiles
+  const int* lo;    // [groups] first live m-tile
+  int g;            // group of the previous tile of this walker (tile indices only grow)
+};
+
 template <int MODE>
-__device__ __forceinline__ Tile decode_tile(const Params& p, int t) {
+__device__ __forceinline__ int live_tiles(const Params& p, const Sched& sc) {
+  return MODE == MODE_REDUCE ? p.total_tiles : sc.pref[p.groups] * p.n_tiles;
+}
+
+template <int MODE>
+__device__ __forceinline__ Tile decode_tile(const Params& p, Sched& sc, int t) {
   Tile tl;
   if (MODE == MODE_REDUCE) {
     // tiles_per_group = m_tiles * n_tiles per expert; `group` holds the expert index
@@ -204,24 +220,26 @@ __device__ __forceinline__ Tile decode_tile(const Params& p, int t) {
     tl.nt = r / p.m_tiles;
     tl.mt = r - tl.nt * p.m_tiles;
     tl.rows = p.Mout;
-    tl.live = true;
     return tl;
   }
-  tl.group = t / p.tiles_per_group;
-  int r = t - tl.group * p.tiles_per_group;
+  int g = sc.g;
+  while (t >= sc.pref[g + 1] * p.n_tiles) ++g;
+  sc.g = g;
+  tl.group = g;
+  int r = t - sc.pref[g] * p.n_tiles;
+  const int nm = sc.pref[g + 1] - sc.pref[g];
   const int band_tiles = BAND * p.n_tiles;
   const int band = r / band_tiles;
   r -= band * band_tiles;
-  const int m_in_band = min(BAND, p.m_tiles - band * BAND);
+  const int m_in_band = min(BAND, nm - band * BAND);
   tl.nt = r / m_in_band;
-  tl.mt = band * BAND + (r - tl.nt * m_in_band);
+  tl.mt = sc.lo[g] + band * BAND + (r - tl.nt * m_in_band);
   int rows = p.C;
   if (p.counts) {
-    rows = p.counts[tl.group];
+    rows = p.counts[g];
     rows = rows < 0 ? 0 : (rows > p.C ? p.C : rows);
   }
   tl.rows = rows;
-  tl.live = tl.nt < p.n_tiles && tl.mt * BM < rows;
   return tl;
 }
 
@@ -254,8 +272,43 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const uint32_t bar_tfull = smem_u32(bars + 2 * STAGES), bar_tempty = smem_u32(bars + 2 * STAGES + 2);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* s_pref = reinterpret_cast<int*>(smem + SMEM_DATA + 256);
+  int* s_lo = s_pref + MAX_GROUPS + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (MODE == MODE_ROWS && warp == 2) {
+    // live m-tiles of every group and their exclusive prefix (warp scan, 32 groups a round)
+    int carry = 0;
+    for (int base = 0; base < p.groups; base += 32) {
+      const int g = base + lane;
+      int lo = 0, nm = 0;
+      if (g < p.groups) {
+        int rows = p.C;
+        if (p.counts) {
+          rows = p.counts[g];
+          rows = rows < 0 ? 0 : (rows > p.C ? p.C : rows);
+        }
+        if (p.row_lo) {
+          lo = p.row_lo[g];
+          lo = (lo < 0 ? 0 : lo) / BM;
+        }
+        nm = (rows + BM - 1) / BM - lo;
+        nm = nm < 0 ? 0 : nm;
+      }
+      int incl = nm;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d) incl += v;
+      }
+      if (g < p.groups) {
+        s_pref[g] = carry + incl - nm;
+        s_lo[g] = lo;
+      }
+      carry += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) s_pref[p.groups] = carry;
+  }
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(bar_full + 8 * s, 1);
@@ -284,9 +337,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
-        const Tile tl = decode_tile<MODE>(p, t);
-        if (!tl.live) continue;
+      Sched sc{s_pref, s_lo, 0};
+      const int n_live = live_tiles<MODE>(p, sc);
+      for (int t = blockIdx.x; t < n_live && ok; t += gridDim.x) {
+        const Tile tl = decode_tile<MODE>(p, sc, t);
         if (MODE == MODE_ROWS) {
           const int e = tl.group % p.LE;
           const int a_row = tl.group * p.C + tl.mt * BM;
@@ -334,9 +388,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       int buf = 0;
       uint32_t tphase[2] = {0, 0};
       bool ok = true;
-      for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
-        const Tile tl = decode_tile<MODE>(p, t);
-        if (!tl.live) continue;
+      Sched sc{s_pref, s_lo, 0};
+      const int n_live = live_tiles<MODE>(p, sc);
+      for (int t = blockIdx.x; t < n_live && ok; t += gridDim.x) {
+        const Tile tl = decode_tile<MODE>(p, sc, t);
         // an empty reduction (weight-gradient form, all counts zero) still hands the accumulator over:
         // the epilogue masks its contents to zero
         const int k_blocks = tile_k_blocks<MODE>(p, tl);
@@ -375,9 +430,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     T* D = static_cast<T*>(p.D);
     T* PRE = static_cast<T*>(p.preact);
     const T* bias = static_cast<const T*>(p.bias);
-    for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
-      const Tile tl = decode_tile<MODE>(p, t);
-      if (!tl.live) continue;
+    Sched sc{s_pref, s_lo, 0};
+    const int n_live = live_tiles<MODE>(p, sc);
+    for (int t = blockIdx.x; t < n_live && ok; t += gridDim.x) {
+      const Tile tl = decode_tile<MODE>(p, sc, t);
       // row-parallel forms always reduce over K >= 1; only the weight-gradient form can meet an empty
       // reduction, whose accumulator holds stale values: they are masked to zero bit-wise (no branch in
       // the hot loop: extra control flow here made the compiler serialise the epilogue)
@@ -597,6 +653,7 @@ static int rows_common(const char* fn, const void* A, const void* B, void* D, in
                  "%s: inputs must be bfloat16 or float16 (dtype code %d)", fn, dtype);
   LANCET_REQUIRE(groups >= 1 && LE >= 1 && groups % LE == 0 && C >= 0 && N >= 1 && K >= 1, LANCET_ERR_INVALID,
                  "%s: bad sizes groups=%d LE=%d C=%d N=%d K=%d", fn, groups, LE, C, N, K);
+  LANCET_REQUIRE(groups <= MAX_GROUPS, LANCET_ERR_INVALID, "%s: at most %d groups (got %d)", fn, MAX_GROUPS, groups);
   LANCET_REQUIRE(N % BN == 0 && K % 8 == 0, LANCET_ERR_INVALID, "%s: N=%d must be a multiple of %d and K=%d a multiple of 8",
                  fn, N, BN, K);
   LANCET_REQUIRE(act >= 0 && act <= 3, LANCET_ERR_INVALID, "%s: unknown activation %d", fn, act);
@@ -614,6 +671,7 @@ static int rows_common(const char* fn, const void* A, const void* B, void* D, in
   p->total_tiles = (int)total;
   p->status = status;
   p->act = act;
+  p->row_lo = nullptr;
   return LANCET_OK;
 }
 
@@ -623,23 +681,35 @@ static int rows_common(const char* fn, const void* A, const void* B, void* D, in
 extern "C" {
 using namespace lancet;
 
-int lancet_grouped_gemm_nt(const void* A, const void* B, void* D, const void* bias, void* preact, int groups, int LE,
-                           int C, int N, int K, const int32_t* counts, int act, int dtype, int32_t* status,
-                           lancet_stream_t stream) {
+int lancet_grouped_gemm_nt_window(const void* A, const void* B, void* D, const void* bias, void* preact, int groups, int LE,
+                                  int C, int N, int K, const int32_t* row_begin, const int32_t* row_end, int act, int dtype,
+                                  int32_t* status, lancet_stream_t stream) {
   using namespace lancet::gemm;
   Params p;
   if (int rc = rows_common("lancet_grouped_gemm_nt", A, B, D, groups, LE, C, N, K, act, dtype, status, &p)) return rc;
   if (C == 0) return LANCET_OK;
   LANCET_REQUIRE(aligned(bias, 2) && aligned(preact, 16), LANCET_ERR_INVALID, "lancet_grouped_gemm_nt: bias/preact alignment");
-  p.counts = counts; p.bias = bias; p.D = D; p.preact = preact; p.epi = EPI_ACT;
+  p.counts = row_end; p.row_lo = row_begin; p.bias = bias; p.D = D; p.preact = preact; p.epi = EPI_ACT;
   CUtensorMap tmA, tmB;
   if (int rc = make_map(&tmA, A, (uint64_t)groups * C, (uint64_t)K, BM, dtype)) return rc;
   if (int rc = make_map(&tmB, B, (uint64_t)LE * N, (uint64_t)K, BN, dtype)) return rc;
   return launch<MODE_ROWS, false, EPI_ACT>(tmA, tmB, p, dtype, "grouped_gemm_nt_kernel", static_cast<cudaStream_t>(stream));
 }
 
+int lancet_grouped_gemm_nt(const void* A, const void* B, void* D, const void* bias, void* preact, int groups, int LE,
+                           int C, int N, int K, const int32_t* counts, int act, int dtype, int32_t* status,
+                           lancet_stream_t stream) {
+  return lancet_grouped_gemm_nt_window(A, B, D, bias, preact, groups, LE, C, N, K, nullptr, counts, act, dtype, status, stream);
+}
+
 int lancet_grouped_gemm_nn(const void* A, const void* B, void* D, const void* preact, int groups, int LE, int C, int N,
                            int K, const int32_t* counts, int act, int dtype, int32_t* status, lancet_stream_t stream) {
+  return lancet_grouped_gemm_nn_window(A, B, D, preact, groups, LE, C, N, K, nullptr, counts, act, dtype, status, stream);
+}
+
+int lancet_grouped_gemm_nn_window(const void* A, const void* B, void* D, const void* preact, int groups, int LE, int C, int N,
+                                  int K, const int32_t* row_begin, const int32_t* counts, int act, int dtype, int32_t* status,
+                                  lancet_stream_t stream) {
   using namespace lancet::gemm;
   Params p;
   if (int rc = rows_common("lancet_grouped_gemm_nn", A, B, D, groups, LE, C, N, K, act, dtype, status, &p)) return rc;
@@ -647,7 +717,7 @@ int lancet_grouped_gemm_nn(const void* A, const void* B, void* D, const void* pr
   LANCET_REQUIRE(K % BK == 0, LANCET_ERR_INVALID, "lancet_grouped_gemm_nn: K=%d must be a multiple of %d", K, BK);
   LANCET_REQUIRE(act == 0 || preact, LANCET_ERR_NULL, "lancet_grouped_gemm_nn: an activation derivative needs the saved pre-activation");
   LANCET_REQUIRE(aligned(preact, 16), LANCET_ERR_INVALID, "lancet_grouped_gemm_nn: preact must be 16-byte aligned");
-  p.counts = counts; p.bias = nullptr; p.D = D; p.preact = const_cast<void*>(preact);
+  p.counts = counts; p.row_lo = row_begin; p.bias = nullptr; p.D = D; p.preact = const_cast<void*>(preact);
   p.epi = (act != 0) ? EPI_DACT : EPI_ACT;
   if (act == 0) p.preact = nullptr;
   CUtensorMap tmA, tmB;
@@ -677,7 +747,8 @@ int lancet_grouped_gemm_tn(const void* A, const void* B, void* D, int groups, in
   p.m_tiles = Mout / BM; p.n_tiles = N / BN;
   p.tiles_per_group = p.m_tiles * p.n_tiles;
   p.total_tiles = p.tiles_per_group * LE;
-  p.counts = counts; p.bias = nullptr; p.D = D; p.preact = nullptr; p.act = 0; p.epi = EPI_ACT; p.status = status;
+  p.counts = counts; p.row_lo = nullptr; p.bias = nullptr; p.D = D; p.preact = nullptr; p.act = 0; p.epi = EPI_ACT;
+  p.status = status;
   CUtensorMap tmA, tmB;
   if (C == 0) {
     LANCET_CUDA(cudaMemsetAsync(D, 0, (size_t)LE * Mout * N * 2, static_cast<cudaStream_t>(stream)));

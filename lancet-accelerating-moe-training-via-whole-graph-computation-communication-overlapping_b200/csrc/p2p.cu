@@ -259,6 +259,35 @@ __global__ void p2p_barrier_kernel(PeerTable flags, int W, int my_rank, unsigned
   __threadfence_system();
 }
 
+// Staged exchange: every rank tells the owners, before the first row travels, how the rows of its block
+// will arrive: tables.ptr[owner] is int32 [W][n1][LE], entry (source, c, le) = rows of (source, expert) placed
+// by the chunks before c (n1 = n_chunks + 1 entries; the last is the total).
+__global__ void publish_chain_kernel(const int32_t* __restrict__ chain, PeerTable tables, int n1, int E, int LE, int my_rank) {
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n1 * E; i += gridDim.x * blockDim.x) {
+    const int c = i / E, e = i - c * E;
+    const int owner = e / LE, le = e - owner * LE;
+    static_cast<int32_t*>(tables.ptr[owner])[((size_t)my_rank * n1 + c) * LE + le] = chain[i];
+  }
+}
+
+// Row windows of the pipeline stages on the owner's side.  Stage c may work on the rows of group g = (source, le)
+// that have arrived with chunks 0..c and form whole tiles of `align` rows: [begin, end) with
+// begin = floor(chain[c] / align) * align, end = floor(chain[c+1] / align) * align; the last stage ends at the total.
+__global__ void stage_windows_kernel(const int32_t* __restrict__ chain, int W, int LE, int n, int align,
+                                     int32_t* __restrict__ row_begin, int32_t* __restrict__ row_end,
+                                     int32_t* __restrict__ counts) {
+  const int G = W * LE, n1 = n + 1;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n * G; i += gridDim.x * blockDim.x) {
+    const int c = i / G, g = i - c * G;
+    const int src = g / LE, le = g - src * LE;
+    const int32_t* col = chain + (size_t)src * n1 * LE + le;
+    const int lo = col[(size_t)c * LE], hi = col[(size_t)(c + 1) * LE];
+    row_begin[i] = c == 0 ? 0 : lo / align * align;
+    row_end[i] = c == n - 1 ? hi : hi / align * align;
+    if (c == 0 && counts) counts[g] = col[(size_t)n * LE];
+  }
+}
+
 static int p2p_grid(long long tasks) {
   long long ctas = (tasks + kP2PWarps - 1) / kP2PWarps;
   const long long cap = (long long)sm_count() * 8;
@@ -429,6 +458,90 @@ int lancet_moe_dispatch_chunked_p2p(const void* x, const void* gate, int gate_dt
     dispatch_rows_peer_kernel<uint4, 2><<<p2p_grid(tasks), kP2PThreads, 0, st>>>(
         idx_loc, used, static_cast<const uint4*>(x), t, tc, S, Sp > 0 ? Sp : 1, row_vecs, C, E, LE, rank, zero_tail);
   return launch_status("dispatch_rows_peer_kernel");
+}
+
+int lancet_moe_gate_chunked_p2p(const void* gate, int gate_dtype, float capacity_factor, int S, int M, int LE, int W, int rank,
+                                int k, int n_chunks, void* gates_s, int32_t* idx_loc, int32_t* capused_chain, uint64_t* elems,
+                                void* const* peer_chain, void* ws, size_t ws_bytes, lancet_stream_t stream) {
+  LANCET_REQUIRE(W >= 1 && W <= kMaxPeers && rank >= 0 && rank < W && LE >= 1, LANCET_ERR_INVALID,
+                 "lancet_moe_gate_chunked_p2p: bad world %d / rank %d / local experts %d", W, rank, LE);
+  LANCET_REQUIRE(n_chunks >= 1 && S >= 0 && S % n_chunks == 0, LANCET_ERR_INVALID,
+                 "lancet_moe_gate_chunked_p2p: S=%d is not divisible into %d chunks", S, n_chunks);
+  LANCET_REQUIRE((k == 1 || k == 2) && M >= 0 && valid_dtype(gate_dtype), LANCET_ERR_INVALID,
+                 "lancet_moe_gate_chunked_p2p: bad k=%d, M=%d or dtype", k, M);
+  LANCET_REQUIRE(peer_chain && capused_chain && elems && ws && (S == 0 || (gate && gates_s && idx_loc)), LANCET_ERR_NULL,
+                 "lancet_moe_gate_chunked_p2p: null pointer argument");
+  const int E = LE * W;
+  const int Sp = S / n_chunks;
+  const int C = lancet_moe_capacity(Sp, E, capacity_factor * n_chunks, k);
+  LANCET_REQUIRE(C >= 0 && (long long)E * C < (1ll << 31), LANCET_ERR_INVALID,
+                 "lancet_moe_gate_chunked_p2p: capacity %d out of range", C);
+  LANCET_REQUIRE(E >= k && k * E <= 1024 && (long long)n_chunks * k * E <= 8192, LANCET_ERR_INVALID,
+                 "lancet_moe_gate_chunked_p2p: k*E=%d or n_chunks*k*E too large", k * E);
+  LANCET_REQUIRE(ws_bytes >= gate_workspace_bytes(S, E, k, n_chunks) && aligned(ws, 16), LANCET_ERR_INVALID,
+                 "lancet_moe_gate_chunked_p2p: workspace too small or unaligned");
+  PeerTable t;
+  for (int i = 0; i < kMaxPeers; ++i) t.ptr[i] = i < W ? peer_chain[i] : nullptr;
+  for (int i = 0; i < W; ++i)
+    LANCET_REQUIRE(t.ptr[i] && aligned(t.ptr[i], 4), LANCET_ERR_NULL, "lancet_moe_gate_chunked_p2p: chain table %d is null or unaligned", i);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int rc = gate_launch(gate, gate_dtype, S, E, k, n_chunks, nullptr, C, M, gates_s, LANCET_F32, idx_loc, capused_chain + E,
+                       elems, ws, 1, st, capused_chain);
+  if (rc != LANCET_OK) return rc;
+  const int n1 = n_chunks + 1;
+  publish_chain_kernel<<<1, 256, 0, st>>>(capused_chain, t, n1, E, LE, rank);
+  return launch_status("publish_chain_kernel");
+}
+
+int lancet_moe_dispatch_rows_p2p(const void* x, const int32_t* idx_loc, int S, int M, int C, int LE, int W, int rank, int k,
+                                 int n_chunks, int chunk_begin, int chunk_end, int dtype, void* const* peer_recv,
+                                 lancet_stream_t stream) {
+  LANCET_REQUIRE(W >= 1 && W <= kMaxPeers && rank >= 0 && rank < W && LE >= 1, LANCET_ERR_INVALID,
+                 "lancet_moe_dispatch_rows_p2p: bad world %d / rank %d / local experts %d", W, rank, LE);
+  LANCET_REQUIRE(n_chunks >= 1 && S >= 0 && S % n_chunks == 0, LANCET_ERR_INVALID,
+                 "lancet_moe_dispatch_rows_p2p: S=%d is not divisible into %d chunks", S, n_chunks);
+  LANCET_REQUIRE(chunk_begin >= 0 && chunk_begin <= chunk_end && chunk_end <= n_chunks, LANCET_ERR_INVALID,
+                 "lancet_moe_dispatch_rows_p2p: bad chunk range [%d, %d) of %d", chunk_begin, chunk_end, n_chunks);
+  LANCET_REQUIRE((k == 1 || k == 2) && M >= 0 && C >= 0 && valid_dtype(dtype), LANCET_ERR_INVALID,
+                 "lancet_moe_dispatch_rows_p2p: bad k=%d, M=%d, C=%d or dtype", k, M, C);
+  const int E = LE * W, Sp = S / n_chunks;
+  LANCET_REQUIRE((long long)E * C < (1ll << 31), LANCET_ERR_INVALID, "lancet_moe_dispatch_rows_p2p: capacity %d out of range", C);
+  const long long tokens = (long long)(chunk_end - chunk_begin) * Sp;
+  if (tokens == 0 || M == 0 || C == 0) return LANCET_OK;
+  LANCET_REQUIRE(x && idx_loc && peer_recv, LANCET_ERR_NULL, "lancet_moe_dispatch_rows_p2p: null pointer argument");
+  const size_t row_bytes = (size_t)M * dtype_bytes(dtype);
+  LANCET_REQUIRE(row_bytes % 16 == 0 && aligned(x, 16), LANCET_ERR_INVALID,
+                 "lancet_moe_dispatch_rows_p2p: rows must be a multiple of 16 bytes and 16-byte aligned");
+  PeerTable t, none;
+  for (int i = 0; i < kMaxPeers; ++i) {
+    t.ptr[i] = i < W ? peer_recv[i] : nullptr;
+    none.ptr[i] = nullptr;
+  }
+  for (int i = 0; i < W; ++i)
+    LANCET_REQUIRE(t.ptr[i] && aligned(t.ptr[i], 16), LANCET_ERR_NULL, "lancet_moe_dispatch_rows_p2p: peer buffer %d is null or unaligned", i);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int row_vecs = (int)(row_bytes / 16);
+  const uint4* xs = static_cast<const uint4*>(x) + (size_t)chunk_begin * Sp * row_vecs;
+  const int32_t* il = idx_loc + (size_t)chunk_begin * 2 * k * Sp;
+  ProfScope prof("dispatch_rows_peer_kernel", st);
+  if (k == 1)
+    dispatch_rows_peer_kernel<uint4, 1><<<p2p_grid(tokens), kP2PThreads, 0, st>>>(il, nullptr, xs, t, none, (int)tokens, Sp,
+                                                                                 row_vecs, C, E, LE, rank, 0);
+  else
+    dispatch_rows_peer_kernel<uint4, 2><<<p2p_grid(tokens), kP2PThreads, 0, st>>>(il, nullptr, xs, t, none, (int)tokens, Sp,
+                                                                                 row_vecs, C, E, LE, rank, 0);
+  return launch_status("dispatch_rows_peer_kernel");
+}
+
+int lancet_moe_stage_windows(const int32_t* chain, int W, int LE, int n_chunks, int row_align, int32_t* row_begin,
+                             int32_t* row_end, int32_t* counts, lancet_stream_t stream) {
+  LANCET_REQUIRE(W >= 1 && W <= kMaxPeers && LE >= 1 && n_chunks >= 1 && row_align >= 1, LANCET_ERR_INVALID,
+                 "lancet_moe_stage_windows: bad world %d / local experts %d / chunks %d / alignment %d", W, LE, n_chunks, row_align);
+  LANCET_REQUIRE(chain && row_begin && row_end, LANCET_ERR_NULL, "lancet_moe_stage_windows: null pointer argument");
+  const int total = n_chunks * W * LE;
+  stage_windows_kernel<<<(total + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(chain, W, LE, n_chunks, row_align,
+                                                                                          row_begin, row_end, counts);
+  return launch_status("stage_windows_kernel");
 }
 
 int lancet_moe_combine_chunked_p2p(void* const* peer_expert_out, const void* gates_s, const int32_t* idx_loc, int S, int M,

@@ -126,7 +126,8 @@ class DistChunkedMoE:
         cnt_bytes = _up(self.W * self.LE * 4)
         self.train = train
         n_regions = 5 if train else 3            # recv x2, expert_out, and for training d_expert_out, d_expert_in
-        total = n_regions * self.recv_bytes + flag_bytes + 2 * cnt_bytes
+        chain_bytes = _up(self.W * (n_chunks + 1) * self.LE * 4)
+        total = n_regions * self.recv_bytes + flag_bytes + 2 * cnt_bytes + 2 * chain_bytes
         bases = self.fabric.alloc(total)
         mk = lambda off: (ctypes.c_void_p * 16)(*[b + off for b in bases])
         self.peer_recv = [mk(0), mk(self.recv_bytes)]
@@ -136,6 +137,8 @@ class DistChunkedMoE:
         self.peer_flags = mk(n_regions * self.recv_bytes)
         cnt_off = n_regions * self.recv_bytes + flag_bytes
         self.peer_counts = [mk(cnt_off), mk(cnt_off + cnt_bytes)]
+        chain_off = cnt_off + 2 * cnt_bytes
+        self.peer_chain = [mk(chain_off), mk(chain_off + chain_bytes)]
         self.base = bases[self.rank]
         d = self.device
         self.gates_s = torch.empty((n_chunks, k, self.Sp), dtype=torch.float32, device=d)
@@ -161,6 +164,12 @@ class DistChunkedMoE:
             self.dx = torch.empty((S, M), dtype=dtype, device=d)
         self.counts = [tensor_from_ptr(self.base + cnt_off + i * cnt_bytes, (self.W * self.LE,), torch.int32, d)
                        for i in range(2)]
+        # staged (pipelined) exchange: the owners' view of how each chunk's rows arrive, and the row windows per stage
+        G = self.W * self.LE
+        self.chain = [tensor_from_ptr(self.base + chain_off + i * chain_bytes, (self.W, n_chunks + 1, self.LE),
+                                      torch.int32, d) for i in range(2)]
+        self.win_begin = torch.zeros((n_chunks, G), dtype=torch.int32, device=d)
+        self.win_end = torch.zeros((n_chunks, G), dtype=torch.int32, device=d)
         if self.fabric.real and self.W > 1:
             torch.cuda.synchronize(d)
             self.fabric.dist.barrier(group=self.fabric.group)
@@ -211,6 +220,61 @@ class DistChunkedMoE:
             self.n, _DT[self.dtype], _ptr(out), _stream(out)))
         return out
 
+    # -- staged exchange: chunk c+1 travels while the experts work on chunk c ---------------------
+    def stage_gate(self, gate):
+        """Gate all chunks and tell every owner where each chunk's rows of this rank's blocks will lie."""
+        self.parity ^= 1
+        check(_capi.lib().lancet_moe_gate_chunked_p2p(
+            _ptr(gate), _DT[gate.dtype], self.cf, self.S, self.M, self.LE, self.W, self.rank, self.k, self.n,
+            _ptr(self.gates_s), _ptr(self.idx_loc), _ptr(self.capused), _ptr(self.elems), self.peer_chain[self.parity],
+            _ptr(self.ws), self.ws.numel(), _stream(gate)))
+
+    def stage_dispatch(self, x, c):
+        """Scatter the rows of chunk c into the owners' receive buffers (follow with barrier())."""
+        check(_capi.lib().lancet_moe_dispatch_rows_p2p(
+            _ptr(x), _ptr(self.idx_loc), self.S, self.M, self.C, self.LE, self.W, self.rank, self.k, self.n, c, c + 1,
+            _DT[x.dtype], self.peer_recv[self.parity], _stream(x)))
+
+    def stage_prepare(self, buf=None):
+        """After the first barrier of a pass: row windows of every stage, row totals, zero-fill of the rows of
+        `buf` (default: the receive buffer) that no token owns.  Returns (win_begin, win_end, counts)."""
+        L = _capi.lib()
+        cnt = self.counts[self.parity]
+        if buf is None:
+            buf = self.recv[self.parity]
+            check(L.lancet_moe_stage_windows(_ptr(self.chain[self.parity]), self.W, self.LE, self.n, 128,
+                                             _ptr(self.win_begin), _ptr(self.win_end), _ptr(cnt), _stream(cnt)))
+        check(L.lancet_moe_zero_tail(_ptr(buf), _ptr(cnt), self.M, self.C, self.W * self.LE, _DT[self.dtype], _stream(cnt)))
+        return self.win_begin, self.win_end, cnt
+
+    def _chunk_views(self, c):
+        return self.gates_s[c], self.idx_loc[c]
+
+    def stage_combine(self, c, out=None):
+        """Combine the tokens of chunk c from the owners' expert outputs (rows must be complete: see MoELayer)."""
+        out = self.out if out is None else out
+        g, il = self._chunk_views(c)
+        o = out[c * self.Sp:(c + 1) * self.Sp]
+        check(_capi.lib().lancet_moe_combine_chunked_p2p(
+            self.peer_eo, _ptr(g), _ptr(il), self.Sp, self.M, self.C, self.LE, self.W, self.rank, self.k, 1,
+            _DT[self.dtype], _ptr(o), _stream(o)))
+        return o
+
+    def stage_combine_backward(self, dout, c):
+        g, il = self._chunk_views(c)
+        d = dout[c * self.Sp:(c + 1) * self.Sp]
+        check(_capi.lib().lancet_moe_combine_bwd_p2p(
+            _ptr(d), _ptr(g), _ptr(il), self.peer_deo, self.peer_eo, _ptr(self.dgates[c]), self.Sp, self.M, self.C,
+            self.LE, self.W, self.rank, self.k, 1, _DT[self.dtype], _stream(d)))
+
+    def stage_dispatch_backward(self, c):
+        _, il = self._chunk_views(c)
+        o = self.dx[c * self.Sp:(c + 1) * self.Sp]
+        check(_capi.lib().lancet_moe_combine_chunked_p2p(
+            self.peer_dxe, None, _ptr(il), self.Sp, self.M, self.C, self.LE, self.W, self.rank, self.k, 1,
+            _DT[self.dtype], _ptr(o), _stream(o)))
+        return o
+
     # -- backward ------------------------------------------------------------------------------
     def combine_backward_send(self, dout):
         """Backward of combine, fused with the exchange: gate-weighted rows of dout go to the owners'
@@ -241,6 +305,6 @@ class DistChunkedMoE:
 
     def close(self):
         torch.cuda.synchronize(self.device)
-        self.recv, self.expert_out, self.counts = None, None, None
+        self.recv, self.expert_out, self.counts, self.chain = None, None, None, None
         self.d_expert_out, self.d_expert_in = None, None
         self.fabric.close()

@@ -55,6 +55,116 @@ class MoELayer:
         self.fwd_experts()
         return self.fwd_combine()
 
+    # ---- pipelined forward: the rows of chunk c+1 cross NVLink while the experts work on chunk c --------
+    # Stage c of the expert GEMMs covers the whole 128-row tiles of every (source, expert) block that have arrived
+    # with chunks 0..c, so no tile is computed twice and none is padded; the rows of chunk c are therefore complete
+    # after stage c+1 (or the last stage), which is when its tokens are combined.  The stage methods below are the
+    # units; `forward_pipelined` issues them on two streams.  Results are bit-identical to `forward`.
+    def fwd_gate(self, x, gate):
+        self._x = x
+        self.moe.stage_gate(gate)
+
+    def fwd_stage_dispatch(self, c):
+        self.moe.stage_dispatch(self._x, c)
+
+    def fwd_prepare(self):
+        self.win_begin, self.win_end, self.cnt = self.moe.stage_prepare()
+        self.x_e = self.moe.recv[self.moe.parity].view(self.G, self.C, self.M)
+
+    def fwd_stage_experts(self, c):
+        lo, hi = self.win_begin[c], self.win_end[c]
+        ops.grouped_gemm_nt(self.x_e, self.w1, bias=self.b1, counts=hi, row_begin=lo, act=self.act, out=self.h,
+                            preact=self.hpre)
+        ops.grouped_gemm_nt(self.h, self.w2, bias=self.b2, counts=hi, row_begin=lo,
+                            out=self.moe.expert_out.view(self.G, self.C, self.M))
+
+    def fwd_stage_combine(self, c):
+        return self.moe.stage_combine(c)
+
+    def _streams(self):
+        if getattr(self, "comm", None) is None:
+            self.comm = torch.cuda.Stream(device=self.device)
+        return torch.cuda.current_stream(self.device), self.comm
+
+    def forward_pipelined(self, x, gate):
+        n = self.moe.n
+        main, comm = self._streams()
+        self.fwd_gate(x, gate)
+        comm.wait_stream(main)
+        arrived = []
+        with torch.cuda.stream(comm):
+            for c in range(n):
+                self.fwd_stage_dispatch(c)
+                self.moe.barrier()
+                arrived.append(comm.record_event())
+        main.wait_event(arrived[0])
+        self.fwd_prepare()
+        for c in range(n):
+            main.wait_event(arrived[c])
+            self.fwd_stage_experts(c)
+            done = main.record_event()
+            if c >= 1 or n == 1:
+                with torch.cuda.stream(comm):
+                    comm.wait_event(done)
+                    self.moe.barrier()
+                    if n > 1:
+                        self.fwd_stage_combine(c - 1)
+                    if c == n - 1:
+                        self.fwd_stage_combine(c)
+        main.wait_stream(comm)
+        return self.moe.out
+
+    # ---- pipelined backward ----
+    def bwd_stage_combine(self, dout, c):
+        self.moe.stage_combine_backward(dout, c)
+
+    def bwd_prepare(self):
+        self.moe.stage_prepare(self.moe.d_expert_out)
+        self.dy = self.moe.d_expert_out.view(self.G, self.C, self.M)
+
+    def bwd_stage_experts(self, c):
+        lo, hi = self.win_begin[c], self.win_end[c]
+        ops.grouped_gemm_nn(self.dy, self.w2, counts=hi, row_begin=lo, act=self.act, preact=self.hpre, out=self.dh)
+        ops.grouped_gemm_nn(self.dh, self.w1, counts=hi, row_begin=lo, out=self.moe.d_expert_in.view(self.G, self.C, self.M))
+
+    def bwd_weights(self):
+        ops.grouped_gemm_tn(self.dy, self.h, self.LE, counts=self.cnt, out=self.dw2)
+        ops.grouped_gemm_tn(self.dh, self.x_e, self.LE, counts=self.cnt, out=self.dw1)
+        ops.grouped_bias_grad(self.dy, self.LE, counts=self.cnt, out=self.db2)
+        ops.grouped_bias_grad(self.dh, self.LE, counts=self.cnt, out=self.db1)
+
+    def bwd_stage_dispatch(self, c):
+        return self.moe.stage_dispatch_backward(c)
+
+    def backward_pipelined(self, dout):
+        n = self.moe.n
+        main, comm = self._streams()
+        comm.wait_stream(main)
+        arrived = []
+        with torch.cuda.stream(comm):
+            for c in range(n):
+                self.bwd_stage_combine(dout, c)
+                self.moe.barrier()
+                arrived.append(comm.record_event())
+        main.wait_event(arrived[0])
+        self.bwd_prepare()
+        for c in range(n):
+            main.wait_event(arrived[c])
+            self.bwd_stage_experts(c)
+            done = main.record_event()
+            if c >= 1 or n == 1:
+                with torch.cuda.stream(comm):
+                    comm.wait_event(done)
+                    self.moe.barrier()
+                    if n > 1:
+                        self.bwd_stage_dispatch(c - 1)
+                    if c == n - 1:
+                        self.bwd_stage_dispatch(c)
+        # the weight gradients have no consumer before the optimizer: they run under the last gathers
+        self.bwd_weights()
+        main.wait_stream(comm)
+        return self.moe.dx, self.moe.dgates
+
     # ---- backward ----
     def bwd_combine(self, dout):
         self.moe.combine_backward_send(dout)

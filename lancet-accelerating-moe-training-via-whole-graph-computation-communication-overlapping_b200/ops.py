@@ -255,13 +255,14 @@ def gemm_status(device):
     return st
 
 
-def grouped_gemm_nt(a, b, bias=None, counts=None, act=None, out=None, preact=None):
+def grouped_gemm_nt(a, b, bias=None, counts=None, act=None, out=None, preact=None, row_begin=None):
     """Expert FFN GEMM: out[g] = act(a[g] @ b[g % LE].T + bias[g % LE]).
 
     a [groups, C, K], b [LE, N, K] (the nn.Linear weight layout of Experts.forward,
     models/benchmark/pytorch/utils.py:546-562 of the reference), bias [LE, N], counts int32 [groups]
-    (live rows per group; rows past them are neither computed nor written)."""
-    _require_cuda(a, b, bias, counts, out, preact)
+    (live rows per group; rows past them are neither computed nor written).  With row_begin (int32 [groups])
+    only the rows [row_begin[g] rounded down to 128, counts[g]) of every group are computed (pipeline stages)."""
+    _require_cuda(a, b, bias, counts, out, preact, row_begin)
     groups, C, K = a.shape
     LE, N, K2 = b.shape
     if K2 != K or groups % LE:
@@ -270,14 +271,16 @@ def grouped_gemm_nt(a, b, bias=None, counts=None, act=None, out=None, preact=Non
         raise TypeError("grouped_gemm_nt: bfloat16 or float16 operands of one type")
     out = torch.empty((groups, C, N), dtype=a.dtype, device=a.device) if out is None else out
     st = gemm_status(a.device)
-    check(_capi.lib().lancet_grouped_gemm_nt(_ptr(a), _ptr(b), _ptr(out), _ptr(bias), _ptr(preact), groups, LE, C, N, K,
-                                             _ptr(counts), ACT[act], _dt(a), _ptr(st), _stream(a)))
+    check(_capi.lib().lancet_grouped_gemm_nt_window(_ptr(a), _ptr(b), _ptr(out), _ptr(bias), _ptr(preact), groups, LE, C, N,
+                                                    K, _ptr(row_begin), _ptr(counts), ACT[act], _dt(a), _ptr(st),
+                                                    _stream(a)))
     return out
 
 
-def grouped_gemm_nn(a, b, counts=None, act=None, preact=None, out=None):
-    """Data gradient: out[g] = (a[g] @ b[g % LE]) * act'(preact[g]); a [groups, C, K], b [LE, K, N]."""
-    _require_cuda(a, b, counts, out, preact)
+def grouped_gemm_nn(a, b, counts=None, act=None, preact=None, out=None, row_begin=None):
+    """Data gradient: out[g] = (a[g] @ b[g % LE]) * act'(preact[g]); a [groups, C, K], b [LE, K, N].
+    row_begin as in grouped_gemm_nt."""
+    _require_cuda(a, b, counts, out, preact, row_begin)
     groups, C, K = a.shape
     LE, K2, N = b.shape
     if K2 != K or groups % LE:
@@ -286,8 +289,8 @@ def grouped_gemm_nn(a, b, counts=None, act=None, preact=None, out=None):
         raise TypeError("grouped_gemm_nn: bfloat16 or float16 operands of one type")
     out = torch.empty((groups, C, N), dtype=a.dtype, device=a.device) if out is None else out
     st = gemm_status(a.device)
-    check(_capi.lib().lancet_grouped_gemm_nn(_ptr(a), _ptr(b), _ptr(out), _ptr(preact), groups, LE, C, N, K, _ptr(counts),
-                                             ACT[act], _dt(a), _ptr(st), _stream(a)))
+    check(_capi.lib().lancet_grouped_gemm_nn_window(_ptr(a), _ptr(b), _ptr(out), _ptr(preact), groups, LE, C, N, K,
+                                                    _ptr(row_begin), _ptr(counts), ACT[act], _dt(a), _ptr(st), _stream(a)))
     return out
 
 

@@ -180,3 +180,48 @@ def test_gemm_empty_groups_and_zero_capacity():
                             torch.zeros((4, 0, 256), dtype=torch.bfloat16, device=DEV), 2)
     torch.cuda.synchronize()
     assert dw.shape == (2, 128, 256) and (dw == 0).all()     # an empty reduction is zero
+
+
+@pytest.mark.parametrize("groups,LE,C,N,K,stages", [(8, 2, 1000, 512, 256, 4), (3, 1, 300, 256, 64, 3), (40, 2, 130, 256, 128, 2)])
+def test_row_windows_tile_the_full_product(groups, LE, C, N, K, stages):
+    """Stages over disjoint row windows reproduce the one-call result bit for bit and touch nothing outside
+    their window (plus the zeroed rest of the last tile)."""
+    g = torch.Generator(device=DEV).manual_seed(groups * 7 + stages)
+    a = torch.randn((groups, C, K), device=DEV, generator=g).bfloat16()
+    b = (torch.randn((LE, N, K), device=DEV, generator=g) * 0.1).bfloat16()
+    bias = torch.randn((LE, N), device=DEV, generator=g).bfloat16()
+    counts = torch.randint(0, C + 1, (groups,), device=DEV, generator=g, dtype=torch.int32)
+    counts[0] = C
+    if groups > 2:
+        counts[2] = 0
+    full = torch.full((groups, C, N), 3.0, device=DEV, dtype=torch.bfloat16)
+    pre_full = torch.full_like(full, 3.0)
+    LB.grouped_gemm_nt(a, b, bias=bias, counts=counts, act="gelu", out=full, preact=pre_full)
+    # stage s ends at a random point of the live rows rounded down to a tile; the last one at the count
+    cuts = torch.sort(torch.rand((stages - 1, groups), device=DEV, generator=g), dim=0).values
+    ends = [(cuts[s] * counts).to(torch.int32) // 128 * 128 for s in range(stages - 1)] + [counts]
+    begins = [torch.zeros_like(counts)] + ends[:-1]
+    out = torch.full_like(full, 3.0)
+    pre = torch.full_like(full, 3.0)
+    for s in range(stages):
+        before = out.clone()
+        LB.grouped_gemm_nt(a, b, bias=bias, counts=ends[s].contiguous(), row_begin=begins[s].contiguous(), act="gelu", out=out,
+                           preact=pre)
+        lo, hi = begins[s].cpu().numpy(), ends[s].cpu().numpy()
+        changed = (out != before).any(dim=2).cpu().numpy()
+        for gi in range(groups):
+            rows = np.nonzero(changed[gi])[0]
+            if rows.size:
+                assert rows.min() >= lo[gi] and rows.max() < (hi[gi] + 127) // 128 * 128, (s, gi, rows.min(), rows.max())
+    assert torch.equal(out, full) and torch.equal(pre, pre_full)
+    # data-gradient form
+    w = (torch.randn((LE, K, N), device=DEV, generator=g) * 0.1).bfloat16()
+    dfull = torch.full((groups, C, N), 5.0, device=DEV, dtype=torch.bfloat16)
+    LB.grouped_gemm_nn(a, w, counts=counts, act="gelu", preact=pre_full, out=dfull) if K % 64 == 0 else None
+    if K % 64 == 0:
+        dout = torch.full_like(dfull, 5.0)
+        for s in range(stages):
+            LB.grouped_gemm_nn(a, w, counts=ends[s].contiguous(), row_begin=begins[s].contiguous(), act="gelu", preact=pre_full,
+                               out=dout)
+        assert torch.equal(dout, dfull)
+    check_status()

@@ -78,3 +78,112 @@ def test_layer_forward_backward(W, k, n):
         close(l.db2, b2[r].grad, "db2[%d]" % r)
     st = LB.gemm_status(torch.device(DEV))
     assert int(st.item()) == 0
+
+
+def _run_plain(layers, xs, gates, douts):
+    for r, l in enumerate(layers):
+        l.fwd_dispatch(xs[r], gates[r])
+    for l in layers:
+        l.fwd_experts()
+    outs = [l.fwd_combine().clone() for l in layers]
+    for r, l in enumerate(layers):
+        l.bwd_combine(douts[r])
+    for l in layers:
+        l.bwd_experts()
+    res = [tuple(t.clone() for t in l.bwd_dispatch()) for l in layers]
+    grads = [[t.clone() for t in (l.dw1, l.dw2, l.db1, l.db2)] for l in layers]
+    return outs, res, grads
+
+
+def _run_staged(layers, xs, gates, douts, n):
+    """The pipeline's units in an order a two-stream schedule can produce: exchange stage c+1 before expert stage c,
+    chunk c combined after expert stage c+1."""
+    for r, l in enumerate(layers):
+        l.fwd_gate(xs[r], gates[r])
+    for l in layers:
+        l.fwd_stage_dispatch(0)
+    for l in layers:
+        l.fwd_prepare()
+    for c in range(n):
+        if c + 1 < n:
+            for l in layers:
+                l.fwd_stage_dispatch(c + 1)
+        for l in layers:
+            l.fwd_stage_experts(c)
+        if c >= 1:
+            for l in layers:
+                l.fwd_stage_combine(c - 1)
+    for l in layers:
+        l.fwd_stage_combine(n - 1)
+    outs = [l.moe.out.clone() for l in layers]
+    for r, l in enumerate(layers):
+        l.bwd_stage_combine(douts[r], 0)
+    for l in layers:
+        l.bwd_prepare()
+    for c in range(n):
+        if c + 1 < n:
+            for r, l in enumerate(layers):
+                l.bwd_stage_combine(douts[r], c + 1)
+        for l in layers:
+            l.bwd_stage_experts(c)
+        if c >= 1:
+            for l in layers:
+                l.bwd_stage_dispatch(c - 1)
+    for l in layers:
+        l.bwd_stage_dispatch(n - 1)
+        l.bwd_weights()
+    res = [(l.moe.dx.clone(), l.moe.dgates.clone()) for l in layers]
+    grads = [[t.clone() for t in (l.dw1, l.dw2, l.db1, l.db2)] for l in layers]
+    return outs, res, grads
+
+
+@pytest.mark.parametrize("W,k,n,S", [(2, 2, 4, 2048), (1, 2, 4, 4096), (2, 1, 2, 1024), (4, 2, 1, 512)])
+def test_staged_pipeline_is_bit_identical(W, k, n, S):
+    """The staged exchange + row-window GEMMs give exactly the results of the unpipelined layer."""
+    M, H, LE, cf = 256, 512, 2, 1.25
+    E = LE * W
+    shared = {}
+    layers = [LB.MoELayer(S, M, H, k, cf, n, torch.bfloat16, DEV, LE, fabric=LB.LocalFabric(W, r, shared), seed=9)
+              for r in range(W)]
+    g = torch.Generator(device=DEV).manual_seed(W * 100 + k * 10 + n)
+    xs = [torch.randn((S, M), device=DEV, generator=g).bfloat16() for _ in range(W)]
+    gates = [torch.softmax(torch.randn((S, E), device=DEV, generator=g), dim=1) for _ in range(W)]
+    douts = [torch.randn((S, M), device=DEV, generator=g).bfloat16() for _ in range(W)]
+    ref = _run_plain(layers, xs, gates, douts)
+    for l in layers:                      # stale results must not pass for fresh ones
+        for t in (l.h, l.hpre, l.dh, l.moe.out, l.moe.dx, l.moe.expert_out, l.moe.d_expert_in, l.dw1, l.dw2):
+            t.fill_(float("nan"))
+    got = _run_staged(layers, xs, gates, douts, n)
+    torch.cuda.synchronize()
+    for r in range(W):
+        assert torch.equal(got[0][r], ref[0][r]), "out[%d]" % r
+        assert torch.equal(got[1][r][0], ref[1][r][0]), "dx[%d]" % r
+        assert torch.equal(got[1][r][1], ref[1][r][1]), "dgates[%d]" % r
+        for a, b, name in zip(got[2][r], ref[2][r], ("dw1", "dw2", "db1", "db2")):
+            assert torch.equal(a, b), "%s[%d]" % (name, r)
+    # the windows tile the live rows of every block exactly once
+    for l in layers:
+        lo, hi, cnt = l.win_begin.cpu().numpy(), l.win_end.cpu().numpy(), l.cnt.cpu().numpy()
+        assert (lo[0] == 0).all() and (hi[-1] == cnt).all()
+        assert (lo[1:] == hi[:-1]).all() and (lo % 128 == 0).all()
+    assert int(LB.gemm_status(torch.device(DEV)).item()) == 0
+
+
+def test_pipelined_two_stream_schedule_single_rank():
+    """forward_pipelined / backward_pipelined (two streams, events) on one rank equal the plain path."""
+    S, M, H, LE, k, n = 4096, 256, 512, 4, 2, 4
+    layer = LB.MoELayer(S, M, H, k, 1.25, n, torch.bfloat16, DEV, LE, fabric=LB.LocalFabric(1, 0, {}), seed=3)
+    g = torch.Generator(device=DEV).manual_seed(77)
+    x = torch.randn((S, M), device=DEV, generator=g).bfloat16()
+    gate = torch.softmax(torch.randn((S, LE), device=DEV, generator=g), dim=1)
+    dout = torch.randn((S, M), device=DEV, generator=g).bfloat16()
+    out0 = layer.forward(x, gate).clone()
+    dx0, dg0 = [t.clone() for t in layer.backward(dout)]
+    w0 = [t.clone() for t in (layer.dw1, layer.dw2, layer.db1, layer.db2)]
+    for step in range(2):
+        out1 = layer.forward_pipelined(x, gate).clone()
+        dx1, dg1 = [t.clone() for t in layer.backward_pipelined(dout)]
+    torch.cuda.synchronize()
+    assert torch.equal(out0, out1) and torch.equal(dx0, dx1) and torch.equal(dg0, dg1)
+    for a, b in zip(w0, (layer.dw1, layer.dw2, layer.db1, layer.db2)):
+        assert torch.equal(a, b)
