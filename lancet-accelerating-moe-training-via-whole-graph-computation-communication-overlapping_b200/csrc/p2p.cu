@@ -21,7 +21,9 @@ struct PeerTable {
   void* ptr[kMaxPeers];
 };
 
-constexpr int kP2PThreads = 256;
+// 128-thread blocks: one of them still fits beside a resident CTA of the expert GEMM (up to 168 registers x 320
+// threads), so the exchange kernels make progress while a GEMM occupies every SM
+constexpr int kP2PThreads = 128;
 constexpr int kP2PWarps = kP2PThreads / 32;
 
 __device__ __forceinline__ size_t il_index_p2p(int s, int Sp, int K2, int row) {
@@ -290,7 +292,7 @@ __global__ void stage_windows_kernel(const int32_t* __restrict__ chain, int W, i
 
 static int p2p_grid(long long tasks) {
   long long ctas = (tasks + kP2PWarps - 1) / kP2PWarps;
-  const long long cap = (long long)sm_count() * 8;
+  const long long cap = (long long)sm_count() * 16;
   if (ctas > cap) ctas = cap;
   if (ctas < 1) ctas = 1;
   return (int)ctas;

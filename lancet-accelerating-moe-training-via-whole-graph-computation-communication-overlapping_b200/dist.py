@@ -229,10 +229,11 @@ class DistChunkedMoE:
             _ptr(self.gates_s), _ptr(self.idx_loc), _ptr(self.capused), _ptr(self.elems), self.peer_chain[self.parity],
             _ptr(self.ws), self.ws.numel(), _stream(gate)))
 
-    def stage_dispatch(self, x, c):
-        """Scatter the rows of chunk c into the owners' receive buffers (follow with barrier())."""
+    def stage_dispatch(self, x, c0, c1=None):
+        """Scatter the rows of chunks [c0, c1) into the owners' receive buffers (follow with barrier())."""
+        c1 = c0 + 1 if c1 is None else c1
         check(_capi.lib().lancet_moe_dispatch_rows_p2p(
-            _ptr(x), _ptr(self.idx_loc), self.S, self.M, self.C, self.LE, self.W, self.rank, self.k, self.n, c, c + 1,
+            _ptr(x), _ptr(self.idx_loc), self.S, self.M, self.C, self.LE, self.W, self.rank, self.k, self.n, c0, c1,
             _DT[x.dtype], self.peer_recv[self.parity], _stream(x)))
 
     def stage_prepare(self, buf=None):
@@ -247,32 +248,30 @@ class DistChunkedMoE:
         check(L.lancet_moe_zero_tail(_ptr(buf), _ptr(cnt), self.M, self.C, self.W * self.LE, _DT[self.dtype], _stream(cnt)))
         return self.win_begin, self.win_end, cnt
 
-    def _chunk_views(self, c):
-        return self.gates_s[c], self.idx_loc[c]
-
-    def stage_combine(self, c, out=None):
-        """Combine the tokens of chunk c from the owners' expert outputs (rows must be complete: see MoELayer)."""
+    def stage_combine(self, c0, c1=None, out=None):
+        """Combine the tokens of chunks [c0, c1) from the owners' expert outputs (rows must be complete: see MoELayer)."""
+        c1 = c0 + 1 if c1 is None else c1
         out = self.out if out is None else out
-        g, il = self._chunk_views(c)
-        o = out[c * self.Sp:(c + 1) * self.Sp]
+        o = out[c0 * self.Sp:c1 * self.Sp]
         check(_capi.lib().lancet_moe_combine_chunked_p2p(
-            self.peer_eo, _ptr(g), _ptr(il), self.Sp, self.M, self.C, self.LE, self.W, self.rank, self.k, 1,
-            _DT[self.dtype], _ptr(o), _stream(o)))
+            self.peer_eo, _ptr(self.gates_s[c0:c1]), _ptr(self.idx_loc[c0:c1]), (c1 - c0) * self.Sp, self.M, self.C,
+            self.LE, self.W, self.rank, self.k, c1 - c0, _DT[self.dtype], _ptr(o), _stream(o)))
         return o
 
-    def stage_combine_backward(self, dout, c):
-        g, il = self._chunk_views(c)
-        d = dout[c * self.Sp:(c + 1) * self.Sp]
+    def stage_combine_backward(self, dout, c0, c1=None):
+        c1 = c0 + 1 if c1 is None else c1
+        d = dout[c0 * self.Sp:c1 * self.Sp]
         check(_capi.lib().lancet_moe_combine_bwd_p2p(
-            _ptr(d), _ptr(g), _ptr(il), self.peer_deo, self.peer_eo, _ptr(self.dgates[c]), self.Sp, self.M, self.C,
-            self.LE, self.W, self.rank, self.k, 1, _DT[self.dtype], _stream(d)))
+            _ptr(d), _ptr(self.gates_s[c0:c1]), _ptr(self.idx_loc[c0:c1]), self.peer_deo, self.peer_eo,
+            _ptr(self.dgates[c0:c1]), (c1 - c0) * self.Sp, self.M, self.C, self.LE, self.W, self.rank, self.k, c1 - c0,
+            _DT[self.dtype], _stream(d)))
 
-    def stage_dispatch_backward(self, c):
-        _, il = self._chunk_views(c)
-        o = self.dx[c * self.Sp:(c + 1) * self.Sp]
+    def stage_dispatch_backward(self, c0, c1=None):
+        c1 = c0 + 1 if c1 is None else c1
+        o = self.dx[c0 * self.Sp:c1 * self.Sp]
         check(_capi.lib().lancet_moe_combine_chunked_p2p(
-            self.peer_dxe, None, _ptr(il), self.Sp, self.M, self.C, self.LE, self.W, self.rank, self.k, 1,
-            _DT[self.dtype], _ptr(o), _stream(o)))
+            self.peer_dxe, None, _ptr(self.idx_loc[c0:c1]), (c1 - c0) * self.Sp, self.M, self.C, self.LE, self.W, self.rank,
+            self.k, c1 - c0, _DT[self.dtype], _ptr(o), _stream(o)))
         return o
 
     # -- backward ------------------------------------------------------------------------------

@@ -13,7 +13,7 @@ from .dist import DistChunkedMoE
 
 class MoELayer:
     def __init__(self, S, M, H, k=2, capacity_factor=1.25, n_chunks=4, dtype=torch.bfloat16, device="cuda",
-                 local_experts=2, fabric=None, group=None, act="gelu", seed=0, overlap_dw=True):
+                 local_experts=2, fabric=None, group=None, act="gelu", seed=0, overlap_dw=True, stages=None):
         self.moe = DistChunkedMoE(S, M, k, capacity_factor, n_chunks, dtype, device, local_experts, fabric=fabric,
                                   group=group, train=True)
         self.S, self.M, self.H, self.LE, self.act = S, M, H, local_experts, act
@@ -34,6 +34,11 @@ class MoELayer:
         self.db2 = torch.empty_like(self.b2)
         self.side = torch.cuda.Stream(device=d) if overlap_dw else None
         self.G, self.C = G, C
+        # pipeline stages of the staged schedule: consecutive chunks grouped into `stages` exchange steps
+        P = n_chunks if stages is None else stages
+        if P < 1 or n_chunks % P:
+            raise ValueError("stages must divide n_chunks")
+        self.stage_chunks = [(s * n_chunks // P, (s + 1) * n_chunks // P) for s in range(P)]
 
     # ---- forward, in the three phases between which the ranks meet ----
     def fwd_dispatch(self, x, gate):
@@ -64,31 +69,47 @@ class MoELayer:
         self._x = x
         self.moe.stage_gate(gate)
 
+    def _window(self, c):
+        c0, c1 = self.stage_chunks[c]
+        return self.win_begin[c0], self.win_end[c1 - 1]
+
     def fwd_stage_dispatch(self, c):
-        self.moe.stage_dispatch(self._x, c)
+        self.moe.stage_dispatch(self._x, *self.stage_chunks[c])
 
     def fwd_prepare(self):
         self.win_begin, self.win_end, self.cnt = self.moe.stage_prepare()
         self.x_e = self.moe.recv[self.moe.parity].view(self.G, self.C, self.M)
 
-    def fwd_stage_experts(self, c):
-        lo, hi = self.win_begin[c], self.win_end[c]
+    def fwd_stage_experts_1(self, c):
+        lo, hi = self._window(c)
         ops.grouped_gemm_nt(self.x_e, self.w1, bias=self.b1, counts=hi, row_begin=lo, act=self.act, out=self.h,
                             preact=self.hpre)
+
+    def fwd_stage_experts_2(self, c):
+        lo, hi = self._window(c)
         ops.grouped_gemm_nt(self.h, self.w2, bias=self.b2, counts=hi, row_begin=lo,
                             out=self.moe.expert_out.view(self.G, self.C, self.M))
 
+    def fwd_stage_experts(self, c):
+        self.fwd_stage_experts_1(c)
+        self.fwd_stage_experts_2(c)
+
     def fwd_stage_combine(self, c):
-        return self.moe.stage_combine(c)
+        return self.moe.stage_combine(*self.stage_chunks[c])
 
     def _streams(self):
         if getattr(self, "comm", None) is None:
             self.comm = torch.cuda.Stream(device=self.device)
-        return torch.cuda.current_stream(self.device), self.comm
+            self.aux = torch.cuda.Stream(device=self.device, priority=-1)
+        return torch.cuda.current_stream(self.device), self.aux, self.comm
 
     def forward_pipelined(self, x, gate):
-        n = self.moe.n
-        main, comm = self._streams()
+        """Three streams: `comm` carries the exchange stages and the flag barriers (one fixed order on every
+        rank), the current stream the first expert GEMM of every stage, `aux` the second one: the first GEMM of
+        stage c+1 does not depend on the second of stage c, so its CTAs fill the SMs that the other's last,
+        partial wave of tiles leaves idle."""
+        n = len(self.stage_chunks)
+        main, aux, comm = self._streams()
         self.fwd_gate(x, gate)
         comm.wait_stream(main)
         arrived = []
@@ -101,8 +122,12 @@ class MoELayer:
         self.fwd_prepare()
         for c in range(n):
             main.wait_event(arrived[c])
-            self.fwd_stage_experts(c)
-            done = main.record_event()
+            self.fwd_stage_experts_1(c)
+            half = main.record_event()
+            with torch.cuda.stream(aux):
+                aux.wait_event(half)
+                self.fwd_stage_experts_2(c)
+                done = aux.record_event()
             if c >= 1 or n == 1:
                 with torch.cuda.stream(comm):
                     comm.wait_event(done)
@@ -111,21 +136,29 @@ class MoELayer:
                         self.fwd_stage_combine(c - 1)
                     if c == n - 1:
                         self.fwd_stage_combine(c)
+        main.wait_stream(aux)
         main.wait_stream(comm)
         return self.moe.out
 
     # ---- pipelined backward ----
     def bwd_stage_combine(self, dout, c):
-        self.moe.stage_combine_backward(dout, c)
+        self.moe.stage_combine_backward(dout, *self.stage_chunks[c])
 
     def bwd_prepare(self):
         self.moe.stage_prepare(self.moe.d_expert_out)
         self.dy = self.moe.d_expert_out.view(self.G, self.C, self.M)
 
-    def bwd_stage_experts(self, c):
-        lo, hi = self.win_begin[c], self.win_end[c]
+    def bwd_stage_experts_1(self, c):
+        lo, hi = self._window(c)
         ops.grouped_gemm_nn(self.dy, self.w2, counts=hi, row_begin=lo, act=self.act, preact=self.hpre, out=self.dh)
+
+    def bwd_stage_experts_2(self, c):
+        lo, hi = self._window(c)
         ops.grouped_gemm_nn(self.dh, self.w1, counts=hi, row_begin=lo, out=self.moe.d_expert_in.view(self.G, self.C, self.M))
+
+    def bwd_stage_experts(self, c):
+        self.bwd_stage_experts_1(c)
+        self.bwd_stage_experts_2(c)
 
     def bwd_weights(self):
         ops.grouped_gemm_tn(self.dy, self.h, self.LE, counts=self.cnt, out=self.dw2)
@@ -134,11 +167,11 @@ class MoELayer:
         ops.grouped_bias_grad(self.dh, self.LE, counts=self.cnt, out=self.db1)
 
     def bwd_stage_dispatch(self, c):
-        return self.moe.stage_dispatch_backward(c)
+        return self.moe.stage_dispatch_backward(*self.stage_chunks[c])
 
     def backward_pipelined(self, dout):
-        n = self.moe.n
-        main, comm = self._streams()
+        n = len(self.stage_chunks)
+        main, aux, comm = self._streams()
         comm.wait_stream(main)
         arrived = []
         with torch.cuda.stream(comm):
@@ -150,8 +183,12 @@ class MoELayer:
         self.bwd_prepare()
         for c in range(n):
             main.wait_event(arrived[c])
-            self.bwd_stage_experts(c)
-            done = main.record_event()
+            self.bwd_stage_experts_1(c)
+            half = main.record_event()
+            with torch.cuda.stream(aux):
+                aux.wait_event(half)
+                self.bwd_stage_experts_2(c)
+                done = aux.record_event()
             if c >= 1 or n == 1:
                 with torch.cuda.stream(comm):
                     comm.wait_event(done)
@@ -162,6 +199,7 @@ class MoELayer:
                         self.bwd_stage_dispatch(c)
         # the weight gradients have no consumer before the optimizer: they run under the last gathers
         self.bwd_weights()
+        main.wait_stream(aux)
         main.wait_stream(comm)
         return self.moe.dx, self.moe.dgates
 

@@ -39,6 +39,27 @@ def main():
         np.testing.assert_array_equal(recv.cpu().numpy().reshape(E, -1, M), want_recv[rank])
         np.testing.assert_array_equal(out.cpu().numpy().astype(np.float32),
                                       torch.from_numpy(ref).half().float().numpy())
+    # whole layer: the two-stream pipelined schedule (exchange of chunk c+1 under the experts of chunk c, real flag
+    # barriers between the ranks) gives exactly the results of the unpipelined one
+    layer = LB.MoELayer(4096, 256, 512, 2, 1.25, 4, torch.bfloat16, dev, LE, seed=21)
+    g = torch.Generator(device=dev).manual_seed(300 + rank)
+    lx = torch.randn((4096, 256), device=dev, generator=g).bfloat16()
+    lgate = torch.softmax(torch.randn((4096, E), device=dev, generator=g), dim=1)
+    ldout = torch.randn((4096, 256), device=dev, generator=g).bfloat16()
+    out0 = layer.forward(lx, lgate).clone()
+    dx0, dg0 = [t.clone() for t in layer.backward(ldout)]
+    w0 = [t.clone() for t in (layer.dw1, layer.dw2, layer.db1, layer.db2)]
+    for step in range(3):
+        out1 = layer.forward_pipelined(lx, lgate).clone()
+        dx1, dg1 = [t.clone() for t in layer.backward_pipelined(ldout)]
+    torch.cuda.synchronize()
+    layer.moe.check()
+    assert torch.equal(out0, out1) and torch.equal(dx0, dx1) and torch.equal(dg0, dg1)
+    for a, b in zip(w0, (layer.dw1, layer.dw2, layer.db1, layer.db2)):
+        assert torch.equal(a, b)
+    assert int(LB.gemm_status(dev).item()) == 0
+    dist.barrier()
+    layer.moe.close()
     # stand-alone _all_to_all over NCCL: rank r sends rows filled with r+1, expects row i = i+1
     # (tests/python/distributed/test_alltoall.py:22-59 of the reference)
     comm = LB.Communicator(dev)

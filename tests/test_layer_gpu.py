@@ -137,14 +137,15 @@ def _run_staged(layers, xs, gates, douts, n):
     return outs, res, grads
 
 
-@pytest.mark.parametrize("W,k,n,S", [(2, 2, 4, 2048), (1, 2, 4, 4096), (2, 1, 2, 1024), (4, 2, 1, 512)])
-def test_staged_pipeline_is_bit_identical(W, k, n, S):
+@pytest.mark.parametrize("W,k,n,S,stages", [(2, 2, 4, 2048, None), (1, 2, 4, 4096, 2), (2, 1, 2, 1024, None),
+                                             (4, 2, 1, 512, None), (2, 2, 4, 1024, 1)])
+def test_staged_pipeline_is_bit_identical(W, k, n, S, stages):
     """The staged exchange + row-window GEMMs give exactly the results of the unpipelined layer."""
     M, H, LE, cf = 256, 512, 2, 1.25
     E = LE * W
     shared = {}
-    layers = [LB.MoELayer(S, M, H, k, cf, n, torch.bfloat16, DEV, LE, fabric=LB.LocalFabric(W, r, shared), seed=9)
-              for r in range(W)]
+    layers = [LB.MoELayer(S, M, H, k, cf, n, torch.bfloat16, DEV, LE, fabric=LB.LocalFabric(W, r, shared), seed=9,
+                          stages=stages) for r in range(W)]
     g = torch.Generator(device=DEV).manual_seed(W * 100 + k * 10 + n)
     xs = [torch.randn((S, M), device=DEV, generator=g).bfloat16() for _ in range(W)]
     gates = [torch.softmax(torch.randn((S, E), device=DEV, generator=g), dim=1) for _ in range(W)]
@@ -153,7 +154,7 @@ def test_staged_pipeline_is_bit_identical(W, k, n, S):
     for l in layers:                      # stale results must not pass for fresh ones
         for t in (l.h, l.hpre, l.dh, l.moe.out, l.moe.dx, l.moe.expert_out, l.moe.d_expert_in, l.dw1, l.dw2):
             t.fill_(float("nan"))
-    got = _run_staged(layers, xs, gates, douts, n)
+    got = _run_staged(layers, xs, gates, douts, len(layers[0].stage_chunks))
     torch.cuda.synchronize()
     for r in range(W):
         assert torch.equal(got[0][r], ref[0][r]), "out[%d]" % r
