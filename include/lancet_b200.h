@@ -298,6 +298,12 @@ int lancet_all_to_all_evenly(const void* send, void* recv, size_t total_bytes, l
  * out_ws and a kernel unpacks it into recvs[i].  in_ws and out_ws: sum(nbytes) bytes each. */
 int lancet_all_to_all_tuple(const void* const* sends, void* const* recvs, const size_t* nbytes, int n_tensors,
                             void* in_ws, void* out_ws, size_t ws_bytes, lancet_comm_t comm, lancet_stream_t stream);
+/* Count-aware all-to-all over NCCL, replaces NCCLAllToAllv::Execute (nccl.cc:357-431) for buffers that are not in
+ * symmetric memory: send / recv are [W][n_chunks][chunk_elems]; the counts (device uint64 [W*n_chunks]) are
+ * exchanged on the device, whole chunks travel, and a kernel clears everything past recv_counts[i*n_chunks+j]
+ * elements of every received chunk - the same result as the reference without its host round trip (:388-390). */
+int lancet_all_to_allv(const void* send, void* recv, const uint64_t* send_counts, uint64_t* recv_counts, int n_chunks,
+                       size_t elem_size, size_t chunk_elems, lancet_comm_t comm, lancet_stream_t stream);
 /* Peer-memory transport for receive buffers in symmetric memory: one kernel stores chunk i of
  * `send` into block `rank` of peer_recv[i].  Follow with lancet_p2p_barrier before reading. */
 int lancet_all_to_all_p2p(const void* send, void* const* peer_recv, size_t bytes_per_rank, int W, int rank,
@@ -345,6 +351,19 @@ int lancet_grouped_gemm_nt_window(const void* A, const void* B, void* D, const v
 int lancet_grouped_gemm_nn_window(const void* A, const void* B, void* D, const void* preact, int groups, int LE,
                                   int C, int N, int K, const int32_t* row_begin, const int32_t* row_end, int act,
                                   int dtype, int32_t* status, lancet_stream_t stream);
+/* `sparse_expert_matmul_nt` (SparseExpertMatmulNtImpl, src/op/dialect/cublas/matmul.cc:144-326; schema
+ * scripts/src_codegen/def_schema.py:711-718): data [C][G][M] (capacity-major, the G source ranks interleaved),
+ * weight [N][M], out [C][G][N] = data * weight^T for the rows every source really sent:
+ * rows_g = nelements_per_gpu[offset + g * stride] * scale / M (device uint64, the element counts `_all_to_allv`
+ * returns), clamped to C.  Rows past rows_g are written as zeros (the count-aware path the reference sketches in
+ * :221-247 and :289 but ships disabled: as shipped it multiplies the padded rows too, which gives the same output
+ * when the padding is zero).  bf16 / fp16, N % 256 == 0, M % 8 == 0; the operands are read in place through a
+ * 3-D tensor map, nothing is compacted.  ws: lancet_sparse_expert_matmul_nt_workspace_bytes(G) bytes, 16-byte
+ * aligned (row counts and the status word of the bounded waits). */
+size_t lancet_sparse_expert_matmul_nt_workspace_bytes(int G);
+int lancet_sparse_expert_matmul_nt(const void* data, const void* weight, void* out, const uint64_t* nelements_per_gpu,
+                                   int nelements_offset, int nelements_stride, int nelements_scale, int C, int G, int M,
+                                   int N, int dtype, void* ws, size_t ws_bytes, lancet_stream_t stream);
 /* Weight gradient (the reference's dW = matmul_tn(a, dy), src/op/grad/gemm.cc:31-36), summed over the
  * source ranks of an expert: D[e] = sum over groups g with g % LE == e of A[g][:counts[g]]^T * B[g][:counts[g]];
  * A [groups][C][Mout], B [groups][C][N], D [LE][Mout][N].  Rows from counts[g] to the next multiple

@@ -129,6 +129,10 @@ SIGNATURES = {
     "lancet_moe_dispatch_rows_p2p": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                              c_int, c_int, c_int, ctypes.POINTER(c_void_p), c_void_p]),
     "lancet_moe_stage_windows": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "lancet_sparse_expert_matmul_nt_workspace_bytes": (c_size_t, [c_int]),
+    "lancet_sparse_expert_matmul_nt": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                               c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
+    "lancet_all_to_allv": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_size_t, c_size_t, c_void_p, c_void_p]),
     "lancet_grouped_bias_grad_workspace_bytes": (c_size_t, [c_int, c_int]),
     "lancet_grouped_bias_grad": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_size_t,
                                          c_void_p]),

@@ -41,6 +41,22 @@ class Communicator:
         check(_capi.lib().lancet_all_to_all(_ptr(x), _ptr(out), nbytes // self.world, self.handle, _stream(x)))
         return out
 
+    def all_to_allv(self, x, send_counts):
+        """`_all_to_allv` over NCCL: x viewed [W, n_chunks, chunk]; for (peer i, chunk j) only the first
+        send_counts[i*n_chunks+j] elements count.  Returns (out, recv_counts); out is zero past the counts."""
+        if not x.is_cuda or not x.is_contiguous() or not send_counts.is_cuda:
+            raise ValueError("all_to_allv needs contiguous CUDA tensors")
+        if send_counts.dtype not in (torch.int64, torch.uint64) or send_counts.numel() % self.world:
+            raise ValueError("send_counts must be a 64-bit tensor of world * n_chunks entries")
+        n_chunks = send_counts.numel() // self.world
+        if x.numel() % (self.world * n_chunks):
+            raise ValueError("Cannot evenly distribute input tensor to all ranks and chunks.")
+        out = torch.empty_like(x)
+        rc = torch.empty_like(send_counts)
+        check(_capi.lib().lancet_all_to_allv(_ptr(x), _ptr(out), _ptr(send_counts), _ptr(rc), n_chunks, x.element_size(),
+                                             x.numel() // (self.world * n_chunks), self.handle, _stream(x)))
+        return out, rc
+
     def all_to_all_tuple(self, xs):
         """`_all_to_all` of a tuple of tensors in one grouped exchange; returns the list of outputs."""
         outs = [torch.empty_like(x) for x in xs]

@@ -143,6 +143,31 @@ a2av_store_kernel(const unsigned char* __restrict__ send, PeerTableA recv, PeerT
   }
 }
 
+// NCCL transport of the count-aware exchange: whole chunks travel, then everything past the received count is
+// cleared in place.  grid = (blocks, n_chunks, W).
+__global__ void __launch_bounds__(256)
+a2av_mask_kernel(unsigned char* __restrict__ recv, const unsigned long long* __restrict__ recv_counts, int n_chunks,
+                 size_t chunk_bytes, int elem_size) {
+  const int src = blockIdx.z, j = blockIdx.y;
+  size_t live = (size_t)recv_counts[(size_t)src * n_chunks + j] * elem_size;
+  if (live > chunk_bytes) live = chunk_bytes;
+  uint4* d4 = reinterpret_cast<uint4*>(recv + ((size_t)src * n_chunks + j) * chunk_bytes);
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  const size_t tid = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t live_vecs = live / 16, vecs = chunk_bytes / 16;
+  const uint4 z = make_uint4(0, 0, 0, 0);
+  for (size_t i = live_vecs + tid; i < vecs; i += stride) {
+    if (i == live_vecs && (live & 15)) {
+      uint4 w = d4[i];
+      unsigned char* wb = reinterpret_cast<unsigned char*>(&w);
+      for (int b = (int)(live & 15); b < 16; ++b) wb[b] = 0;
+      d4[i] = w;
+    } else {
+      d4[i] = z;
+    }
+  }
+}
+
 }  // namespace lancet
 
 extern "C" {
@@ -300,6 +325,33 @@ int lancet_all_to_all_p2p(const void* send, void* const* peer_recv, size_t bytes
   ProfScope prof("a2a_store_kernel", st);
   a2a_store_kernel<<<(unsigned)bx, 256, 0, st>>>(static_cast<const uint4*>(send), t, vecs, W, rank);
   return launch_status("a2a_store_kernel");
+}
+
+int lancet_all_to_allv(const void* send, void* recv, const uint64_t* send_counts, uint64_t* recv_counts, int n_chunks,
+                       size_t elem_size, size_t chunk_elems, lancet_comm_t comm, lancet_stream_t stream) {
+  LANCET_REQUIRE(comm, LANCET_ERR_NULL, "lancet_all_to_allv: null communicator");
+  LANCET_REQUIRE(nccl().ok, LANCET_ERR_COMM, "NCCL (libnccl.so.2) could not be loaded");
+  LANCET_REQUIRE(n_chunks >= 1 && n_chunks <= 65535 && elem_size >= 1 && elem_size <= 16, LANCET_ERR_INVALID,
+                 "lancet_all_to_allv: bad n_chunks %d or element size %zu", n_chunks, elem_size);
+  LANCET_REQUIRE(send_counts && recv_counts, LANCET_ERR_NULL, "lancet_all_to_allv: null counts");
+  const size_t chunk_bytes = chunk_elems * elem_size;
+  int W = 0;
+  LANCET_NCCL(nccl().CommCount(static_cast<ncclComm_t>(comm), &W));
+  LANCET_REQUIRE(W >= 1 && W <= 65535, LANCET_ERR_INVALID, "lancet_all_to_allv: bad communicator size %d", W);
+  if (int rc = lancet_all_to_all(send_counts, recv_counts, (size_t)n_chunks * sizeof(uint64_t), comm, stream)) return rc;
+  if (chunk_bytes == 0) return LANCET_OK;
+  LANCET_REQUIRE(send && recv, LANCET_ERR_NULL, "lancet_all_to_allv: null buffer");
+  LANCET_REQUIRE(chunk_bytes % 16 == 0 && aligned(recv, 16), LANCET_ERR_INVALID,
+                 "lancet_all_to_allv: the chunk (%zu bytes) must be a multiple of 16 bytes and recv 16-byte aligned", chunk_bytes);
+  if (int rc = lancet_all_to_all(send, recv, (size_t)n_chunks * chunk_bytes, comm, stream)) return rc;
+  long long bx = (long long)((chunk_bytes / 16 + 255) / 256);
+  const long long cap = (long long)sm_count() * 8 / ((long long)W * n_chunks) + 1;
+  if (bx > cap) bx = cap;
+  if (bx < 1) bx = 1;
+  a2av_mask_kernel<<<dim3((unsigned)bx, n_chunks, W), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<unsigned char*>(recv), reinterpret_cast<const unsigned long long*>(recv_counts), n_chunks, chunk_bytes,
+      (int)elem_size);
+  return launch_status("a2av_mask_kernel");
 }
 
 int lancet_all_to_allv_p2p(const void* send, void* const* peer_recv, const uint64_t* send_counts,

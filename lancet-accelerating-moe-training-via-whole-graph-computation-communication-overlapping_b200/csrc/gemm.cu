@@ -53,6 +53,7 @@ struct Params {
   int m_tiles, n_tiles, tiles_per_group, total_tiles;
   const int32_t* counts;  // [groups] live rows (end of the row window), or null
   const int32_t* row_lo;  // [groups] first row of the window (rounded down to a tile boundary), or null; MODE_ROWS only
+  int interleaved;        // MODE_ROWS: A, D and preact are [C][groups][.] (row c of group g at c * groups + g) instead of [groups][C][.]
   const void* bias;       // [LE][N] or null
   void* D;
   void* preact;           // EPI_ACT: optional copy of the pre-activation; EPI_DACT: the saved pre-activation (input)
@@ -349,7 +350,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             if (!(ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, p.status, 1))) break;
             const uint32_t full = bar_full + 8 * stage;
             mbar_expect_tx(full, A_STAGE_BYTES + B_STAGE_BYTES);
-            tma_load_2d(smem_u32(sA + stage * A_STAGE_BYTES), &tmA, full, kb * BK, a_row);
+            if (p.interleaved)
+              tma_load_3d(smem_u32(sA + stage * A_STAGE_BYTES), &tmA, full, kb * BK, tl.group, tl.mt * BM);
+            else
+              tma_load_2d(smem_u32(sA + stage * A_STAGE_BYTES), &tmA, full, kb * BK, a_row);
             const uint32_t b_dst = smem_u32(sB + stage * B_STAGE_BYTES);
             if (!B_MN) {
               tma_load_2d(b_dst, &tmB, full, kb * BK, e * p.N + tl.nt * BN);
@@ -449,7 +453,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       if (MODE == MODE_ROWS) {
         const int row_in_group = tl.mt * BM + row_in_tile;
         row_live = row_in_group < tl.rows;
-        out_row = (size_t)tl.group * p.C + row_in_group;
+        out_row = p.interleaved ? (size_t)row_in_group * p.groups + tl.group : (size_t)tl.group * p.C + row_in_group;
         e = tl.group % p.LE;
       } else {
         const int r = tl.mt * BM + row_in_tile;
@@ -524,17 +528,35 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 // A kernel of its own: merged into the epilogue above it slowed the live path down 2.5x.
 template <typename T>
 __global__ void __launch_bounds__(256)
-zero_dead_rows_kernel(T* __restrict__ D, const int32_t* __restrict__ counts, int C, int N) {
+zero_dead_rows_kernel(T* __restrict__ D, const int32_t* __restrict__ counts, int C, int N, int groups, int interleaved,
+                      int to_end) {
   const int g = blockIdx.y;
   int rows = counts[g];
   rows = rows < 0 ? 0 : (rows > C ? C : rows);
-  int end = (rows + BM - 1) / BM * BM;
+  int end = to_end ? C : (rows + BM - 1) / BM * BM;
   if (end > C) end = C;
   const size_t vec_per_row = (size_t)N * sizeof(T) / 16;
   const size_t total = (size_t)(end - rows) * vec_per_row;
-  uint4* base = reinterpret_cast<uint4*>(D + ((size_t)g * C + rows) * N);
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
-    base[i] = make_uint4(0, 0, 0, 0);
+  if (!interleaved) {
+    uint4* base = reinterpret_cast<uint4*>(D + ((size_t)g * C + rows) * N);
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
+      base[i] = make_uint4(0, 0, 0, 0);
+  } else {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+      const size_t r = rows + i / vec_per_row, v = i % vec_per_row;
+      reinterpret_cast<uint4*>(D + (r * groups + g) * N)[v] = make_uint4(0, 0, 0, 0);
+    }
+  }
+}
+
+// Live rows of every source block from the element counts the count-aware all-to-all returns
+// (uint64, entry offset + g * stride, scaled, divided by the row length; src/op/dialect/cublas/matmul.cc:221-247).
+__global__ void nelements_to_rows_kernel(const uint64_t* __restrict__ nelem, int offset, int stride, int scale, int M, int C,
+                                         int G, int32_t* __restrict__ counts) {
+  const int g = blockIdx.x * blockDim.x + threadIdx.x;
+  if (g >= G) return;
+  const unsigned long long rows = nelem[(size_t)offset + (size_t)g * stride] * (unsigned long long)scale / (unsigned long long)M;
+  counts[g] = rows > (unsigned long long)C ? C : (int)rows;
 }
 
 // Bias gradient of an expert layer: db[e][n] = sum over the groups g of expert e and their live rows r of dY[g][r][n].
@@ -605,13 +627,14 @@ static int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t 
   return LANCET_OK;
 }
 
-// 3-D tensor [groups][rows][cols] of 16-bit elements, box = 1 x 64 x 64, 128-byte swizzle.
-static int make_map3(CUtensorMap* map, const void* base, uint64_t groups, uint64_t rows, uint64_t cols, int dtype) {
+// 3-D tensor [groups][rows][cols] of 16-bit elements, box = box_groups x box_rows x 64, 128-byte swizzle.
+static int make_map3(CUtensorMap* map, const void* base, uint64_t groups, uint64_t rows, uint64_t cols, int dtype,
+                     uint32_t box_rows = 64, uint32_t box_groups = 1) {
   EncodeTiledFn fn = encode_fn();
   LANCET_REQUIRE(fn, LANCET_ERR_CUDA, "grouped gemm: the driver does not provide cuTensorMapEncodeTiled");
   cuuint64_t dims[3] = {cols, rows, groups};
   cuuint64_t strides[2] = {cols * 2, rows * cols * 2};
-  cuuint32_t box[3] = {(cuuint32_t)BK, 64, 1};
+  cuuint32_t box[3] = {(cuuint32_t)BK, box_rows, box_groups};
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = fn(map, dtype == LANCET_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
                   const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -642,7 +665,8 @@ static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const Params& 
                                 : launch_t<__half, MODE, B_MN, EPI>(tmA, tmB, p, name, st);
   if (rc != LANCET_OK || MODE != MODE_ROWS || !p.counts) return rc;
   // both 16-bit types have the same size: one instantiation serves them
-  zero_dead_rows_kernel<__half><<<dim3(8, p.groups), 256, 0, st>>>(static_cast<__half*>(p.D), p.counts, p.C, p.N);
+  zero_dead_rows_kernel<__half><<<dim3(8, p.groups), 256, 0, st>>>(static_cast<__half*>(p.D), p.counts, p.C, p.N, p.groups,
+                                                                    p.interleaved, 0);
   return launch_status("zero_dead_rows_kernel");
 }
 
@@ -672,6 +696,7 @@ static int rows_common(const char* fn, const void* A, const void* B, void* D, in
   p->status = status;
   p->act = act;
   p->row_lo = nullptr;
+  p->interleaved = 0;
   return LANCET_OK;
 }
 
@@ -747,7 +772,8 @@ int lancet_grouped_gemm_tn(const void* A, const void* B, void* D, int groups, in
   p.m_tiles = Mout / BM; p.n_tiles = N / BN;
   p.tiles_per_group = p.m_tiles * p.n_tiles;
   p.total_tiles = p.tiles_per_group * LE;
-  p.counts = counts; p.row_lo = nullptr; p.bias = nullptr; p.D = D; p.preact = nullptr; p.act = 0; p.epi = EPI_ACT;
+  p.counts = counts; p.row_lo = nullptr; p.interleaved = 0; p.bias = nullptr; p.D = D; p.preact = nullptr; p.act = 0;
+  p.epi = EPI_ACT;
   p.status = status;
   CUtensorMap tmA, tmB;
   if (C == 0) {
@@ -757,6 +783,45 @@ int lancet_grouped_gemm_tn(const void* A, const void* B, void* D, int groups, in
   if (int rc = make_map3(&tmA, A, (uint64_t)groups, (uint64_t)C, (uint64_t)Mout, dtype)) return rc;
   if (int rc = make_map3(&tmB, B, (uint64_t)groups, (uint64_t)C, (uint64_t)N, dtype)) return rc;
   return launch<MODE_REDUCE, true, EPI_ACT>(tmA, tmB, p, dtype, "grouped_gemm_tn_kernel", static_cast<cudaStream_t>(stream));
+}
+
+size_t lancet_sparse_expert_matmul_nt_workspace_bytes(int G) {
+  if (G < 1) return 0;
+  return ((size_t)G * sizeof(int32_t) + 255) / 256 * 256 + 256;
+}
+
+int lancet_sparse_expert_matmul_nt(const void* data, const void* weight, void* out, const uint64_t* nelements_per_gpu,
+                                   int nelements_offset, int nelements_stride, int nelements_scale, int C, int G, int M, int N,
+                                   int dtype, void* ws, size_t ws_bytes, lancet_stream_t stream) {
+  using namespace lancet::gemm;
+  LANCET_REQUIRE(nelements_offset >= 0 && nelements_stride >= 1 && nelements_scale >= 1, LANCET_ERR_INVALID,
+                 "lancet_sparse_expert_matmul_nt: bad nelements offset %d / stride %d / scale %d", nelements_offset,
+                 nelements_stride, nelements_scale);
+  LANCET_REQUIRE(G >= 1 && ws && ws_bytes >= lancet_sparse_expert_matmul_nt_workspace_bytes(G) && aligned(ws, 16),
+                 LANCET_ERR_INVALID, "lancet_sparse_expert_matmul_nt: workspace missing, too small or unaligned");
+  int32_t* counts = static_cast<int32_t*>(ws);
+  int32_t* status = reinterpret_cast<int32_t*>(static_cast<char*>(ws) + lancet_sparse_expert_matmul_nt_workspace_bytes(G) - 256);
+  Params p;
+  if (int rc = rows_common("lancet_sparse_expert_matmul_nt", data, weight, out, G, 1, C, N, M, 0, dtype, status, &p)) return rc;
+  if (C == 0) return LANCET_OK;
+  LANCET_REQUIRE(nelements_per_gpu, LANCET_ERR_NULL, "lancet_sparse_expert_matmul_nt: null nelements_per_gpu");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  LANCET_CUDA(cudaMemsetAsync(status, 0, sizeof(int32_t), st));
+  nelements_to_rows_kernel<<<(G + 127) / 128, 128, 0, st>>>(nelements_per_gpu, nelements_offset, nelements_stride,
+                                                          nelements_scale, M, C, G, counts);
+  if (int rc = launch_status("nelements_to_rows_kernel")) return rc;
+  p.counts = counts; p.interleaved = 1; p.bias = nullptr; p.D = out; p.preact = nullptr; p.epi = EPI_ACT;
+  CUtensorMap tmA, tmB;
+  // data [C][G][M]: dimension order (M, G, C), one group and 128 rows of it per box
+  if (int rc = make_map3(&tmA, data, (uint64_t)C, (uint64_t)G, (uint64_t)M, dtype, 1, BM)) return rc;
+  if (int rc = make_map(&tmB, weight, (uint64_t)N, (uint64_t)M, BN, dtype)) return rc;
+  const int rc = dtype == LANCET_BF16
+                     ? launch_t<__nv_bfloat16, MODE_ROWS, false, EPI_ACT>(tmA, tmB, p, "sparse_expert_matmul_nt_kernel", st)
+                     : launch_t<__half, MODE_ROWS, false, EPI_ACT>(tmA, tmB, p, "sparse_expert_matmul_nt_kernel", st);
+  if (rc != LANCET_OK) return rc;
+  // every row past the count is zero in the output (the reference's intended path memsets it, matmul.cc:289)
+  zero_dead_rows_kernel<__half><<<dim3(8, G), 256, 0, st>>>(static_cast<__half*>(out), counts, C, N, G, 1, 1);
+  return launch_status("zero_dead_rows_kernel");
 }
 
 size_t lancet_grouped_bias_grad_workspace_bytes(int LE, int N) {

@@ -3,7 +3,9 @@
 //   raf.op.cuda.{moe_encode, moe_decode, moe_encode_dx, moe_encode_dg, moe_decode_dx, moe_decode_dg, lans}
 //     (src/op/dialect/cuda/moe.cc:411, :1152, :1224, :1310, :1394, :1480; cuda/lans.cc:176-177)
 //   raf.op.nccl._all_to_all (src/op/dialect/nccl/nccl.cc:285-286)
-//   raf.op.cublas.matmul_nt (src/op/dialect/cublas/matmul.cc: the expert GEMM, here on tcgen05)
+//   raf.op.nccl._all_to_allv (nccl.cc:438-439)
+//   raf.op.cublas.{matmul, matmul_nt, matmul_tn, dense, sparse_expert_matmul_nt} (src/op/dialect/cublas/matmul.cc:328-335:
+//     the expert GEMMs and their gradients, here on tcgen05; matmul_tt is not on the path and is left to the next dialect)
 // Constructors see the concrete shapes and issue their workspace / stream requests; Execute only
 // calls the C ABI on the current stream.  Declarations restate src/op/declare/moe.cc:26-299,
 // declare/optimizer.cc:46-63 and declare/collective_comm.cc:54-81.
@@ -189,6 +191,51 @@ RAF_OP_DECLARE("raf.op.moe_decode_dg", MoeDecodeDgDeclare);
 RAF_OP_DECLARE("raf.op.lans", LansDeclare);
 RAF_OP_DECLARE("raf.op._all_to_all", AllToAllDeclare);
 RAF_OP_DECLARE("raf.op.matmul_nt", MatmulNtDeclare);
+RAF_OP_DECLARE("raf.op.dense", MatmulNtDeclare);
+
+void MatmulDeclare(CallValues* call) {
+  const Tensor& a = TensorArg(*call, 0);
+  const Tensor& b = TensorArg(*call, 1);
+  RAF_SHIM_CHECK(a.shape.size() == 2 && b.shape.size() == 2 && a.shape[1] == b.shape[0], "matmul: a [n,k], b [k,m]");
+  call->out = Value::T(Make(a.device, a.dtype, {a.shape[0], b.shape[1]}));
+  call->device = a.device;
+}
+void MatmulTnDeclare(CallValues* call) {
+  const Tensor& a = TensorArg(*call, 0);
+  const Tensor& b = TensorArg(*call, 1);
+  RAF_SHIM_CHECK(a.shape.size() == 2 && b.shape.size() == 2 && a.shape[0] == b.shape[0], "matmul_tn: a [k,n], b [k,m]");
+  call->out = Value::T(Make(a.device, a.dtype, {a.shape[1], b.shape[1]}));
+  call->device = a.device;
+}
+// src/op/declare/moe.cc:243-261
+void SparseExpertMatmulNtDeclare(CallValues* call) {
+  const Tensor& data = TensorArg(*call, 0);
+  const Tensor& weight = TensorArg(*call, 1);
+  const Tensor& nelem = TensorArg(*call, 2);
+  RAF_SHIM_CHECK(data.shape.size() == 3, "Expected input data to be 3D.");
+  RAF_SHIM_CHECK(weight.shape.size() == 2, "Expected input weight to be 2D.");
+  RAF_SHIM_CHECK(nelem.shape.size() == 1, "Expected input nelements_per_gpu to be 1D.");
+  const int64_t stride = call->args.size() > 4 ? call->args[4].i : 1;
+  RAF_SHIM_CHECK(stride >= 1 && data.shape[1] == nelem.shape[0] / stride,
+                 "Input data and nelements should have matching shape in dim 1 and 0 after stride.");
+  RAF_SHIM_CHECK(weight.shape[1] == data.shape[2], "Input weight and data should have matching shapes in dim 1 and 2.");
+  call->out = Value::T(Make(data.device, data.dtype, {data.shape[0], data.shape[1], weight.shape[0]}));
+  call->device = data.device;
+}
+// src/op/declare/collective_comm.cc:84-128: (x, send_counts) -> (tensor like x, tensor like send_counts)
+void AllToAllvDeclare(CallValues* call) {
+  RAF_SHIM_CHECK(call->args.size() >= 2 && call->args[0].kind == Value::kTuple && call->args[0].fields.size() == 1 &&
+                     call->args[1].kind == Value::kTuple && call->args[1].fields.size() == 1,
+                 "AllToAllv currently only supports one input tensor and one send_counts tensor.");
+  const Tensor& x = call->args[0].fields[0].tensor;
+  const Tensor& sc = call->args[1].fields[0].tensor;
+  call->out = Value::Tuple({Value::T(Make(x.device, x.dtype, x.shape)), Value::T(Make(sc.device, sc.dtype, sc.shape))});
+  call->device = x.device;
+}
+RAF_OP_DECLARE("raf.op.matmul", MatmulDeclare);
+RAF_OP_DECLARE("raf.op.matmul_tn", MatmulTnDeclare);
+RAF_OP_DECLARE("raf.op.sparse_expert_matmul_nt", SparseExpertMatmulNtDeclare);
+RAF_OP_DECLARE("raf.op._all_to_allv", AllToAllvDeclare);
 
 // ---------------------------------------------------------------- op envs
 class MoeEncode : public OpEnv {
@@ -601,21 +648,185 @@ class MatmulNt : public OpEnv {
     Ok(lancet_grouped_gemm_nt(in[0].tensor.data, in[1].tensor.data, out.tensor.data, nullptr, nullptr, 1, 1, n_, m_, k_, nullptr, 0,
                               dtype_, (int32_t*)status_, GetStream()));
   }
+  static bool Accepts(const CallValues& cv) {
+    if (cv.args.size() < 2 || cv.args[0].kind != Value::kTensor || cv.args[1].kind != Value::kTensor) return false;
+    const Tensor& a = cv.args[0].tensor;
+    const Tensor& b = cv.args[1].tensor;
+    if (a.dtype.bits != 16 || !(a.dtype == b.dtype)) return false;
+    return a.shape.size() == 2 && b.shape.size() == 2 && b.shape[0] % 256 == 0 && a.shape[1] % 8 == 0;
+  }
+  static OpEnv* make(const CallValues& cv) { return Accepts(cv) ? new MatmulNt(cv) : nullptr; }
+
+ protected:
+  int n_, k_, m_, dtype_;
+  void* status_ = nullptr;
+};
+RAF_REGISTER_DIALECT_OP(cublas, matmul_nt, 15);
+RAF_OP_ENV_MAKER("raf.op.cublas.matmul_nt", MatmulNt::make);
+
+// dense(x [n,k], w [m,k]) is the same contraction under another name (nn.Linear without bias)
+class Dense : public MatmulNt {
+ public:
+  using MatmulNt::MatmulNt;
+  std::string name() const override { return "raf.op.cublas.dense"; }
+  static OpEnv* make(const CallValues& cv) { return Accepts(cv) ? new Dense(cv) : nullptr; }
+};
+RAF_REGISTER_DIALECT_OP(cublas, dense, 15);
+RAF_OP_ENV_MAKER("raf.op.cublas.dense", Dense::make);
+
+// matmul(a [n,k], b [k,m]) -> [n,m]: the data-gradient form (dX = matmul(dy, w), src/op/grad/gemm.cc:31-36)
+class Matmul : public OpEnv {
+ public:
+  explicit Matmul(const CallValues& cv) {
+    const Tensor& a = TensorArg(cv, 0);
+    const Tensor& b = TensorArg(cv, 1);
+    n_ = (int)a.shape[0]; k_ = (int)a.shape[1]; m_ = (int)b.shape[1];
+    dtype_ = LancetDType(a.dtype);
+    arg_indices = {0, 1};
+    RequestWorkspace(&status_, cv.device, 256);
+  }
+  std::string name() const override { return "raf.op.cublas.matmul"; }
+  void Execute(const CallValues& cv) override { Execute({cv.args[0], cv.args[1]}, cv.out); }
+  void Execute(const std::vector<Value>& in, Value out) override {
+    RAF_SHIM_CHECK(cudaMemsetAsync(status_, 0, 4, (cudaStream_t)GetStream()) == cudaSuccess, "memset failed");
+    Ok(lancet_grouped_gemm_nn(in[0].tensor.data, in[1].tensor.data, out.tensor.data, nullptr, 1, 1, n_, m_, k_, nullptr, 0, dtype_,
+                              (int32_t*)status_, GetStream()));
+  }
   static OpEnv* make(const CallValues& cv) {
     if (cv.args.size() < 2 || cv.args[0].kind != Value::kTensor || cv.args[1].kind != Value::kTensor) return nullptr;
     const Tensor& a = cv.args[0].tensor;
     const Tensor& b = cv.args[1].tensor;
     if (a.dtype.bits != 16 || !(a.dtype == b.dtype)) return nullptr;
-    if (a.shape.size() != 2 || b.shape.size() != 2 || b.shape[0] % 256 != 0 || a.shape[1] % 8 != 0) return nullptr;
-    return new MatmulNt(cv);
+    if (a.shape.size() != 2 || b.shape.size() != 2 || b.shape[1] % 256 != 0 || a.shape[1] % 64 != 0) return nullptr;
+    return new Matmul(cv);
   }
 
  private:
   int n_, k_, m_, dtype_;
   void* status_ = nullptr;
 };
-RAF_REGISTER_DIALECT_OP(cublas, matmul_nt, 15);
-RAF_OP_ENV_MAKER("raf.op.cublas.matmul_nt", MatmulNt::make);
+RAF_REGISTER_DIALECT_OP(cublas, matmul, 15);
+RAF_OP_ENV_MAKER("raf.op.cublas.matmul", Matmul::make);
+
+// matmul_tn(a [k,n], b [k,m]) -> [n,m]: the weight-gradient form (dW = matmul_tn(dy, x), src/op/grad/gemm.cc:31-36)
+class MatmulTn : public OpEnv {
+ public:
+  explicit MatmulTn(const CallValues& cv) {
+    const Tensor& a = TensorArg(cv, 0);
+    const Tensor& b = TensorArg(cv, 1);
+    k_ = (int)a.shape[0]; n_ = (int)a.shape[1]; m_ = (int)b.shape[1];
+    dtype_ = LancetDType(a.dtype);
+    arg_indices = {0, 1};
+    RequestWorkspace(&status_, cv.device, 256);
+  }
+  std::string name() const override { return "raf.op.cublas.matmul_tn"; }
+  void Execute(const CallValues& cv) override { Execute({cv.args[0], cv.args[1]}, cv.out); }
+  void Execute(const std::vector<Value>& in, Value out) override {
+    RAF_SHIM_CHECK(cudaMemsetAsync(status_, 0, 4, (cudaStream_t)GetStream()) == cudaSuccess, "memset failed");
+    Ok(lancet_grouped_gemm_tn(in[0].tensor.data, in[1].tensor.data, out.tensor.data, 1, 1, k_, n_, m_, nullptr, dtype_,
+                              (int32_t*)status_, GetStream()));
+  }
+  static OpEnv* make(const CallValues& cv) {
+    if (cv.args.size() < 2 || cv.args[0].kind != Value::kTensor || cv.args[1].kind != Value::kTensor) return nullptr;
+    const Tensor& a = cv.args[0].tensor;
+    const Tensor& b = cv.args[1].tensor;
+    if (a.dtype.bits != 16 || !(a.dtype == b.dtype)) return nullptr;
+    if (a.shape.size() != 2 || b.shape.size() != 2 || a.shape[1] % 128 != 0 || b.shape[1] % 256 != 0) return nullptr;
+    return new MatmulTn(cv);
+  }
+
+ private:
+  int n_, k_, m_, dtype_;
+  void* status_ = nullptr;
+};
+RAF_REGISTER_DIALECT_OP(cublas, matmul_tn, 15);
+RAF_OP_ENV_MAKER("raf.op.cublas.matmul_tn", MatmulTn::make);
+
+// sparse_expert_matmul_nt(data [C,G,M], weight [N,M], nelements_per_gpu u64, offset, stride, scale) -> [C,G,N]
+// (src/op/dialect/cublas/matmul.cc:144-326).  Only the rows each source rank really sent are multiplied (what the
+// reference's commented-out path intended); the other rows of the output are zero.
+class SparseExpertMatmulNt : public OpEnv {
+ public:
+  explicit SparseExpertMatmulNt(const CallValues& cv) {
+    const Tensor& data = TensorArg(cv, 0);
+    const Tensor& weight = TensorArg(cv, 1);
+    C_ = (int)data.shape[0]; G_ = (int)data.shape[1]; M_ = (int)data.shape[2]; N_ = (int)weight.shape[0];
+    offset_ = cv.args.size() > 3 ? (int)cv.args[3].i : 0;
+    stride_ = cv.args.size() > 4 ? (int)cv.args[4].i : 1;
+    scale_ = cv.args.size() > 5 ? (int)cv.args[5].i : 1;
+    dtype_ = LancetDType(data.dtype);
+    arg_indices = {0, 1, 2};
+    ws_bytes_ = lancet_sparse_expert_matmul_nt_workspace_bytes(G_);
+    RequestWorkspace(&ws_, cv.device, (int64_t)ws_bytes_);  // replaces the two input-sized scratch buffers (matmul.cc:189-190)
+  }
+  std::string name() const override { return "raf.op.cublas.sparse_expert_matmul_nt"; }
+  void Execute(const CallValues& cv) override { Execute({cv.args[0], cv.args[1], cv.args[2]}, cv.out); }
+  void Execute(const std::vector<Value>& in, Value out) override {
+    Ok(lancet_sparse_expert_matmul_nt(in[0].tensor.data, in[1].tensor.data, out.tensor.data, (const uint64_t*)in[2].tensor.data,
+                                      offset_, stride_, scale_, C_, G_, M_, N_, dtype_, ws_, ws_bytes_, GetStream()));
+  }
+  static OpEnv* make(const CallValues& cv) {
+    if (cv.args.size() < 3 || cv.args[0].kind != Value::kTensor || cv.args[1].kind != Value::kTensor ||
+        cv.args[2].kind != Value::kTensor)
+      return nullptr;
+    const Tensor& d = cv.args[0].tensor;
+    const Tensor& w = cv.args[1].tensor;
+    if (d.dtype.bits != 16 || !(d.dtype == w.dtype) || cv.args[2].tensor.dtype.bits != 64) return nullptr;
+    if (d.shape.size() != 3 || w.shape.size() != 2 || w.shape[0] % 256 != 0 || d.shape[2] % 8 != 0) return nullptr;
+    return new SparseExpertMatmulNt(cv);
+  }
+
+ private:
+  int C_, G_, M_, N_, offset_, stride_, scale_, dtype_;
+  void* ws_ = nullptr;
+  size_t ws_bytes_ = 0;
+};
+RAF_REGISTER_DIALECT_OP(cublas, sparse_expert_matmul_nt, 20);
+RAF_OP_ENV_MAKER("raf.op.cublas.sparse_expert_matmul_nt", SparseExpertMatmulNt::make);
+
+// _all_to_allv over NCCL (nccl.cc:288-439) without the reference's device-to-host copy of the counts and stream
+// synchronisation (:388-390): the counts are exchanged on the device, whole chunks travel, and a kernel clears what
+// lies past the received counts.
+class NCCLAllToAllv : public OpEnv {
+ public:
+  explicit NCCLAllToAllv(const CallValues& cv) {
+    arg_indices = {0, 1};
+    RequestStream(&stream_, cv.device, kCudaCommunicate);
+    RequestDistributed(&communicator_);
+    const Tensor& x = cv.args[0].fields[0].tensor;
+    const Tensor& sc = cv.args[1].fields[0].tensor;
+    const int world = GetCommunicatorSize();
+    RAF_SHIM_CHECK(world >= 1 && sc.numel() % world == 0, "send_counts must hold world_size * n_chunks entries");
+    n_chunks_ = (int)(sc.numel() / world);
+    RAF_SHIM_CHECK(n_chunks_ >= 1 && x.numel() % ((int64_t)world * n_chunks_) == 0,
+                   "Cannot evenly distribute input tensor to all ranks and chunks.");
+    chunk_elems_ = (size_t)(x.numel() / ((int64_t)world * n_chunks_));
+    elem_size_ = (size_t)(x.dtype.bits / 8);
+  }
+  std::string name() const override { return "raf.op.nccl._all_to_allv"; }
+  void Execute(const CallValues& cv) override { Execute({cv.args[0], cv.args[1]}, cv.out); }
+  void Execute(const std::vector<Value>& in, Value out) override {
+    RAF_SHIM_CHECK(communicator_ != nullptr, "_all_to_allv: no communicator (RequestDistributed was not satisfied)");
+    RAF_SHIM_CHECK(out.kind == Value::kTuple && out.fields.size() == 2, "Expected output to be a 2-Tuple");
+    Ok(lancet_all_to_allv(in[0].fields[0].tensor.data, out.fields[0].tensor.data, (const uint64_t*)in[1].fields[0].tensor.data,
+                          (uint64_t*)out.fields[1].tensor.data, n_chunks_, elem_size_, chunk_elems_, communicator_, stream_));
+  }
+  static OpEnv* make(const CallValues& cv) {
+    if (cv.args.size() < 2 || cv.args[0].kind != Value::kTuple || cv.args[0].fields.size() != 1 ||
+        cv.args[1].kind != Value::kTuple || cv.args[1].fields.size() != 1)
+      return nullptr;
+    if (cv.args[1].fields[0].tensor.dtype.bits != 64) return nullptr;
+    return new NCCLAllToAllv(cv);
+  }
+
+ private:
+  void* stream_ = nullptr;
+  void* communicator_ = nullptr;
+  int n_chunks_ = 1;
+  size_t chunk_elems_ = 0, elem_size_ = 1;
+};
+RAF_REGISTER_DIALECT_OP(nccl, _all_to_allv, 10);
+RAF_OP_ENV_MAKER("raf.op.nccl._all_to_allv", NCCLAllToAllv::make);
 
 // ---------------------------------------------------------------- C bridge for hosts without C++ (tests)
 Value FromC(const lancet_raf_value_t* a, int n, int* pos) {

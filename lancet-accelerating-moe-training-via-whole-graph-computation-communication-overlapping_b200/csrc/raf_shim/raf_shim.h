@@ -125,6 +125,7 @@ void SetStream(void* stream);
 void* GetStream();
 void SetCommunicator(void* comm, int rank, int size);
 void* GetCommunicator();
+int GetCommunicatorSize();  // DistContext::Global()->size of the reference
 
 #define RAF_SHIM_CONCAT_(a, b) a##b
 #define RAF_SHIM_CONCAT(a, b) RAF_SHIM_CONCAT_(a, b)

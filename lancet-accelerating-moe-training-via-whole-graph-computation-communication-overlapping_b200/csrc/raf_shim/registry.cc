@@ -86,5 +86,6 @@ void SetCommunicator(void* comm, int rank, int size) {
   R().size = size;
 }
 void* GetCommunicator() { return R().comm; }
+int GetCommunicatorSize() { return R().size; }
 
 }  // namespace raf_shim

@@ -294,6 +294,32 @@ def grouped_gemm_nn(a, b, counts=None, act=None, preact=None, out=None, row_begi
     return out
 
 
+def sparse_expert_matmul_nt(data, weight, nelements_per_gpu, nelements_offset=0, nelements_stride=1, nelements_scale=1,
+                            out=None):
+    """`raf.op.sparse_expert_matmul_nt` (scripts/src_codegen/def_schema.py:711-718 of the reference):
+    data [C, G, M], weight [N, M], nelements_per_gpu uint64 [G*stride] -> [C, G, N]; source block g has
+    nelements_per_gpu[offset + g*stride] * scale / M live rows, the other rows of the output are zero."""
+    _require_cuda(data, weight, nelements_per_gpu, out)
+    C, G, M = data.shape
+    N, M2 = weight.shape
+    if M2 != M:
+        raise ValueError("Input data and weight should have matching shape in dim 2 and 1, respectively.")
+    if nelements_per_gpu.dim() != 1 or nelements_per_gpu.numel() // nelements_stride != G:
+        raise ValueError("Input data and nelements should have matching shape in dim 1 and 0 after stride.")
+    if data.dtype != weight.dtype or data.dtype not in (torch.bfloat16, torch.float16):
+        raise TypeError("sparse_expert_matmul_nt: bfloat16 or float16 operands of one type")
+    if nelements_per_gpu.dtype not in (torch.uint64, torch.int64):
+        raise TypeError("sparse_expert_matmul_nt: nelements_per_gpu must be a 64-bit integer tensor")
+    out = torch.empty((C, G, N), dtype=data.dtype, device=data.device) if out is None else out
+    L = _capi.lib()
+    nws = L.lancet_sparse_expert_matmul_nt_workspace_bytes(G)
+    ws = workspace(data.device, nws, "sparse_expert_matmul_nt")
+    check(L.lancet_sparse_expert_matmul_nt(_ptr(data), _ptr(weight), _ptr(out), _ptr(nelements_per_gpu), nelements_offset,
+                                           nelements_stride, nelements_scale, C, G, M, N, _dt(data), _ptr(ws), nws,
+                                           _stream(data)))
+    return out
+
+
 def grouped_gemm_tn(a, b, n_local_experts, counts=None, out=None):
     """Weight gradient: out[e] = sum_{g % LE == e} a[g, :n_g].T @ b[g, :n_g]; a [groups, C, Mout], b [groups, C, N]."""
     _require_cuda(a, b, counts, out)

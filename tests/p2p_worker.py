@@ -94,6 +94,18 @@ def main():
             c = (rank + j + i) % 4 + 1          # what rank i sent us for chunk j
             assert rc.cpu().numpy()[i * 2 + j] == c
             assert np.all(gvh[i, j, c:] == 0)
+    # the NCCL transport of the count-aware exchange gives the same data and counts
+    gn, rn = comm.all_to_allv(big, counts)
+    torch.cuda.synchronize()
+    assert torch.equal(gn, gv.view_as(gn)) and torch.equal(rn.view(torch.int64), rc.view(torch.int64))
+    # the same two collectives through the RAF-style registry: RequestDistributed hands the OpEnv the communicator
+    from lancet_b200 import raf, _capi
+    _capi.lib().lancet_raf_set_communicator(comm.handle, rank, world)
+    (y1,), name = raf.call("raf.op._all_to_all", [big])
+    assert name == "raf.op.nccl._all_to_all" and torch.equal(y1, comm.all_to_all(big))
+    (y2, c2), name = raf.call("raf.op._all_to_allv", [big], [counts.view(torch.uint64)])
+    assert name == "raf.op.nccl._all_to_allv" and torch.equal(y2, gn) and torch.equal(c2.view(torch.int64), rn.view(torch.int64))
+    _capi.lib().lancet_raf_set_communicator(None, 0, 1)
     comm.close()
     dist.barrier()
     sa.close()

@@ -225,3 +225,31 @@ def test_row_windows_tile_the_full_product(groups, LE, C, N, K, stages):
                                out=dout)
         assert torch.equal(dout, dfull)
     check_status()
+
+
+@pytest.mark.parametrize("C,G,M,N,elements,stride,offset,scale,dt", [
+    (256, 5, 768, 3072, [128, 32, 256, 32, 64], 2, 1, 1, torch.float16),   # the reference's own test configuration
+    (300, 3, 264, 256, [300, 0, 17], 1, 0, 1, torch.bfloat16),             # full, empty and ragged blocks; C, M off the tile
+    (128, 16, 128, 512, list(range(0, 128, 8)), 3, 2, 4, torch.bfloat16),  # counts given in units of 4 elements
+])
+def test_sparse_expert_matmul_nt(C, G, M, N, elements, stride, offset, scale, dt):
+    """tests/python/op/cublas/test_sparse_expert_matmul_nt.py of the reference: [C, G, M] x [N, M]^T with per-source
+    element counts; here the rows past the counts must come out zero."""
+    from oracle import moe_oracle as O
+    rng = np.random.default_rng(C + G)
+    x = rng.standard_normal((C, G, M)).astype(np.float32)
+    w = (rng.standard_normal((N, M)) * 0.1).astype(np.float32)
+    nelem = rng.integers(0, 256, size=stride * G).astype(np.int64)
+    for i, e in enumerate(elements):
+        nelem[i * stride + offset] = e * M // scale
+    xd = torch.from_numpy(x).to(DEV).to(dt)
+    wd = torch.from_numpy(w).to(DEV).to(dt)
+    out = torch.full((C, G, N), 9.0, device=DEV, dtype=dt)
+    LB.sparse_expert_matmul_nt(xd, wd, torch.from_numpy(nelem).to(DEV), offset, stride, scale, out=out)
+    ref = O.sparse_expert_matmul_nt(xd.float().cpu().numpy(), wd.float().cpu().numpy(), nelem, offset, stride, scale)
+    got = out.float().cpu().numpy()
+    for gi, e in enumerate(elements):
+        assert (got[e:, gi] == 0).all(), "rows past the count of block %d must be zero" % gi
+    scale_ = np.abs(ref).max() + 1e-6
+    assert np.abs(got - ref).max() <= 1e-2 * scale_          # 16-bit operands, fp32 accumulation
+    check_status()

@@ -31,6 +31,10 @@ def test_dialect_names_and_priorities():
     assert raf.dialect_ops("raf.op._all_to_all") == [("raf.op.nccl._all_to_all", "10")]
     assert raf.dialect_ops("raf.op.lans") == [("raf.op.cuda.lans", "20")]
     assert raf.dialect_ops("raf.op.matmul_nt") == [("raf.op.cublas.matmul_nt", "15")]
+    assert raf.dialect_ops("raf.op._all_to_allv") == [("raf.op.nccl._all_to_allv", "10")]
+    assert raf.dialect_ops("raf.op.sparse_expert_matmul_nt") == [("raf.op.cublas.sparse_expert_matmul_nt", "20")]
+    for op in ("matmul", "matmul_tn", "dense"):
+        assert raf.dialect_ops("raf.op." + op) == [("raf.op.cublas." + op, "15")]
     for op in ("moe_decode", "moe_encode_dx", "moe_encode_dg", "moe_decode_dx", "moe_decode_dg",
                "moe_encode_batch_prioritized", "moe_merge_masks", "moe_redispatch", "moe_redispatch_expert_input"):
         assert raf.dialect_ops("raf.op." + op) == [("raf.op.cuda." + op, "20")]
@@ -54,6 +58,17 @@ def test_declarations():
     assert outs[1] == ((2, 512), torch.int32) and outs[4] == ((8, 256, 512), torch.float32)
     assert raf.declare("raf.op.moe_merge_masks", [il, il, il], 8) == [((2, 3 * 2048), torch.int32)]
     assert raf.declare("raf.op.moe_redispatch", [torch.zeros(8, 16, 4).half()] * 2, [il, il]) == [((8, 16, 4), torch.float16)]
+    h = torch.zeros(1, dtype=torch.float16)
+    assert raf.declare("raf.op.matmul", h.expand(6, 4).contiguous(), h.expand(4, 8).contiguous()) == [((6, 8), torch.float16)]
+    assert raf.declare("raf.op.matmul_tn", h.expand(4, 6).contiguous(), h.expand(4, 8).contiguous()) == [((6, 8), torch.float16)]
+    assert raf.declare("raf.op.dense", h.expand(6, 4).contiguous(), h.expand(8, 4).contiguous()) == [((6, 8), torch.float16)]
+    ne = torch.zeros(10, dtype=torch.uint64)
+    assert raf.declare("raf.op.sparse_expert_matmul_nt", torch.zeros(256, 5, 64).half(), torch.zeros(128, 64).half(), ne, 1, 2,
+                       1) == [((256, 5, 128), torch.float16)]
+    with pytest.raises(raf.RafError, match="after stride"):
+        raf.declare("raf.op.sparse_expert_matmul_nt", torch.zeros(256, 4, 64).half(), torch.zeros(128, 64).half(), ne, 1, 2, 1)
+    assert raf.declare("raf.op._all_to_allv", [torch.zeros(4, 2, 6)], [torch.zeros(8, dtype=torch.uint64)]) == [
+        ((4, 2, 6), torch.float32), ((8,), torch.uint64)]
     with pytest.raises(raf.RafError, match="matching shape in dim 0"):
         raf.declare("raf.op.moe_encode", x, torch.zeros(100, 8), used, 1.0)
     with pytest.raises(raf.RafError, match="no declaration"):

@@ -74,6 +74,38 @@ def test_matmul_nt_dispatch_and_decline():
         raf.call("raf.op.matmul_nt", a.float(), b.float())
 
 
+def test_expert_gemm_family_through_registry():
+    """matmul / matmul_tn / dense (the forward, data-gradient and weight-gradient contractions of an expert layer,
+    src/op/grad/gemm.cc:31-36) and sparse_expert_matmul_nt dispatch to the tensor-core ops under the reference's names."""
+    g = torch.Generator(device=DEV).manual_seed(4)
+    a = torch.randn((384, 128), device=DEV, generator=g).bfloat16()
+    w = (torch.randn((128, 512), device=DEV, generator=g) * 0.1).bfloat16()
+    tol = lambda y, want: torch.allclose(y.float(), want, rtol=1e-2, atol=1e-2 * float(want.abs().max()))
+    (y,), name = raf.call("raf.op.matmul", a, w)
+    assert name == "raf.op.cublas.matmul" and tol(y, a.float() @ w.float())
+    (y,), name = raf.call("raf.op.dense", a, w.t().contiguous())
+    assert name == "raf.op.cublas.dense" and tol(y, a.float() @ w.float())
+    dy = torch.randn((384, 512), device=DEV, generator=g).bfloat16()
+    (dw,), name = raf.call("raf.op.matmul_tn", a, dy)
+    assert name == "raf.op.cublas.matmul_tn" and dw.shape == (128, 512) and tol(dw, a.float().t() @ dy.float())
+    with pytest.raises(raf.RafError, match="declined"):
+        raf.call("raf.op.matmul", a.float(), w.float())
+    # count-aware expert matmul in the [C, G, M] layout of the partitioned graphs
+    C, G, M, N = 256, 3, 128, 256
+    x = torch.randn((C, G, M), device=DEV, generator=g).half()
+    wt = (torch.randn((N, M), device=DEV, generator=g) * 0.1).half()
+    rows = [200, 0, 77]
+    nelem = torch.tensor([r * M for r in rows], dtype=torch.int64, device=DEV).view(torch.uint64)
+    (out,), name = raf.call("raf.op.sparse_expert_matmul_nt", x, wt, nelem, 0, 1, 1)
+    assert name == "raf.op.cublas.sparse_expert_matmul_nt"
+    want = torch.zeros((C, G, N), device=DEV)
+    for gi, r in enumerate(rows):
+        want[:r, gi] = x[:r, gi].float() @ wt.float().t()
+    assert tol(out, want)
+    for gi, r in enumerate(rows):
+        assert (out[r:, gi] == 0).all()
+
+
 def test_partitioned_graph_ops_through_registry():
     """n chained moe_encode + moe_merge_masks + moe_redispatch, as the reference's scheduler emits them
     (tests/python/op/cuda/test_cuda_moe.py:387-471), all through dispatch."""
