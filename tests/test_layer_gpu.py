@@ -162,8 +162,12 @@ def test_staged_pipeline_is_bit_identical(W, k, n, S, stages):
         assert torch.equal(got[1][r][1], ref[1][r][1]), "dgates[%d]" % r
         for a, b, name in zip(got[2][r], ref[2][r], ("dw1", "dw2", "db1", "db2")):
             assert torch.equal(a, b), "%s[%d]" % (name, r)
-    # the windows tile the live rows of every block exactly once
+    # the windows equal the CPU restatement and tile the live rows of every block exactly once
+    from oracle import moe_oracle as O
     for l in layers:
+        ob, oe, oc = O.stage_windows(l.moe.chain[l.moe.parity].cpu().numpy(), 128)
+        assert (l.win_begin.cpu().numpy() == ob).all() and (l.win_end.cpu().numpy() == oe).all()
+        assert (l.cnt.cpu().numpy() == oc).all()
         lo, hi, cnt = l.win_begin.cpu().numpy(), l.win_end.cpu().numpy(), l.cnt.cpu().numpy()
         assert (lo[0] == 0).all() and (hi[-1] == cnt).all()
         assert (lo[1:] == hi[:-1]).all() and (lo % 128 == 0).all()

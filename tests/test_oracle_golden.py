@@ -199,3 +199,17 @@ def test_all_to_all_pattern():
                 assert rcs[r][i * nch + j] == c
                 np.testing.assert_array_equal(o[i, j, :c], bufs[i].reshape(W, nch, 5)[r, j, :c])
                 assert np.all(o[i, j, c:] == 0)
+
+
+def test_stage_windows_tile_every_block_once():
+    """Windows of the staged exchange: contiguous, tile-aligned except at the total, monotone."""
+    rng = np.random.default_rng(5)
+    W, n, LE = 3, 4, 2
+    steps = rng.integers(0, 700, size=(W, n, LE))
+    chain = np.concatenate([np.zeros((W, 1, LE), np.int64), np.cumsum(steps, axis=1)], axis=1)
+    b, e, cnt = O.stage_windows(chain, 128)
+    assert (b[0] == 0).all() and (e[-1] == cnt).all() and (cnt == chain[:, n].reshape(-1)).all()
+    assert (b[1:] == e[:-1]).all() and (b % 128 == 0).all() and (e[:-1] % 128 == 0).all()
+    for c in range(n - 1):
+        assert (e[c] <= chain[:, c + 1].reshape(-1)).all()           # nothing that has not arrived yet
+        assert (chain[:, c + 1].reshape(-1) - e[c] < 128).all()      # and every whole tile that has
