@@ -326,7 +326,7 @@ int lancet_all_to_allv_p2p(const void* send, void* const* peer_recv, const uint6
  * nullable.  counts (nullable, device int32 [groups]): only the first counts[g] rows of group g are
  * computed; rows from counts[g] up to the end of the last 128-row tile that holds a live row are
  * written as zeros, later rows are not touched.  act: 0 none, 1 relu, 2 gelu (erf), 3 gelu (tanh).
- * N % 256 == 0, K % 8 == 0.
+ * N % 256 == 0, K % 8 == 0; A, B and bias 16-byte aligned, D and preact 32-byte aligned (32-byte stores).
  * status: device int32, zero when healthy; a bounded wait that gave up stores its site there
  * (read it with lancet_p2p_status). */
 int lancet_grouped_gemm_nt(const void* A, const void* B, void* D, const void* bias, void* preact, int groups,

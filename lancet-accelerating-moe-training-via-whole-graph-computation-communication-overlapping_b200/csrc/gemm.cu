@@ -141,6 +141,13 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 
 // Shared-memory matrix descriptor of a K-major tile stored as rows of 64 bf16 (128 bytes) with the
 // 128-byte swizzle TMA applies: 8 rows form a 1024-byte atom, atoms follow each other along M/N.
+// 32-byte store (one full sector per lane): half as many store transactions as two 16-byte stores.
+__device__ __forceinline__ void st_global_32B(void* ptr, const uint4& a, const uint4& b) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(ptr), "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w),
+               "r"(b.x), "r"(b.y), "r"(b.z), "r"(b.w)
+               : "memory");
+}
+
 __device__ __forceinline__ uint64_t smem_desc_k_sw128(uint32_t addr) {
   uint64_t d = 0;
   d |= (uint64_t)((addr >> 4) & 0x3FFF);   // start address
@@ -172,9 +179,29 @@ __device__ __forceinline__ uint32_t instr_desc(bool a_mn, bool b_mn) {
          ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);  // D = f32
 }
 
-__device__ __forceinline__ float dactivate(float x, int act) {
+// erf(|x| / sqrt 2) and exp(-x^2 / 2) from one reciprocal, one exp2 and a degree-5 polynomial (Abramowitz & Stegun
+// 7.1.26, absolute error 6e-7 in float32: three orders below the rounding of a 16-bit output).  The library erff costs
+// about twice the instructions, and the epilogue's FP32 work is what holds the first expert GEMM back.
+__device__ __forceinline__ void erf_exp_half_sq(float x, float* erf_abs, float* e) {
+  const float z = fabsf(x) * 0.70710678118654752f;
+  const float t = __fdividef(1.0f, fmaf(0.3275911f, z, 1.0f));
+  float poly = fmaf(1.061405429f, t, -1.453152027f);
+  poly = fmaf(poly, t, 1.421413741f);
+  poly = fmaf(poly, t, -0.284496736f);
+  poly = fmaf(poly, t, 0.254829592f);
+  poly *= t;
+  *e = __expf(-z * z);
+  *erf_abs = fmaf(-poly, *e, 1.0f);
+}
+
+template <int act>
+__device__ __forceinline__ float dactivate(float x) {
   if (act == 1) return x > 0.f ? 1.f : 0.f;
-  if (act == 2) return 0.5f * (1.0f + erff(x * 0.70710678118654752f)) + x * 0.3989422804014327f * __expf(-0.5f * x * x);
+  if (act == 2) {
+    float ea, e;
+    erf_exp_half_sq(x, &ea, &e);
+    return fmaf(0.5f, copysignf(ea, x), 0.5f) + x * 0.3989422804014327f * e;
+  }
   if (act == 3) {
     const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
     const float t = tanhf(u);
@@ -244,9 +271,14 @@ __device__ __forceinline__ Tile decode_tile(const Params& p, Sched& sc, int t) {
   return tl;
 }
 
-__device__ __forceinline__ float activate(float v, int act) {
+template <int act>
+__device__ __forceinline__ float activate(float v) {
   if (act == 1) return fmaxf(v, 0.f);
-  if (act == 2) return 0.5f * v * (1.0f + erff(v * 0.70710678118654752f));
+  if (act == 2) {
+    float ea, e;
+    erf_exp_half_sq(v, &ea, &e);
+    return v * fmaf(0.5f, copysignf(ea, v), 0.5f);
+  }
   if (act == 3) return 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
   return v;
 }
@@ -259,7 +291,10 @@ __device__ __forceinline__ int tile_k_blocks(const Params& p, const Tile& tl) {
   return n;
 }
 
-template <typename T, int MODE, bool B_MN, int EPI>
+// ACT is a template parameter: with the activation chosen at run time inside the element loop every element
+// became its own chain of basic blocks, the 32 independent chains of a lane could not be interleaved, and the
+// GELU epilogue (latency-bound, 1.5 ms against 1.1 ms without it) held the tensor pipe back.
+template <typename T, int MODE, bool B_MN, int EPI, int ACT>
 __global__ void __launch_bounds__(THREADS, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, Params p) {
   constexpr bool A_MN = (MODE == MODE_REDUCE);
@@ -479,25 +514,36 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             for (int q = 0; q < 4; ++q) reinterpret_cast<uint4*>(pre)[q] = pp[q];
 #pragma unroll
             for (int i = 0; i < 32; ++i)
-              o[i] = Num<T>::from_f(__uint_as_float(r[i]) * dactivate(Num<T>::to_f(pre[i]), p.act));
+              o[i] = Num<T>::from_f(__uint_as_float(r[i]) * dactivate<ACT>(Num<T>::to_f(pre[i])));
           } else {
             alignas(16) T pre[32];
+            alignas(16) T bv[32];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) reinterpret_cast<uint4*>(bv)[q] = make_uint4(0, 0, 0, 0);
+            if (bias) {
+              // N is a multiple of 256 and col0 of 32: 16-byte loads as long as the bias base is 16-byte aligned
+              const uint4* bp = reinterpret_cast<const uint4*>(bias + (size_t)e * p.N + col0);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) reinterpret_cast<uint4*>(bv)[q] = __ldg(bp + q);
+            }
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
               float v = __uint_as_float(r[i]);
-              if (bias) v += Num<T>::to_f(bias[(size_t)e * p.N + col0 + i]);
+              v += Num<T>::to_f(bv[i]);
               pre[i] = Num<T>::from_f(v);
-              o[i] = Num<T>::from_f(activate(v, p.act));
+              o[i] = Num<T>::from_f(activate<ACT>(v));
             }
             if (PRE) {
               uint4* dp = reinterpret_cast<uint4*>(PRE + out_row * p.N + col0);
 #pragma unroll
-              for (int q = 0; q < 4; ++q) dp[q] = reinterpret_cast<const uint4*>(pre)[q];
+              for (int q = 0; q < 4; q += 2)
+                st_global_32B(dp + q, reinterpret_cast<const uint4*>(pre)[q], reinterpret_cast<const uint4*>(pre)[q + 1]);
             }
           }
           uint4* dst = reinterpret_cast<uint4*>(D + out_row * p.N + col0);
 #pragma unroll
-          for (int q = 0; q < 4; ++q) dst[q] = reinterpret_cast<const uint4*>(o)[q];
+          for (int q = 0; q < 4; q += 2)
+            st_global_32B(dst + q, reinterpret_cast<const uint4*>(o)[q], reinterpret_cast<const uint4*>(o)[q + 1]);
         }
       }
       tc_fence_before();
@@ -643,20 +689,36 @@ static int make_map3(CUtensorMap* map, const void* base, uint64_t groups, uint64
   return LANCET_OK;
 }
 
-template <typename T, int MODE, bool B_MN, int EPI>
-static int launch_t(const CUtensorMap& tmA, const CUtensorMap& tmB, const Params& p, const char* name, cudaStream_t st) {
+template <typename T, int MODE, bool B_MN, int EPI, int ACT>
+static int launch_a(const CUtensorMap& tmA, const CUtensorMap& tmB, const Params& p, const char* name, cudaStream_t st) {
   static bool attr_set = false;
   if (!attr_set) {
-    LANCET_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel<T, MODE, B_MN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    LANCET_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel<T, MODE, B_MN, EPI, ACT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     SMEM_BYTES));
     attr_set = true;
   }
   int grid = sm_count();
   if (grid > p.total_tiles) grid = p.total_tiles;
   {
     ProfScope prof(name, st);
-    grouped_gemm_kernel<T, MODE, B_MN, EPI><<<grid, THREADS, SMEM_BYTES, st>>>(tmA, tmB, p);
+    grouped_gemm_kernel<T, MODE, B_MN, EPI, ACT><<<grid, THREADS, SMEM_BYTES, st>>>(tmA, tmB, p);
   }
   return launch_status(name);
+}
+
+// Only the combinations that exist are instantiated: the forward form takes any activation, the data-gradient form
+// either none (EPI_ACT) or the derivative of one (EPI_DACT), the weight-gradient form none.
+template <typename T, int MODE, bool B_MN, int EPI>
+static int launch_t(const CUtensorMap& tmA, const CUtensorMap& tmB, const Params& p, const char* name, cudaStream_t st) {
+  if constexpr (MODE == MODE_ROWS && (EPI == EPI_DACT || !B_MN)) {
+    if (p.act == 1) return launch_a<T, MODE, B_MN, EPI, 1>(tmA, tmB, p, name, st);
+    if (p.act == 2) return launch_a<T, MODE, B_MN, EPI, 2>(tmA, tmB, p, name, st);
+    if (p.act == 3) return launch_a<T, MODE, B_MN, EPI, 3>(tmA, tmB, p, name, st);
+  }
+  if constexpr (EPI == EPI_DACT)
+    return fail(LANCET_ERR_INVALID, "%s: an activation derivative needs an activation", name);
+  else
+    return launch_a<T, MODE, B_MN, EPI, 0>(tmA, tmB, p, name, st);
 }
 
 template <int MODE, bool B_MN, int EPI>
@@ -683,7 +745,8 @@ static int rows_common(const char* fn, const void* A, const void* B, void* D, in
   LANCET_REQUIRE(act >= 0 && act <= 3, LANCET_ERR_INVALID, "%s: unknown activation %d", fn, act);
   if (C == 0) return LANCET_OK;
   LANCET_REQUIRE(A && B && D && status, LANCET_ERR_NULL, "%s: null pointer argument", fn);
-  LANCET_REQUIRE(aligned(A, 16) && aligned(B, 16) && aligned(D, 16), LANCET_ERR_INVALID, "%s: operands must be 16-byte aligned", fn);
+  LANCET_REQUIRE(aligned(A, 16) && aligned(B, 16) && aligned(D, 32), LANCET_ERR_INVALID,
+                 "%s: inputs must be 16-byte aligned, the output 32-byte aligned", fn);
   LANCET_REQUIRE((long long)groups * C < (1ll << 31) && (long long)LE * N < (1ll << 31) && (long long)LE * K < (1ll << 31),
                  LANCET_ERR_INVALID, "%s: row counts exceed 2^31", fn);
   p->groups = groups; p->LE = LE; p->C = C; p->N = N; p->K = K; p->Mout = 0;
@@ -713,7 +776,8 @@ int lancet_grouped_gemm_nt_window(const void* A, const void* B, void* D, const v
   Params p;
   if (int rc = rows_common("lancet_grouped_gemm_nt", A, B, D, groups, LE, C, N, K, act, dtype, status, &p)) return rc;
   if (C == 0) return LANCET_OK;
-  LANCET_REQUIRE(aligned(bias, 2) && aligned(preact, 16), LANCET_ERR_INVALID, "lancet_grouped_gemm_nt: bias/preact alignment");
+  LANCET_REQUIRE(aligned(bias, 16) && aligned(preact, 32), LANCET_ERR_INVALID,
+                 "lancet_grouped_gemm_nt: bias must be 16-byte aligned, preact 32-byte aligned");
   p.counts = row_end; p.row_lo = row_begin; p.bias = bias; p.D = D; p.preact = preact; p.epi = EPI_ACT;
   CUtensorMap tmA, tmB;
   if (int rc = make_map(&tmA, A, (uint64_t)groups * C, (uint64_t)K, BM, dtype)) return rc;
@@ -763,8 +827,8 @@ int lancet_grouped_gemm_tn(const void* A, const void* B, void* D, int groups, in
   LANCET_REQUIRE(Mout % BM == 0 && N % BN == 0, LANCET_ERR_INVALID,
                  "lancet_grouped_gemm_tn: Mout=%d must be a multiple of %d and N=%d of %d", Mout, BM, N, BN);
   LANCET_REQUIRE(D && status && (C == 0 || (A && B)), LANCET_ERR_NULL, "lancet_grouped_gemm_tn: null pointer argument");
-  LANCET_REQUIRE(aligned(A, 16) && aligned(B, 16) && aligned(D, 16), LANCET_ERR_INVALID,
-                 "lancet_grouped_gemm_tn: operands must be 16-byte aligned");
+  LANCET_REQUIRE(aligned(A, 16) && aligned(B, 16) && aligned(D, 32), LANCET_ERR_INVALID,
+                 "lancet_grouped_gemm_tn: inputs must be 16-byte aligned, the output 32-byte aligned");
   LANCET_REQUIRE((long long)groups * C < (1ll << 31) && (long long)LE * Mout < (1ll << 31), LANCET_ERR_INVALID,
                  "lancet_grouped_gemm_tn: row counts exceed 2^31");
   Params p;
