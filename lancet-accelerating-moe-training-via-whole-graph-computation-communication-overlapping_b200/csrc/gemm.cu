@@ -45,7 +45,7 @@ constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
 // MODE_REDUCE: D[e] (Mout x N) = sum over groups g of expert e and their live rows r of A[g][r][:]^T * B[g][r][:]
 //              ("TN": weight gradients), tiles over (expert, m-tile, n-tile), reduction over rows.
 constexpr int MODE_ROWS = 0, MODE_REDUCE = 1;
-constexpr int EPI_ACT = 0, EPI_DACT = 1;
+constexpr int EPI_ACT = 0, EPI_DACT = 1, EPI_ACT_PRE = 2;  // ACT_PRE: as ACT, and the pre-activation is stored too
 
 struct Params {
   int groups, LE, C, N, K;
@@ -533,7 +533,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
               pre[i] = Num<T>::from_f(v);
               o[i] = Num<T>::from_f(activate<ACT>(v));
             }
-            if (PRE) {
+            if (EPI == EPI_ACT_PRE) {
               uint4* dp = reinterpret_cast<uint4*>(PRE + out_row * p.N + col0);
 #pragma unroll
               for (int q = 0; q < 4; q += 2)
@@ -782,6 +782,8 @@ int lancet_grouped_gemm_nt_window(const void* A, const void* B, void* D, const v
   CUtensorMap tmA, tmB;
   if (int rc = make_map(&tmA, A, (uint64_t)groups * C, (uint64_t)K, BM, dtype)) return rc;
   if (int rc = make_map(&tmB, B, (uint64_t)LE * N, (uint64_t)K, BN, dtype)) return rc;
+  if (preact)
+    return launch<MODE_ROWS, false, EPI_ACT_PRE>(tmA, tmB, p, dtype, "grouped_gemm_nt_kernel", static_cast<cudaStream_t>(stream));
   return launch<MODE_ROWS, false, EPI_ACT>(tmA, tmB, p, dtype, "grouped_gemm_nt_kernel", static_cast<cudaStream_t>(stream));
 }
 
