@@ -719,7 +719,8 @@ def run_gpt(args):
     else:
         fabric = LB.LocalFabric(1, 0, {})
     vocab, m, nh, nl, seq, batch, ffn = 50257, 1024, 16, 12, 512, 16, 4096
-    model = GPTMoE(vocab, m, nh, nl, seq, batch, ffn, 2 * world, TOP_K, CAP_FACTOR, N_CHUNKS, dev, fabric=fabric, seed=0)
+    model = GPTMoE(vocab, m, nh, nl, seq, batch, ffn, 2 * world, TOP_K, CAP_FACTOR, N_CHUNKS, dev, fabric=fabric, seed=0,
+                   act="relu")     # the reference's GPT-2 blocks use ReLU
     trainer = LansTrainer(model, lr=1e-3)
     g = torch.Generator(device=dev).manual_seed(1000 + rank)
     ids = [torch.randint(0, vocab, (batch, seq), device=dev, generator=g) for _ in range(2)]

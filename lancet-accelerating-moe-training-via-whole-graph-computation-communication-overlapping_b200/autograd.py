@@ -46,10 +46,10 @@ class MoE(torch.nn.Module):
     this rank's local experts; the layer computes in `dtype`."""
 
     def __init__(self, tokens, model_dim, hidden_dim, world_experts, k=2, capacity_factor=1.25, n_chunks=1,
-                 dtype=torch.bfloat16, device="cuda", local_experts=2, fabric=None, group=None, seed=0):
+                 dtype=torch.bfloat16, device="cuda", local_experts=2, fabric=None, group=None, seed=0, act="gelu"):
         super().__init__()
         self.layer = MoELayer(tokens, model_dim, hidden_dim, k, capacity_factor, n_chunks, dtype, device, local_experts,
-                              fabric=fabric, group=group, seed=seed)
+                              fabric=fabric, group=group, seed=seed, act=act)
         assert self.layer.moe.E == world_experts
         self.wg = torch.nn.Linear(model_dim, world_experts, bias=False, device=device)
         self.w1 = torch.nn.Parameter(self.layer.w1.float().clone())

@@ -38,7 +38,9 @@ class Block(torch.nn.Module):
 
 class GPTMoE(torch.nn.Module):
     def __init__(self, vocab, m, nh, nl, seq, batch, ffn_dim, world_experts, k=2, capacity_factor=1.25, n_chunks=4,
-                 device="cuda", fabric=None, group=None, seed=0):
+                 device="cuda", fabric=None, group=None, seed=0, act="gelu"):
+        """act: activation of every FFN; the reference's GPT-2 uses ReLU (models/benchmark/pytorch/nlp.py:161-165),
+        its BERT / ViT GELU (:137-141)."""
         super().__init__()
         torch.manual_seed(seed)
         self.emb = torch.nn.Embedding(vocab, m)
@@ -47,9 +49,10 @@ class GPTMoE(torch.nn.Module):
         for i in range(nl):
             if i % 2 == 1:
                 ffn = MoE(seq * batch, m, ffn_dim, world_experts, k, capacity_factor, n_chunks, torch.bfloat16, device, 2,
-                          fabric=fabric, group=group, seed=seed + i)
+                          fabric=fabric, group=group, seed=seed + i, act=act)
             else:
-                ffn = torch.nn.Sequential(torch.nn.Linear(m, ffn_dim), torch.nn.GELU(), torch.nn.Linear(ffn_dim, m))
+                ffn = torch.nn.Sequential(torch.nn.Linear(m, ffn_dim), torch.nn.ReLU() if act == "relu" else torch.nn.GELU(),
+                                          torch.nn.Linear(ffn_dim, m))
             blocks.append(Block(m, nh, ffn))
         self.blocks = torch.nn.ModuleList(blocks)
         self.ln = torch.nn.LayerNorm(m)

@@ -26,7 +26,9 @@ class MoELayer:
         self.b2 = (torch.randn((local_experts, M), device=d, generator=g) * 0.02).to(dtype)
         G = W * local_experts
         self.h = torch.empty((G, C, H), dtype=dtype, device=d)
-        self.hpre = torch.empty((G, C, H), dtype=dtype, device=d)
+        # ReLU's derivative can be read off the activated output (h > 0 iff pre > 0): no pre-activation copy, which
+        # saves a second [G, C, H] output of the first GEMM and its buffer
+        self.hpre = None if act == "relu" else torch.empty((G, C, H), dtype=dtype, device=d)
         self.dh = torch.empty((G, C, H), dtype=dtype, device=d)
         self.dw1 = torch.empty_like(self.w1)
         self.dw2 = torch.empty_like(self.w2)
@@ -150,7 +152,7 @@ class MoELayer:
 
     def bwd_stage_experts_1(self, c):
         lo, hi = self._window(c)
-        ops.grouped_gemm_nn(self.dy, self.w2, counts=hi, row_begin=lo, act=self.act, preact=self.hpre, out=self.dh)
+        ops.grouped_gemm_nn(self.dy, self.w2, counts=hi, row_begin=lo, act=self.act, preact=self.h if self.hpre is None else self.hpre, out=self.dh)
 
     def bwd_stage_experts_2(self, c):
         lo, hi = self._window(c)
@@ -212,7 +214,7 @@ class MoELayer:
         dy = d_eo.view(self.G, self.C, self.M)
         main = torch.cuda.current_stream(self.device)
         # dH first: both the data path (dX) and dW1 need it
-        ops.grouped_gemm_nn(dy, self.w2, counts=self.cnt, act=self.act, preact=self.hpre, out=self.dh)
+        ops.grouped_gemm_nn(dy, self.w2, counts=self.cnt, act=self.act, preact=self.h if self.hpre is None else self.hpre, out=self.dh)
         if self.side is not None:
             self.side.wait_stream(main)
         ops.grouped_gemm_nn(self.dh, self.w1, counts=self.cnt, out=self.moe.d_expert_in.view(self.G, self.C, self.M))
