@@ -580,7 +580,7 @@ def run_layer(args):
             layer.backward(dout)
 
     # the three schedules take turns in short bursts, so that clock drift under the power cap hits them alike
-    order = ("pipelined", True, False)
+    order = {"all": ("pipelined", True, False), "staged": ("pipelined",), "side": (True,), "single": (False,)}[args.schedule]
     rounds = 5 if args.steps >= 5 else 1
     per_round = max(args.steps // rounds, 1)
     results = {m: 0.0 for m in order}
@@ -621,7 +621,7 @@ def run_layer(args):
         dist.destroy_process_group()
     if rank != 0:
         return
-    ms = min(results["pipelined"], results[True])
+    ms = min(results.values())
     flops = 6.0 * 2.0 * live * M_DIM * H            # per GPU: 2 GEMMs forward, 4 backward, live rows only
     peaks, peak_kind = load_peaks()
     sustained = float(peaks.get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops"]))
@@ -633,8 +633,8 @@ def run_layer(args):
             S_TOKENS, M_DIM, H, 2 * world, TOP_K, CAP_FACTOR, N_CHUNKS), "l2": "GBs touched per step exceed the 126 MB L2"},
         "tflops_per_gpu": flops / (ms / 1e3) / 1e12, "tensor_frac": flops / (ms / 1e3) / 1e12 / sustained,
         "peak_kind": peak_kind + " (sustained cuBLAS bf16)", "live_rows_rank0": live,
-        "schedules": {"pipeline_stages": args.stages, "ms_pipelined_exchange": results["pipelined"], "ms_dw_on_side_stream": results[True],
-                      "ms_single_stream": results[False]},
+        "schedules": {"pipeline_stages": args.stages, "ms_pipelined_exchange": results.get("pipelined"),
+                      "ms_dw_on_side_stream": results.get(True), "ms_single_stream": results.get(False)},
     })
 
 
@@ -787,6 +787,8 @@ def _main():
     ap.add_argument("--workload", default="moe", choices=["moe", "lans", "ffn", "layer", "a2a", "gpt"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-graph", action="store_true", help="launch every step eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--schedule", default="all", choices=["all", "staged", "side", "single"],
+                    help="layer workload: which schedules to time (all: the three take turns)")
     ap.add_argument("--stages", type=int, default=4, help="layer workload: exchange stages of the pipelined schedule")
     ap.add_argument("--lans-layers", type=int, default=24, help="transformer layers in the LANS tensor list (24 = 196 tensors)")
     args = ap.parse_args()
