@@ -83,7 +83,9 @@ def run_case(ref, name, S, E, M, seed, gate_kind, store_data):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py <checkout of the reference project>")
+    ref_root = sys.argv[1]
     ref = load_reference_utils(ref_root)
     # config "single-rank CPU MoE dispatch/combine": S=2048, E=8, M=512, softmax gate, seed 0
     run_case(ref, "c1_s2048_e8_m512", 2048, 8, 512, 0, "softmax", store_data=False)
