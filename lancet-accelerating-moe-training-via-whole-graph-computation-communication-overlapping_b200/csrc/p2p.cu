@@ -200,20 +200,38 @@ combine_bwd_peer_kernel(const float* __restrict__ gates, const int32_t* __restri
       g[j] = gates[il_index_p2p((int)s, Sp, K, j)];
     }
     const P* src = reinterpret_cast<const P*>(dout + (size_t)s * M);
-    for (int v = lane; v < row_vecs; v += 32) {
-      const P d = src[v];
+    // U vectors of the row in flight per lane (a single one left the kernel latency-bound at half the bandwidth);
+    // every lane still meets its elements in the same order, so the dot products keep their bits
+    constexpr int U = 4;
+    for (int base = 0; base < row_vecs; base += 32 * U) {
+      P d[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int v = base + u * 32 + lane;
+        if (v < row_vecs) d[u] = src[v];
+      }
 #pragma unroll
       for (int j = 0; j < K; ++j) {
         if (!drow[j]) continue;
-        const P e = erow[j][v];
-        P o;
+        P e[U];
 #pragma unroll
-        for (int i = 0; i < N; ++i) {
-          const float dv = Num<T>::to_f(d.v[i]);
-          o.v[i] = Num<T>::from_f(__fmul_rn(g[j], dv));
-          dot[j] = fmaf(Num<T>::to_f(e.v[i]), dv, dot[j]);
+        for (int u = 0; u < U; ++u) {
+          const int v = base + u * 32 + lane;
+          if (v < row_vecs) e[u] = erow[j][v];
         }
-        drow[j][v] = o;
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int v = base + u * 32 + lane;
+          if (v >= row_vecs) continue;
+          P o;
+#pragma unroll
+          for (int i = 0; i < N; ++i) {
+            const float dv = Num<T>::to_f(d[u].v[i]);
+            o.v[i] = Num<T>::from_f(__fmul_rn(g[j], dv));
+            dot[j] = fmaf(Num<T>::to_f(e[u].v[i]), dv, dot[j]);
+          }
+          drow[j][v] = o;
+        }
       }
     }
 #pragma unroll
