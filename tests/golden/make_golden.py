@@ -8,6 +8,23 @@ It imports models/benchmark/pytorch/utils.py from the reference (FakeMoeEncodeOp
 FakeMoeDecodeOp: lines 313-501 of that file), runs them forward and backward on
 seeded inputs and writes tests/golden/moe_ref_*.npz.  The fixtures are committed;
 the GPU box has no reference checkout, so tests only ever read the .npz files.
+
+Two more families:
+  * top2_ref_*.npz: the reference's top-2 gate, `top2gating` of
+    docker/resources/sharded_moe.py:253-324, imported with the absent `deepspeed`
+    package stubbed and its Gumbel sampler returning zeros (the deterministic part of
+    the gate).  The function's own local variables at its return (indices, locations
+    before and after the capacity mask, normalised gates) are recorded through a
+    profile hook, so every stored vector was computed by the reference's code.  For the
+    small cases the dense dispatch and combine einsums of MOELayer.forward (:476-478,
+    :512-514) are stored too.
+  * chain_ref_*.npz: FakeMoeEncodeOp called on consecutive token chunks with each
+    call's used capacity fed to the next one, the way the partition pass chains field 2
+    of moe_encode (src/pass/dist_optimization/partition_exprs.cc:1784-1792).  With a
+    non-zero used capacity only `indices_locations` and `gates_s` of that operator agree
+    with the CUDA operator (drop rule loc >= C - used, tutel_moe_dispatch.cu:199-201);
+    its `used_capacity` output is max(loc)+1 instead of min(used + count, C) (:207-209),
+    so the chain is fed with the CUDA rule and only the two agreeing outputs are pinned.
 """
 import hashlib
 import importlib.util
@@ -82,6 +99,104 @@ def run_case(ref, name, S, E, M, seed, gate_kind, store_data):
     print(name, "C", C, "dropped", int((idx_loc[0] < 0).sum()), "capused", capused.tolist()[:8])
 
 
+def load_reference_sharded_moe(ref_root):
+    """docker/resources/sharded_moe.py with `deepspeed` (absent here) stubbed: it is only used for timers and logging."""
+    import logging
+    ds = types.ModuleType("deepspeed")
+    ds.__path__ = []
+    du = types.ModuleType("deepspeed.utils")
+    du.__path__ = []
+    dt = types.ModuleType("deepspeed.utils.timer")
+    dt.ThroughputTimer = type("ThroughputTimer", (), {})
+    dt.SynchronizedWallClockTimer = type("SynchronizedWallClockTimer", (), {})
+    du.logger = logging.getLogger("deepspeed")
+    du.log_dist = lambda *a, **k: None
+    du.timer = dt
+    ds.utils = du
+    sys.modules.update({"deepspeed": ds, "deepspeed.utils": du, "deepspeed.utils.timer": dt})
+    path = os.path.join(ref_root, "docker", "resources", "sharded_moe.py")
+    spec = importlib.util.spec_from_file_location("ref_sharded_moe", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    # noise off: the second choice becomes the plain argmax with the first one masked
+    mod.gumbel_rsample = lambda shape, device: torch.zeros(shape, device=device)
+    return mod
+
+
+def call_with_locals(fn, *args):
+    """Runs fn and returns (result, the function's local variables at its return)."""
+    grabbed = {}
+
+    def hook(frame, event, arg):
+        if event == "return" and frame.f_code is fn.__code__:
+            grabbed.update(frame.f_locals)
+
+    sys.setprofile(hook)
+    try:
+        res = fn(*args)
+    finally:
+        sys.setprofile(None)
+    return res, grabbed
+
+
+def run_top2_case(sm, name, S, E, M, cf, seed, dense, spread=0.0):
+    g = torch.Generator().manual_seed(seed)
+    # `spread` tilts the logits towards the higher-numbered experts, so that their loads exceed the capacity and choices drop
+    logits = torch.randn(S, E, generator=g) + spread * torch.linspace(-1.0, 1.0, E)
+    (l_aux, combine, mask, exp_counts), loc = call_with_locals(sm.top2gating, logits, cf)
+    gates = loc["gates"]
+    rows = torch.arange(S)
+    i1, i2 = loc["indices1_s"], loc["indices2_s"]
+    # the choice made on the logits must be the choice the probabilities give (no rounding ties in softmax)
+    g_wo1 = gates.masked_fill(torch.nn.functional.one_hot(i1, E).bool(), float("-inf"))
+    assert torch.equal(torch.argmax(g_wo1, dim=1), i2), "softmax rounding tie: pick another seed"
+    rec = dict(
+        S=S, E=E, M=M, C=int(loc["capacity"]), cf=np.float32(cf), seed=seed, logits=logits.numpy(), gate=gates.numpy(),
+        idx1=i1.numpy().astype(np.int32), idx2=i2.numpy().astype(np.int32),
+        loc1_all=loc["locations1"][rows, i1].numpy().astype(np.int32),      # before the capacity mask
+        loc2_all=loc["locations2"][rows, i2].numpy().astype(np.int32),      # offset by the first choices, before the mask
+        kept1=loc["mask1"].sum(dim=1).numpy().astype(np.int32), kept2=loc["mask2"].sum(dim=1).numpy().astype(np.int32),
+        loc1_s=loc["locations1_s"].numpy().astype(np.int32), loc2_s=loc["locations2_s"].numpy().astype(np.int32),
+        gates1_s=loc["gates1_s"].numpy(), gates2_s=loc["gates2_s"].numpy(), exp_counts=exp_counts.numpy().astype(np.int64),
+    )
+    if dense:
+        x = torch.randn(S, M, generator=g)
+        disp = sm.einsum("sec,sm->ecm", mask.type_as(x), x)                  # MOELayer.forward, sharded_moe.py:476-478
+        eo = torch.randn(E, rec["C"], M, generator=g)
+        out = sm.einsum("sec,ecm->sm", combine.type_as(x), eo)               # :512-514
+        rec.update(x=x.numpy(), disp=disp.numpy(), eo=eo.numpy(), out=out.numpy())
+    np.savez_compressed(os.path.join(HERE, f"top2_ref_{name}.npz"), **rec)
+    print("top2", name, "C", rec["C"], "dropped", int((rec["kept1"] == 0).sum()), int((rec["kept2"] == 0).sum()))
+
+
+def run_chain_case(ref, name, S, E, M, n, seed, first_used=None):
+    """n consecutive chunks of S//n tokens through FakeMoeEncodeOp, used capacity chained.  `first_used` = "random"
+    starts the chain from a used capacity drawn in [0, C] per expert (as left by earlier partitions) instead of zero."""
+    g = torch.Generator().manual_seed(seed)
+    gate = torch.softmax(torch.randn(S, E, generator=g) * 1.5, dim=1)
+    x = torch.randn(S, M, generator=g)
+    Sp = S // n
+    C = (Sp + E - 1) // E
+    used = torch.zeros(E, dtype=torch.int32)
+    if first_used == "random":
+        used = torch.randint(0, C + 1, (E,), generator=g).to(torch.int32)
+    il, gs, used_in, ref_used_out = [], [], [], []
+    for c in range(n):
+        sl = slice(c * Sp, (c + 1) * Sp)
+        gates_s, idx_loc, capused, elems, disp = ref.FakeMoeEncodeOp.apply(x[sl], gate[sl], used.clone(), torch.ones(1))
+        il.append(idx_loc.numpy().astype(np.int32))
+        gs.append(gates_s.numpy())
+        used_in.append(used.numpy().copy())
+        ref_used_out.append(capused.numpy().astype(np.int32))
+        # next call's used capacity by the CUDA operator's rule (gen_location_kernel, tutel_moe_dispatch.cu:207-209)
+        cnt = torch.bincount(torch.argmax(gate[sl], dim=1), minlength=E).to(torch.int32)
+        used = torch.minimum(used + cnt, torch.tensor(C, dtype=torch.int32))
+    np.savez_compressed(os.path.join(HERE, f"chain_ref_{name}.npz"), S=S, E=E, M=M, n=n, C=C, seed=seed, gate=gate.numpy(),
+                        idx_loc=np.stack(il), gates_s=np.stack(gs), used_in=np.stack(used_in),
+                        fake_used_out=np.stack(ref_used_out))
+    print("chain", name, "C", C, "dropped per chunk", [int((a[0] < 0).sum()) for a in il], "used_in", used_in[-1].tolist())
+
+
 def main():
     if len(sys.argv) < 2:
         raise SystemExit("usage: python tests/golden/make_golden.py <checkout of the reference project>")
@@ -95,6 +210,17 @@ def main():
     # ragged: S not a multiple of E, tiny
     run_case(ref, "rag_s193_e5_m4", 193, 5, 4, 3, "softmax", store_data=True)
     run_case(ref, "two_s64_e2_m16", 64, 2, 16, 4, "softmax", store_data=True)
+    # non-zero used capacity: chained chunks (capacity factor 1.0 is all the reference's CPU operator accepts)
+    run_chain_case(ref, "s2048_e8_n4", 2048, 8, 4, 4, 5)
+    run_chain_case(ref, "s772_e5_n4", 772, 5, 4, 4, 6)
+    run_chain_case(ref, "s2048_e8_n2_used", 2048, 8, 4, 2, 7, first_used="random")
+    # top-2: shapes where ceil(2S/E * cf) of the reference equals this project's int(cf * ceil(2S/E))
+    sm = load_reference_sharded_moe(ref_root)
+    run_top2_case(sm, "s4096_e16", 4096, 16, 8, 1.25, 10, dense=False, spread=0.6)
+    run_top2_case(sm, "s4096_e2", 4096, 2, 8, 1.25, 11, dense=False)
+    run_top2_case(sm, "s512_e4", 512, 4, 8, 1.25, 12, dense=True)
+    run_top2_case(sm, "rag_s193_e5", 193, 5, 4, 1.25, 13, dense=True, spread=0.6)
+    run_top2_case(sm, "s256_e8_cf05", 256, 8, 4, 0.5, 14, dense=True)
 
 
 if __name__ == "__main__":

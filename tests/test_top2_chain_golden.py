@@ -1,0 +1,115 @@
+"""Pins top-2 gating and gating under a non-zero used capacity to vectors computed by the reference's own code
+(tests/golden/make_golden.py): `top2gating` of docker/resources/sharded_moe.py:253-324 with its noise off, and
+FakeMoeEncodeOp (models/benchmark/pytorch/utils.py:313-379) called on chained chunks.  The CPU tests check the
+NumPy oracle, the GPU tests the CUDA kernels through the C ABI, both against the same files."""
+import glob
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import moe_oracle as O
+
+HERE = os.path.dirname(__file__)
+TOP2 = sorted(glob.glob(os.path.join(HERE, "golden", "top2_ref_*.npz")))
+CHAIN = sorted(glob.glob(os.path.join(HERE, "golden", "chain_ref_*.npz")))
+ids = lambda p: os.path.basename(p)[:-4]
+
+
+def check_top2(rec, gs, il, cap):
+    """gs [2,S] float32, il [4,S] int32, cap [E] int32 of a top-2 gate against the reference's vectors."""
+    S, E, C = int(rec["S"]), int(rec["E"]), int(rec["C"])
+    kept1, kept2 = rec["kept1"] == 1, rec["kept2"] == 1
+    # expert choice: reference indices where kept, -1 where the reference's capacity mask removed the choice
+    np.testing.assert_array_equal(il[0], np.where(kept1, rec["idx1"], -1))
+    np.testing.assert_array_equal(il[2], np.where(kept2, rec["idx2"], -1))
+    # locations before the mask (the second choice is offset by the count of first choices, sharded_moe.py:282-285)
+    np.testing.assert_array_equal(il[1], rec["loc1_all"])
+    np.testing.assert_array_equal(il[3], rec["loc2_all"])
+    # ... and after it, as the reference stores them (zero for a dropped choice)
+    np.testing.assert_array_equal(np.where(il[0] >= 0, il[1], 0), rec["loc1_s"])
+    np.testing.assert_array_equal(np.where(il[2] >= 0, il[3], 0), rec["loc2_s"])
+    # normalised gates: g_j / clamp(g_1 + g_2, eps) in float32 (:306-312): one division, bit-exact
+    np.testing.assert_array_equal(gs[0], rec["gates1_s"])
+    np.testing.assert_array_equal(gs[1], rec["gates2_s"])
+    # rows used per expert = kept first + kept second choices
+    used = np.bincount(rec["idx1"][kept1], minlength=E) + np.bincount(rec["idx2"][kept2], minlength=E)
+    np.testing.assert_array_equal(cap, np.minimum(used, C))
+    np.testing.assert_array_equal(np.bincount(rec["idx1"], minlength=E), rec["exp_counts"])
+
+
+@pytest.mark.parametrize("path", TOP2, ids=ids)
+def test_oracle_top2_matches_reference_gate(path):
+    rec = np.load(path)
+    S, E, M, C = (int(rec[k]) for k in ("S", "E", "M", "C"))
+    assert O.capacity(S, E, float(rec["cf"]), 2) == C, "shape chosen so that both capacity roundings agree"
+    gs, il, cap, elems = O.moe_gate(rec["gate"], np.zeros(E, np.int32), C, M, 2)
+    check_top2(rec, gs, il, cap)
+    if "x" in rec.files:
+        disp = O.moe_encode_fwd(il, rec["x"], E, C)
+        np.testing.assert_array_equal(disp, rec["disp"])          # 0/1 mask times x summed with zeros: exact
+        out = O.moe_decode_fwd(rec["eo"], gs, il)
+        np.testing.assert_allclose(out, rec["out"], rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("path", CHAIN, ids=ids)
+def test_oracle_chained_used_capacity_matches_reference_operator(path):
+    rec = np.load(path)
+    S, E, M, n, C = (int(rec[k]) for k in ("S", "E", "M", "n", "C"))
+    Sp = S // n
+    assert O.capacity(Sp, E, 1.0) == C
+    used = rec["used_in"][0].copy()
+    for c in range(n):
+        np.testing.assert_array_equal(used, rec["used_in"][c])
+        gs, il, cap, elems = O.moe_gate(rec["gate"][c * Sp:(c + 1) * Sp], used, C, M)
+        np.testing.assert_array_equal(il, rec["idx_loc"][c])
+        np.testing.assert_array_equal(gs[0], rec["gates_s"][c])
+        used = cap
+
+
+# ---- the same vectors against the CUDA kernels -----------------------------------------------------------------
+DEV = "cuda:0"
+
+
+def cu(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("path", TOP2, ids=ids)
+def test_gpu_top2_matches_reference_gate(path):
+    import lancet_b200 as LB
+    rec = np.load(path)
+    S, E, M, C = (int(rec[k]) for k in ("S", "E", "M", "C"))
+    cap0 = torch.zeros(E, dtype=torch.int32, device=DEV)
+    gs, il, cap, elems = LB.moe_gate(cu(rec["gate"]), cap0, C, M, k=2)
+    check_top2(rec, gs.cpu().numpy().reshape(2, S), il.cpu().numpy(), cap.cpu().numpy())
+    if "x" in rec.files:
+        g1, il1, cap1, el1, disp = LB.moe_encode(cu(rec["x"]), cu(rec["gate"]), cap0, float(rec["cf"]), k=2)
+        assert tuple(disp.shape) == (E, C, M)
+        np.testing.assert_array_equal(disp.cpu().numpy(), rec["disp"])
+        out = LB.moe_decode(cu(rec["eo"]), g1, il1)
+        np.testing.assert_allclose(out.cpu().numpy(), rec["out"], rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("path", CHAIN, ids=ids)
+def test_gpu_chained_used_capacity_matches_reference_operator(path):
+    import lancet_b200 as LB
+    rec = np.load(path)
+    S, E, M, n, C = (int(rec[k]) for k in ("S", "E", "M", "n", "C"))
+    Sp = S // n
+    used = cu(rec["used_in"][0])
+    for c in range(n):
+        gs, il, cap, elems = LB.moe_gate(cu(rec["gate"][c * Sp:(c + 1) * Sp]), used, C, M)
+        np.testing.assert_array_equal(il.cpu().numpy(), rec["idx_loc"][c])
+        np.testing.assert_array_equal(gs.cpu().numpy().reshape(-1), rec["gates_s"][c])
+        used = cap
+    # the single-call chained gate (all chunks in one launch, capacity factor cf*n with cf = 1/n) gives the same table
+    if bool((rec["used_in"][0] == 0).all()):
+        plan = LB.ChunkedMoE(S, M, E, 1, 1.0 / n, n, torch.float32, device=DEV)
+        assert plan.C == C
+        plan.dispatch(torch.zeros((S, M), device=DEV), cu(rec["gate"]))
+        np.testing.assert_array_equal(plan.idx_loc.cpu().numpy(), rec["idx_loc"])
+        np.testing.assert_array_equal(plan.gates_s.cpu().numpy().reshape(n, -1), rec["gates_s"])
