@@ -402,6 +402,15 @@ int lancet_lans(void* ws, size_t ws_bytes, int n_tensors, const int64_t* numels,
                 void* const* m, void* const* v, int dtype, int step, float lr, float beta1, float beta2, float eps,
                 int bias_correction, float weight_decay, int grad_averaging, int mode, int normalize_grad, int flags,
                 lancet_stream_t stream);
+/* The same step with the step count left where the reference's op receives it: a float32 scalar in DEVICE
+ * memory (`step` tensor of raf.op.lans, read as (int)value).  The reference copies it to the host and waits
+ * (lans.cc:102-107: CopyTo(cpu) = a device-wide synchronisation per optimizer step); here a one-thread kernel
+ * derives the bias corrections (lans.cc:108-113) on the stream and the call stays asynchronous.
+ * Only use LANCET_LANS_TABLES_READY with a workspace nobody else writes between the calls. */
+int lancet_lans_dev_step(void* ws, size_t ws_bytes, int n_tensors, const int64_t* numels, void* const* g, void* const* p,
+                         void* const* m, void* const* v, int dtype, const float* step_dev, float lr, float beta1, float beta2,
+                         float eps, int bias_correction, float weight_decay, int grad_averaging, int mode,
+                         int normalize_grad, int flags, lancet_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -41,7 +41,7 @@ struct LansHyper {
 };
 
 struct LansLayout {
-  size_t tensors_off, part1_off, part2_off, norms_off, counters_off, total;
+  size_t tensors_off, part1_off, part2_off, norms_off, counters_off, bc_off, total;
   long long nchunks;
 };
 
@@ -58,6 +58,7 @@ static LansLayout lans_layout(int n, const int64_t* numels) {
   L.part2_off = off;   off += up256((size_t)(nch > 0 ? nch : 1) * sizeof(float2));
   L.norms_off = off;   off += up256((size_t)n * sizeof(float4));
   L.counters_off = off; off += up256((size_t)n * 2 * sizeof(int));
+  L.bc_off = off;       off += 256;  // 1/bias_correction1, 1/bias_correction2 when the step counter lives on the device
   L.total = off;
   return L;
 }
@@ -123,6 +124,19 @@ __device__ __forceinline__ void finish_tensor(float2 mine, float2* __restrict__ 
   }
 }
 
+// Hardware square root and reciprocal (one special-function instruction each, relative error about 2^-23)
+// instead of the IEEE-rounded sequences: the difference is two orders below the 1e-5 tolerance of the op.
+__device__ __forceinline__ float sqrt_fast(float x) {
+  float y;
+  asm("sqrt.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float rcp_fast(float x) {
+  float y;
+  asm("rcp.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // `inv_gn` is 1 / (||g|| + eps) when the gradient is normalised, else 1.  Multiplying by reciprocals
 // instead of dividing changes results by at most a few ulp, far inside the 1e-5 tolerance.
 __device__ __forceinline__ void lans_directions(float g, float p, float& m, float& v, float inv_gn, const LansHyper& h,
@@ -131,7 +145,7 @@ __device__ __forceinline__ void lans_directions(float g, float p, float& m, floa
   if (h.mode == 0) sg = sg + h.wd * p;
   m = m * h.beta1 + h.beta3 * sg;
   v = v * h.beta2 + (1.0f - h.beta2) * sg * sg;
-  const float r = __frcp_rn(sqrtf(v * h.inv_bc2) + h.eps);
+  const float r = rcp_fast(sqrt_fast(v * h.inv_bc2) + h.eps);
   const float sp = h.mode == 0 ? 0.0f : h.wd * p;
   um = (m * h.inv_bc1) * r + sp;
   ug = sg * r + sp;
@@ -142,7 +156,7 @@ __device__ __forceinline__ void lans_directions_post(float g, float p, float m, 
                                                      const LansHyper& h, float& um, float& ug) {
   float sg = g * inv_gn;
   if (h.mode == 0) sg = sg + h.wd * p;
-  const float r = __frcp_rn(sqrtf(v * h.inv_bc2) + h.eps);
+  const float r = rcp_fast(sqrt_fast(v * h.inv_bc2) + h.eps);
   const float sp = h.mode == 0 ? 0.0f : h.wd * p;
   um = (m * h.inv_bc1) * r + sp;
   ug = sg * r + sp;
@@ -202,27 +216,69 @@ lans_phase1_kernel(const LansTensor* __restrict__ tensors, int n, float2* __rest
   finish_tensor(mine, part1, counters + 2 * t, T, chunk, reinterpret_cast<float*>(norms + t));
 }
 
+// 1/bias_correction from a step counter that lives on the device (a float scalar, as the reference's op takes it:
+// src/op/dialect/cuda/lans.cc:102-113, which copies it to the host first).
+__global__ void lans_bias_correction_kernel(const float* __restrict__ step, float beta1, float beta2, int bias_correction,
+                                            float* __restrict__ inv_bc) {
+  float bc1 = 1.0f, bc2 = 1.0f;
+  if (bias_correction == 1) {
+    const int n = (int)step[0];
+    bc1 = (float)(1 - pow((double)beta1, n));
+    bc2 = (float)(1 - pow((double)beta2, n));
+  }
+  inv_bc[0] = 1.0f / bc1;
+  inv_bc[1] = 1.0f / bc2;
+}
+
+__device__ __forceinline__ void load_bc(LansHyper& h, const float* __restrict__ inv_bc_dev) {
+  if (inv_bc_dev) {
+    h.inv_bc1 = __ldg(inv_bc_dev);
+    h.inv_bc2 = __ldg(inv_bc_dev + 1);
+  }
+}
+
+__device__ __forceinline__ void phase2_vec(const float4& g, const float4& p, float4& m, float4& v, float inv_gn,
+                                           const LansHyper& h, float& sm, float& sq) {
+  float um, ug;
+  lans_directions(g.x, p.x, m.x, v.x, inv_gn, h, um, ug); sm += um * um; sq += ug * ug;
+  lans_directions(g.y, p.y, m.y, v.y, inv_gn, h, um, ug); sm += um * um; sq += ug * ug;
+  lans_directions(g.z, p.z, m.z, v.z, inv_gn, h, um, ug); sm += um * um; sq += ug * ug;
+  lans_directions(g.w, p.w, m.w, v.w, inv_gn, h, um, ug); sm += um * um; sq += ug * ug;
+}
+
+// Two vectors of each of the four arrays are loaded before any arithmetic or store: the stores of one iteration
+// cannot be moved below the next iteration's loads by the compiler (the arrays may alias as far as it knows), so
+// with one vector per array a thread had 64 bytes in flight and the kernel sat at 0.82 of the copy bandwidth.
 __global__ void __launch_bounds__(kLansThreads)
-lans_phase2_kernel(const LansTensor* __restrict__ tensors, int n, LansHyper h, float2* __restrict__ part2,
-                   float4* __restrict__ norms, int* __restrict__ counters) {
+lans_phase2_kernel(const LansTensor* __restrict__ tensors, int n, LansHyper h, const float* __restrict__ inv_bc_dev,
+                   float2* __restrict__ part2, float4* __restrict__ norms, int* __restrict__ counters) {
   const int chunk = blockIdx.x;
   const int t = find_tensor(tensors, n, chunk);
   const LansTensor T = tensors[t];
   const ChunkView c = chunk_view(T, chunk, true);
+  load_bc(h, inv_bc_dev);
   const float gnorm = grad_scale(__ldcg(reinterpret_cast<const float*>(norms + t)), h);
   const float4* g4 = reinterpret_cast<const float4*>(T.g + c.off);
   const float4* p4 = reinterpret_cast<const float4*>(T.p + c.off);
   float4* m4 = reinterpret_cast<float4*>(T.m + c.off);
   float4* v4 = reinterpret_cast<float4*>(T.v + c.off);
-  float sm = 0.f, sq = 0.f;
-  for (int i = threadIdx.x; i < c.nvec; i += kLansThreads) {
+  float sm = 0.f, sq = 0.f, sm2 = 0.f, sq2 = 0.f;
+  int i = threadIdx.x;
+  for (; i + kLansThreads < c.nvec; i += 2 * kLansThreads) {
+    const int j = i + kLansThreads;
+    const float4 ga = __ldcs(g4 + i), pa = __ldcs(p4 + i), gb = __ldcs(g4 + j), pb = __ldcs(p4 + j);
+    float4 ma = __ldcs(m4 + i), va = __ldcs(v4 + i), mb = __ldcs(m4 + j), vb = __ldcs(v4 + j);
+    phase2_vec(ga, pa, ma, va, gnorm, h, sm, sq);
+    phase2_vec(gb, pb, mb, vb, gnorm, h, sm2, sq2);
+    m4[i] = ma;
+    v4[i] = va;
+    m4[j] = mb;
+    v4[j] = vb;
+  }
+  for (; i < c.nvec; i += kLansThreads) {
     const float4 g = g4[i], p = p4[i];
     float4 m = m4[i], v = v4[i];
-    float um, ug;
-    lans_directions(g.x, p.x, m.x, v.x, gnorm, h, um, ug); sm += um * um; sq += ug * ug;
-    lans_directions(g.y, p.y, m.y, v.y, gnorm, h, um, ug); sm += um * um; sq += ug * ug;
-    lans_directions(g.z, p.z, m.z, v.z, gnorm, h, um, ug); sm += um * um; sq += ug * ug;
-    lans_directions(g.w, p.w, m.w, v.w, gnorm, h, um, ug); sm += um * um; sq += ug * ug;
+    phase2_vec(g, p, m, v, gnorm, h, sm, sq);
     m4[i] = m;
     v4[i] = v;
   }
@@ -234,16 +290,27 @@ lans_phase2_kernel(const LansTensor* __restrict__ tensors, int n, LansHyper h, f
     T.m[c.off + e] = m;
     T.v[c.off + e] = v;
   }
-  const float2 mine = block_sum2(sm, sq);
+  const float2 mine = block_sum2(sm + sm2, sq + sq2);
   finish_tensor(mine, part2, counters + 2 * t + 1, T, chunk, reinterpret_cast<float*>(norms + t) + 2);
 }
 
+__device__ __forceinline__ void phase3_vec(const float4& g, float4& p, const float4& m, const float4& v, float inv_gn,
+                                           const LansHyper& h, float rm, float rg) {
+  float um, ug;
+  lans_directions_post(g.x, p.x, m.x, v.x, inv_gn, h, um, ug); p.x = p.x - rm * um - rg * ug;
+  lans_directions_post(g.y, p.y, m.y, v.y, inv_gn, h, um, ug); p.y = p.y - rm * um - rg * ug;
+  lans_directions_post(g.z, p.z, m.z, v.z, inv_gn, h, um, ug); p.z = p.z - rm * um - rg * ug;
+  lans_directions_post(g.w, p.w, m.w, v.w, inv_gn, h, um, ug); p.w = p.w - rm * um - rg * ug;
+}
+
 __global__ void __launch_bounds__(kLansThreads)
-lans_phase3_kernel(const LansTensor* __restrict__ tensors, int n, LansHyper h, const float4* __restrict__ norms) {
+lans_phase3_kernel(const LansTensor* __restrict__ tensors, int n, LansHyper h, const float* __restrict__ inv_bc_dev,
+                   const float4* __restrict__ norms) {
   const int chunk = blockIdx.x;
   const int t = find_tensor(tensors, n, chunk);
   const LansTensor T = tensors[t];
   const ChunkView c = chunk_view(T, chunk, true);
+  load_bc(h, inv_bc_dev);
   const float4 nr = __ldcg(norms + t);  // ||g||, ||p||, ||u_m||, ||u_g||
   float rm = (nr.z != 0.0f && nr.y != 0.0f) ? h.lr * (nr.y / nr.z) : h.lr;
   float rg = (nr.w != 0.0f && nr.y != 0.0f) ? h.lr * (nr.y / nr.w) : h.lr;
@@ -254,14 +321,21 @@ lans_phase3_kernel(const LansTensor* __restrict__ tensors, int n, LansHyper h, c
   float4* p4 = reinterpret_cast<float4*>(T.p + c.off);
   const float4* m4 = reinterpret_cast<const float4*>(T.m + c.off);
   const float4* v4 = reinterpret_cast<const float4*>(T.v + c.off);
-  for (int i = threadIdx.x; i < c.nvec; i += kLansThreads) {
+  int i = threadIdx.x;
+  for (; i + kLansThreads < c.nvec; i += 2 * kLansThreads) {
+    const int j = i + kLansThreads;
+    const float4 ga = __ldcs(g4 + i), ma = __ldcs(m4 + i), va = __ldcs(v4 + i);
+    const float4 gb = __ldcs(g4 + j), mb = __ldcs(m4 + j), vb = __ldcs(v4 + j);
+    float4 pa = __ldcs(p4 + i), pb = __ldcs(p4 + j);
+    phase3_vec(ga, pa, ma, va, inv_gn, h, rm, rg);
+    phase3_vec(gb, pb, mb, vb, inv_gn, h, rm, rg);
+    p4[i] = pa;
+    p4[j] = pb;
+  }
+  for (; i < c.nvec; i += kLansThreads) {
     const float4 g = g4[i], m = m4[i], v = v4[i];
     float4 p = p4[i];
-    float um, ug;
-    lans_directions_post(g.x, p.x, m.x, v.x, inv_gn, h, um, ug); p.x = p.x - rm * um - rg * ug;
-    lans_directions_post(g.y, p.y, m.y, v.y, inv_gn, h, um, ug); p.y = p.y - rm * um - rg * ug;
-    lans_directions_post(g.z, p.z, m.z, v.z, inv_gn, h, um, ug); p.z = p.z - rm * um - rg * ug;
-    lans_directions_post(g.w, p.w, m.w, v.w, inv_gn, h, um, ug); p.w = p.w - rm * um - rg * ug;
+    phase3_vec(g, p, m, v, inv_gn, h, rm, rg);
     p4[i] = p;
   }
   for (int e = c.nvec * 4 + threadIdx.x; e < c.n; e += kLansThreads) {
@@ -284,10 +358,10 @@ size_t lancet_lans_workspace_bytes(int n_tensors, const int64_t* numels) {
   return lans_layout(n_tensors, numels).total;
 }
 
-int lancet_lans(void* ws, size_t ws_bytes, int n_tensors, const int64_t* numels, void* const* g, void* const* p,
-                void* const* m, void* const* v, int dtype, int step, float lr, float beta1, float beta2, float eps,
-                int bias_correction, float weight_decay, int grad_averaging, int mode, int normalize_grad, int flags,
-                lancet_stream_t stream_) {
+static int lans_impl(void* ws, size_t ws_bytes, int n_tensors, const int64_t* numels, void* const* g, void* const* p,
+                     void* const* m, void* const* v, int dtype, int step, const float* step_dev, float lr, float beta1,
+                     float beta2, float eps, int bias_correction, float weight_decay, int grad_averaging, int mode,
+                     int normalize_grad, int flags, lancet_stream_t stream_) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   LANCET_REQUIRE(n_tensors >= 0, LANCET_ERR_INVALID, "lancet_lans: negative tensor count %d", n_tensors);
   if (n_tensors == 0) return LANCET_OK;
@@ -296,7 +370,7 @@ int lancet_lans(void* ws, size_t ws_bytes, int n_tensors, const int64_t* numels,
   LANCET_REQUIRE(ws && numels, LANCET_ERR_NULL, "lancet_lans: null workspace or numels");
   LANCET_REQUIRE((flags & ~LANCET_LANS_TABLES_READY) == 0, LANCET_ERR_INVALID, "lancet_lans: unknown flag bits 0x%x", flags);
   LANCET_REQUIRE(mode == 0 || mode == 1, LANCET_ERR_INVALID, "lancet_lans: mode must be 0 or 1, got %d", mode);
-  LANCET_REQUIRE(step >= 1, LANCET_ERR_INVALID, "lancet_lans: step must be >= 1, got %d", step);
+  LANCET_REQUIRE(step_dev || step >= 1, LANCET_ERR_INVALID, "lancet_lans: step must be >= 1, got %d", step);
   for (int i = 0; i < n_tensors; ++i)
     LANCET_REQUIRE(numels[i] >= 0, LANCET_ERR_INVALID, "lancet_lans: tensor %d has negative size", i);
   const LansLayout L = lans_layout(n_tensors, numels);
@@ -335,7 +409,12 @@ int lancet_lans(void* ws, size_t ws_bytes, int n_tensors, const int64_t* numels,
   h.mode = mode; h.normalize_grad = normalize_grad ? 1 : 0;
   // host-side bias correction, as src/op/dialect/cuda/lans.cc:108-117 of the reference
   h.bc1 = 1.0f; h.bc2 = 1.0f;
-  if (bias_correction == 1) {
+  float* inv_bc_dev = nullptr;
+  if (step_dev) {
+    inv_bc_dev = reinterpret_cast<float*>(base + L.bc_off);
+    lans_bias_correction_kernel<<<1, 1, 0, stream>>>(step_dev, beta1, beta2, bias_correction, inv_bc_dev);
+    if (int st = launch_status("lans_bias_correction_kernel")) return st;
+  } else if (bias_correction == 1) {
     h.bc1 = (float)(1 - std::pow((double)beta1, step));
     h.bc2 = (float)(1 - std::pow((double)beta2, step));
   }
@@ -354,13 +433,30 @@ int lancet_lans(void* ws, size_t ws_bytes, int n_tensors, const int64_t* numels,
   if (int st = launch_status("lans_phase1_kernel")) return st;
   {
     ProfScope prof("lans_phase2_kernel", stream);
-    lans_phase2_kernel<<<grid, kLansThreads, 0, stream>>>(d_tensors, n_tensors, h, part2, norms, counters);
+    lans_phase2_kernel<<<grid, kLansThreads, 0, stream>>>(d_tensors, n_tensors, h, inv_bc_dev, part2, norms, counters);
   }
   if (int st = launch_status("lans_phase2_kernel")) return st;
   {
     ProfScope prof("lans_phase3_kernel", stream);
-    lans_phase3_kernel<<<grid, kLansThreads, 0, stream>>>(d_tensors, n_tensors, h, norms);
+    lans_phase3_kernel<<<grid, kLansThreads, 0, stream>>>(d_tensors, n_tensors, h, inv_bc_dev, norms);
   }
   return launch_status("lans_phase3_kernel");
+}
+
+int lancet_lans(void* ws, size_t ws_bytes, int n_tensors, const int64_t* numels, void* const* g, void* const* p,
+                void* const* m, void* const* v, int dtype, int step, float lr, float beta1, float beta2, float eps,
+                int bias_correction, float weight_decay, int grad_averaging, int mode, int normalize_grad, int flags,
+                lancet_stream_t stream) {
+  return lans_impl(ws, ws_bytes, n_tensors, numels, g, p, m, v, dtype, step, nullptr, lr, beta1, beta2, eps, bias_correction,
+                   weight_decay, grad_averaging, mode, normalize_grad, flags, stream);
+}
+
+int lancet_lans_dev_step(void* ws, size_t ws_bytes, int n_tensors, const int64_t* numels, void* const* g, void* const* p,
+                         void* const* m, void* const* v, int dtype, const float* step_dev, float lr, float beta1, float beta2,
+                         float eps, int bias_correction, float weight_decay, int grad_averaging, int mode,
+                         int normalize_grad, int flags, lancet_stream_t stream) {
+  LANCET_REQUIRE(step_dev, LANCET_ERR_NULL, "lancet_lans_dev_step: null step pointer");
+  return lans_impl(ws, ws_bytes, n_tensors, numels, g, p, m, v, dtype, 0, step_dev, lr, beta1, beta2, eps, bias_correction,
+                   weight_decay, grad_averaging, mode, normalize_grad, flags, stream);
 }
 }

@@ -538,33 +538,25 @@ class LansImpl : public OpEnv {
   void Execute(const std::vector<Value>& in, Value /*output aliases the inputs*/) override {
     if (n_ == 0) return;
     const auto& tl = in[0].fields;
-    // step: host scalar, CPU tensor, or (as in the reference, cuda/lans.cc:102-107) a device tensor read back
-    float fstep = 0;
-    const Value& s = in[1];
-    if (s.kind == Value::kTensor) {
-      if (s.tensor.device.device_type == 1) {
-        fstep = *static_cast<const float*>(s.tensor.data);
-      } else {
-        RAF_SHIM_CHECK(cudaMemcpy(&fstep, s.tensor.data, sizeof(float), cudaMemcpyDeviceToHost) == cudaSuccess, "reading step failed");
-      }
-    } else {
-      fstep = (float)s.f;
-    }
     std::vector<void*> g(n_), p(n_), m(n_), v(n_);
     for (int i = 0; i < n_; ++i) {
       g[i] = tl[i].tensor.data; p[i] = tl[n_ + i].tensor.data; m[i] = tl[2 * n_ + i].tensor.data; v[i] = tl[3 * n_ + i].tensor.data;
     }
-    // the executor may hand out a different workspace on every call (src/impl/vm/vm.cc:1260-1266): the
-    // tensor table is reused only while workspace and tensor addresses stay the same
-    std::vector<void*> key = g;
-    key.insert(key.end(), p.begin(), p.end());
-    key.insert(key.end(), m.begin(), m.end());
-    key.insert(key.end(), v.begin(), v.end());
-    key.push_back(ws_);
-    const int flags = (key == last_key_) ? LANCET_LANS_TABLES_READY : 0;
+    // The workspace belongs to the executor, which may hand the same address out again after another op has used
+    // it as scratch (src/impl/vm/vm.cc:1260-1266, interpreter.cc:283-323): nothing is kept in it between calls, the
+    // tensor table and the counters are written on every call (one small copy and two memsets on the stream).
+    const int flags = 0;
+    const Value& s = in[1];
+    if (s.kind == Value::kTensor && s.tensor.device.device_type != 1) {
+      // step as the reference passes it, a device scalar (cuda/lans.cc:102-107): it stays on the device, no read-back
+      Ok(lancet_lans_dev_step(ws_, ws_bytes_, n_, numels_.data(), g.data(), p.data(), m.data(), v.data(), LANCET_F32,
+                              static_cast<const float*>(s.tensor.data), lr_, beta1_, beta2_, eps_, bias_correction_, wd_,
+                              grad_averaging_, mode_, normalize_grad_ ? 1 : 0, flags, GetStream()));
+      return;
+    }
+    const float fstep = s.kind == Value::kTensor ? *static_cast<const float*>(s.tensor.data) : (float)s.f;
     Ok(lancet_lans(ws_, ws_bytes_, n_, numels_.data(), g.data(), p.data(), m.data(), v.data(), LANCET_F32, (int)fstep, lr_, beta1_,
                    beta2_, eps_, bias_correction_, wd_, grad_averaging_, mode_, normalize_grad_ ? 1 : 0, flags, GetStream()));
-    last_key_ = key;
   }
   static OpEnv* make(const CallValues& cv) { return new LansImpl(cv); }
 
@@ -573,7 +565,6 @@ class LansImpl : public OpEnv {
   bool normalize_grad_ = true;
   float lr_, beta1_, beta2_, eps_, wd_;
   std::vector<int64_t> numels_;
-  std::vector<void*> last_key_;
   void* ws_ = nullptr;
   size_t ws_bytes_ = 0;
 };

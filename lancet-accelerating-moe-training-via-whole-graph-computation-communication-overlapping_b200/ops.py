@@ -218,7 +218,8 @@ def lans(tensor_list, step, learning_rate=1e-3, beta1=0.9, beta2=0.999, eps=1e-6
          weight_decay=0.01, grad_averaging=1, mode=1, normalize_grad=True, state=None):
     """`raf.op.lans`: tensor_list = g_list + x_list + m_list + v_list (python/raf/optim/lans.py:265 of the
     reference); parameters, m and v are updated in place and the list is returned.  `step` is a host
-    integer or float (1-based)."""
+    integer or float (1-based), or - as the reference's op receives it - a float32 scalar tensor on the
+    device, which is then read by the kernels themselves: the call stays asynchronous."""
     n4 = len(tensor_list)
     if n4 % 4 != 0:
         raise ValueError("lans: tensor_list must hold 4 lists of equal length")
@@ -234,6 +235,15 @@ def lans(tensor_list, step, learning_rate=1e-3, beta1=0.9, beta2=0.999, eps=1e-6
             _lans_states.clear()
             _lans_states[key] = state
     flags = _capi.LANS_TABLES_READY if state.ready else 0
+    if isinstance(step, torch.Tensor) and step.is_cuda:
+        if step.dtype != torch.float32 or step.numel() != 1:
+            raise TypeError("lans: a device step must be a float32 scalar")
+        check(_capi.lib().lancet_lans_dev_step(_ptr(state.ws), state.ws.numel(), state.n, state.numels, state.g, state.p,
+                                               state.m, state.v, _capi.F32, _ptr(step), learning_rate, beta1, beta2, eps,
+                                               int(bias_correction), weight_decay, int(grad_averaging), int(mode),
+                                               int(bool(normalize_grad)), flags, _stream(p[0])))
+        state.ready = True
+        return tensor_list
     check(_capi.lib().lancet_lans(_ptr(state.ws), state.ws.numel(), state.n, state.numels, state.g, state.p, state.m,
                                   state.v, _capi.F32, int(step), learning_rate, beta1, beta2, eps, int(bias_correction),
                                   weight_decay, int(grad_averaging), int(mode), int(bool(normalize_grad)), flags,

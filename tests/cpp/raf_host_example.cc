@@ -57,6 +57,76 @@ static int Run(CallValues& cv, cudaStream_t stream, std::string* ran) {
   return 0;
 }
 
+// One cached raf.op.cuda.lans OpEnv executed twice with the executor's workspace scribbled over in between (an
+// executor may hand the same address to another op between two calls, src/impl/vm/vm.cc:1260-1266 of the reference):
+// the result must equal two calls of fresh OpEnvs on a copy of the state.  The step is a device scalar, as RAF passes it.
+static int LansCachedEnv(cudaStream_t stream) {
+  const std::vector<int64_t> sizes = {5000, 8192, 3, 70000};
+  const int n = (int)sizes.size();
+  unsigned rng = 777;
+  auto next = [&]() { rng = rng * 1664525u + 1013904223u; return (rng >> 8) * (1.0f / 16777216.0f) - 0.5f; };
+  std::vector<Tensor> A, B;   // g, p, m, v lists of both copies
+  for (int list = 0; list < 4; ++list)
+    for (int i = 0; i < n; ++i) {
+      std::vector<float> h((size_t)sizes[i]);
+      for (auto& v : h) v = list == 3 ? 1e-6f * (next() + 0.5f) : 0.02f * next();
+      for (std::vector<Tensor>* dst : {&A, &B}) {
+        Tensor t = DeviceTensor({sizes[i]}, {kFloat, 32});
+        CK(cudaMemcpy(t.data, h.data(), h.size() * 4, cudaMemcpyHostToDevice));
+        dst->push_back(t);
+      }
+    }
+  Tensor step = DeviceTensor({}, {kFloat, 32});
+  auto call_for = [&](const std::vector<Tensor>& tl) {
+    CallValues cv;
+    cv.op = "raf.op.lans";
+    std::vector<Value> fields;
+    for (const Tensor& t : tl) fields.push_back(Value::T(t));
+    cv.args = {Value::Tuple(fields), Value::T(step), Value::Float(1e-3), Value::Float(0.9), Value::Float(0.999), Value::Float(1e-6),
+               Value::Int(1), Value::Float(0.01), Value::Int(1), Value::Int(1), Value::Int(1)};
+    Declare(&cv);
+    return cv;
+  };
+  SetStream(stream);
+  CallValues cvA = call_for(A), cvB = call_for(B);
+  std::shared_ptr<OpEnv> cached = Dispatch(cvA);
+  if (cached->name() != "raf.op.cuda.lans") { std::printf("FAILED: lans dispatched to %s\n", cached->name().c_str()); return 1; }
+  if (cached->GetRequests().workspace.size() != 1) { std::printf("FAILED: lans should request one workspace\n"); return 1; }
+  const size_t ws_bytes = (size_t)cached->GetRequests().workspace[0].nbytes;
+  void* ws = nullptr;
+  CK(cudaMalloc(&ws, ws_bytes));
+  for (int it = 1; it <= 2; ++it) {
+    const float fstep = (float)it;
+    CK(cudaMemcpy(step.data, &fstep, 4, cudaMemcpyHostToDevice));
+    // cached OpEnv, same workspace address, contents destroyed since the previous call
+    CK(cudaMemset(ws, 0xFF, ws_bytes));
+    *cached->GetRequests().workspace[0].dest = ws;
+    cached->Execute(cvA);
+    CK(cudaStreamSynchronize(stream));
+    // fresh OpEnv with its own workspace on the second copy
+    std::shared_ptr<OpEnv> fresh = Dispatch(cvB);
+    void* ws2 = nullptr;
+    CK(cudaMalloc(&ws2, ws_bytes));
+    *fresh->GetRequests().workspace[0].dest = ws2;
+    fresh->Execute(cvB);
+    CK(cudaStreamSynchronize(stream));
+    CK(cudaFree(ws2));
+  }
+  for (size_t t = 0; t < A.size(); ++t) {
+    std::vector<float> a((size_t)A[t].numel()), b(a.size());
+    CK(cudaMemcpy(a.data(), A[t].data, a.size() * 4, cudaMemcpyDeviceToHost));
+    CK(cudaMemcpy(b.data(), B[t].data, b.size() * 4, cudaMemcpyDeviceToHost));
+    for (size_t i = 0; i < a.size(); ++i)
+      if (!(a[i] == b[i])) { std::printf("FAILED: lans cached env differs at tensor %zu element %zu: %g vs %g\n", t, i, a[i], b[i]); return 1; }
+  }
+  // the parameters moved, and stayed finite
+  std::vector<float> p0((size_t)sizes[0]);
+  CK(cudaMemcpy(p0.data(), A[n].data, p0.size() * 4, cudaMemcpyDeviceToHost));
+  for (float v : p0) if (!std::isfinite(v)) { std::printf("FAILED: lans produced a non-finite parameter\n"); return 1; }
+  CK(cudaFree(ws));
+  return 0;
+}
+
 int main() {
   const int S = 2048, E = 8, M = 64;
   const int C = (S + E - 1) / E;
@@ -112,6 +182,7 @@ int main() {
       const float w = il[s] >= 0 ? gs[s] * x[(size_t)s * M + m] : 0.f;
       if (out[(size_t)s * M + m] != w) { std::printf("FAILED: combined[%d,%d]\n", s, m); return 1; }
     }
+  if (LansCachedEnv(stream)) return 1;
   std::printf("raf host example ok (%s, %s)\n", "raf.op.cuda.moe_encode", ran.c_str());
   return 0;
 }

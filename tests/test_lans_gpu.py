@@ -85,3 +85,21 @@ def test_many_tensors_deterministic():
     assert torch.equal(outs[0], outs[1])        # fixed-order reductions: run-to-run identical
     wp, _, _ = lans_oracle.lans_step(g, p, m, v, step=3)
     close(outs[0].numpy(), np.concatenate([a.ravel() for a in wp]), "p")
+
+
+def test_step_counter_on_the_device_gives_the_same_bits():
+    """`lancet_lans_dev_step`: the step stays a float32 scalar on the device, as raf.op.lans receives it
+    (src/op/dialect/cuda/lans.cc:102-107 of the reference reads it back; here no host round trip)."""
+    shapes = [(4096,), (8193,), (5, 7)]
+    g, p, m, v = make(shapes, 9)
+    a = [torch.from_numpy(x.copy()).to(DEV) for x in g + p + m + v]
+    b = [torch.from_numpy(x.copy()).to(DEV) for x in g + p + m + v]
+    step = torch.zeros((), dtype=torch.float32, device=DEV)
+    for it in (1, 2, 37):
+        step.fill_(float(it))
+        LB.lans(a, step)
+        LB.lans(b, it)
+        for x, y in zip(a, b):
+            assert torch.equal(x, y)
+    with pytest.raises(TypeError):
+        LB.lans(a, torch.zeros((), dtype=torch.int32, device=DEV))
