@@ -387,6 +387,18 @@ size_t lancet_grouped_bias_grad_workspace_bytes(int LE, int N);
 int lancet_grouped_bias_grad(const void* dY, void* db, int groups, int LE, int C, int N, const int32_t* counts,
                              int dtype, void* ws, size_t ws_bytes, lancet_stream_t stream);
 
+/* ---- scheduling knobs and a plain copy ----------------------------------------------------------
+ * No counterpart in the reference, whose kernels take whatever grid the library picks.  The static
+ * schedule that stands in for the reference's overlap pass (src/pass/dist_optimization/lancet_optimization.cc)
+ * runs an exchange stage beside an expert GEMM; both would otherwise ask for every SM and time-slice.
+ * exchange_ctas caps the grid of the peer-memory exchange kernels, gemm_ctas the persistent grid of the
+ * grouped GEMM (0 = no cap).  Process-wide; change it between steps, not while launches are being issued
+ * from another thread. */
+int lancet_set_cta_limits(int exchange_ctas, int gemm_ctas);
+/* cudaMemcpyAsync(dst, src, bytes) with the kind inferred from the pointers; dst or src may be a peer
+ * mapping from lancet_symm_open (copy-engine transfer over NVLink; the bandwidth yardstick of bench.py). */
+int lancet_peer_copy(void* dst, const void* src, size_t bytes, lancet_stream_t stream);
+
 /* ---- LANS optimizer ---------------------------------------------------------------------------
  * Replaces multi_tensor_lans_cuda (kernel_util.cuh:26-34; multi_tensor_lans.cu:401-450) and the
  * host side of LansImpl::Execute (src/op/dialect/cuda/lans.cc:92-148).  g/p/m/v are HOST arrays of

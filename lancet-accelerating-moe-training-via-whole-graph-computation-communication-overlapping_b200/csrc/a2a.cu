@@ -318,7 +318,8 @@ int lancet_all_to_all_p2p(const void* send, void* const* peer_recv, size_t bytes
     LANCET_REQUIRE(t.ptr[i] && aligned(t.ptr[i], 16), LANCET_ERR_NULL, "lancet_all_to_all_p2p: peer buffer %d is null or unaligned", i);
   const size_t vecs = bytes_per_rank / 16;
   long long bx = (long long)(((vecs + 255) / 256 * W + 7) / 8);
-  const long long cap = (long long)sm_count() * 8;
+  long long cap = (long long)sm_count() * 8;
+  if (exchange_cta_limit() > 0 && exchange_cta_limit() < cap) cap = exchange_cta_limit();
   if (bx > cap) bx = cap;
   if (bx < 1) bx = 1;
   cudaStream_t st = static_cast<cudaStream_t>(stream);

@@ -67,9 +67,27 @@ int sm_count() {
   return cached[dev];
 }
 
+static int g_exchange_ctas = 0, g_gemm_ctas = 0;
+int exchange_cta_limit() { return __atomic_load_n(&g_exchange_ctas, __ATOMIC_RELAXED); }
+int gemm_cta_limit() { return __atomic_load_n(&g_gemm_ctas, __ATOMIC_RELAXED); }
+
 }  // namespace lancet
 
 extern "C" {
+int lancet_set_cta_limits(int exchange_ctas, int gemm_ctas) {
+  if (exchange_ctas < 0 || gemm_ctas < 0) return lancet::fail(LANCET_ERR_INVALID, "lancet_set_cta_limits: negative limit");
+  __atomic_store_n(&lancet::g_exchange_ctas, exchange_ctas, __ATOMIC_RELAXED);
+  __atomic_store_n(&lancet::g_gemm_ctas, gemm_ctas, __ATOMIC_RELAXED);
+  return LANCET_OK;
+}
+
+int lancet_peer_copy(void* dst, const void* src, size_t bytes, lancet_stream_t stream) {
+  if (bytes == 0) return LANCET_OK;
+  if (!dst || !src) return lancet::fail(LANCET_ERR_NULL, "lancet_peer_copy: null pointer");
+  LANCET_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDefault, static_cast<cudaStream_t>(stream)));
+  return LANCET_OK;
+}
+
 const char* lancet_last_error(void) { return lancet::error_buffer(); }
 const char* lancet_version(void) { return "lancet_b200 0.1 (sm_100a)"; }
 int lancet_abi_version(void) { return 1; }

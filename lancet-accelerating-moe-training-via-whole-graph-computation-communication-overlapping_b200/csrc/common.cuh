@@ -62,6 +62,10 @@ inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_
 
 // Number of SMs of the current device (cached per device).
 int sm_count();
+// Process-wide caps on the grids of the exchange kernels and of the persistent expert GEMM (lancet_set_cta_limits);
+// 0 = no cap.  A schedule that runs an exchange stage next to a GEMM gives each a share of the SMs with them.
+int exchange_cta_limit();
+int gemm_cta_limit();
 
 template <typename T>
 struct Num;

@@ -698,6 +698,7 @@ static int launch_a(const CUtensorMap& tmA, const CUtensorMap& tmB, const Params
     attr_set = true;
   }
   int grid = sm_count();
+  if (gemm_cta_limit() > 0 && gemm_cta_limit() < grid) grid = gemm_cta_limit();
   if (grid > p.total_tiles) grid = p.total_tiles;
   {
     ProfScope prof(name, st);

@@ -310,7 +310,8 @@ __global__ void stage_windows_kernel(const int32_t* __restrict__ chain, int W, i
 
 static int p2p_grid(long long tasks) {
   long long ctas = (tasks + kP2PWarps - 1) / kP2PWarps;
-  const long long cap = (long long)sm_count() * 16;
+  long long cap = (long long)sm_count() * 16;
+  if (exchange_cta_limit() > 0 && exchange_cta_limit() < cap) cap = exchange_cta_limit();
   if (ctas > cap) ctas = cap;
   if (ctas < 1) ctas = 1;
   return (int)ctas;

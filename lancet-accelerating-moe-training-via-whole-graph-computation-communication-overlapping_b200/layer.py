@@ -7,13 +7,14 @@ Mirrors MOELayerImpl + Experts of the reference (models/benchmark/pytorch/utils.
 gate probabilities as an input; the two nn.Linear layers of an expert keep their [out, in] layout."""
 import torch
 
-from . import ops
+from . import _capi, ops
 from .dist import DistChunkedMoE
 
 
 class MoELayer:
     def __init__(self, S, M, H, k=2, capacity_factor=1.25, n_chunks=4, dtype=torch.bfloat16, device="cuda",
-                 local_experts=2, fabric=None, group=None, act="gelu", seed=0, overlap_dw=True, stages=None):
+                 local_experts=2, fabric=None, group=None, act="gelu", seed=0, overlap_dw=True, stages=None,
+                 exchange_ctas=0, gemm_ctas=0):
         self.moe = DistChunkedMoE(S, M, k, capacity_factor, n_chunks, dtype, device, local_experts, fabric=fabric,
                                   group=group, train=True)
         self.S, self.M, self.H, self.LE, self.act = S, M, H, local_experts, act
@@ -41,6 +42,11 @@ class MoELayer:
         if P < 1 or n_chunks % P:
             raise ValueError("stages must divide n_chunks")
         self.stage_chunks = [(s * n_chunks // P, (s + 1) * n_chunks // P) for s in range(P)]
+        # staged schedule only: grid caps of the exchange kernels and of the expert GEMMs while both are in flight
+        # (0 = each asks for the whole GPU); see lancet_set_cta_limits
+        self.exchange_ctas, self.gemm_ctas = int(exchange_ctas), int(gemm_ctas)
+        # which schedule produced the activations a backward pass is about to read
+        self._fwd_schedule = None
 
     # ---- forward, in the three phases between which the ranks meet ----
     def fwd_dispatch(self, x, gate):
@@ -60,7 +66,12 @@ class MoELayer:
     def forward(self, x, gate):
         self.fwd_dispatch(x, gate)
         self.fwd_experts()
+        self._fwd_schedule = "plain"
         return self.fwd_combine()
+
+    def _limits(self, on):
+        if self.exchange_ctas or self.gemm_ctas:
+            _capi.check(_capi.lib().lancet_set_cta_limits(self.exchange_ctas if on else 0, self.gemm_ctas if on else 0))
 
     # ---- pipelined forward: the rows of chunk c+1 cross NVLink while the experts work on chunk c --------
     # Stage c of the expert GEMMs covers the whole 128-row tiles of every (source, expert) block that have arrived
@@ -112,6 +123,7 @@ class MoELayer:
         partial wave of tiles leaves idle."""
         n = len(self.stage_chunks)
         main, aux, comm = self._streams()
+        self._limits(True)
         self.fwd_gate(x, gate)
         comm.wait_stream(main)
         arrived = []
@@ -140,6 +152,8 @@ class MoELayer:
                         self.fwd_stage_combine(c)
         main.wait_stream(aux)
         main.wait_stream(comm)
+        self._limits(False)
+        self._fwd_schedule = "staged"
         return self.moe.out
 
     # ---- pipelined backward ----
@@ -172,8 +186,12 @@ class MoELayer:
         return self.moe.stage_dispatch_backward(*self.stage_chunks[c])
 
     def backward_pipelined(self, dout):
+        if self._fwd_schedule != "staged":
+            raise RuntimeError("backward_pipelined needs the row windows of forward_pipelined of the same step "
+                               "(the last forward ran the %s schedule)" % self._fwd_schedule)
         n = len(self.stage_chunks)
         main, aux, comm = self._streams()
+        self._limits(True)
         comm.wait_stream(main)
         arrived = []
         with torch.cuda.stream(comm):
@@ -203,6 +221,8 @@ class MoELayer:
         self.bwd_weights()
         main.wait_stream(aux)
         main.wait_stream(comm)
+        self._limits(False)
+        self._fwd_schedule = None
         return self.moe.dx, self.moe.dgates
 
     # ---- backward ----
@@ -233,6 +253,9 @@ class MoELayer:
         return dx, self.moe.dgates
 
     def backward(self, dout):
+        if self._fwd_schedule is None:
+            raise RuntimeError("backward without a forward of the same step: the saved activations were consumed")
+        self._fwd_schedule = None
         self.bwd_combine(dout)
         self.bwd_experts()
         return self.bwd_dispatch()

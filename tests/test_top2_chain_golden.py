@@ -111,5 +111,11 @@ def test_gpu_chained_used_capacity_matches_reference_operator(path):
         plan = LB.ChunkedMoE(S, M, E, 1, 1.0 / n, n, torch.float32, device=DEV)
         assert plan.C == C
         plan.dispatch(torch.zeros((S, M), device=DEV), cu(rec["gate"]))
-        np.testing.assert_array_equal(plan.idx_loc.cpu().numpy(), rec["idx_loc"])
+        il = plan.idx_loc.cpu().numpy()
+        np.testing.assert_array_equal(il[:, 0], rec["idx_loc"][:, 0])
+        # the plan's locations are rows of the one shared buffer: the used capacity of the expert before the chunk
+        # plus the reference's per-call location
+        first = np.argmax(rec["gate"], axis=1).reshape(n, Sp)
+        base = np.take_along_axis(rec["used_in"], first, axis=1)
+        np.testing.assert_array_equal(il[:, 1] - base, rec["idx_loc"][:, 1])
         np.testing.assert_array_equal(plan.gates_s.cpu().numpy().reshape(n, -1), rec["gates_s"])
