@@ -270,6 +270,22 @@ int lancet_moe_gate_chunked_p2p(const void* gate, int gate_dtype, float capacity
 int lancet_moe_dispatch_rows_p2p(const void* x, const int32_t* idx_loc, int S, int M, int C, int LE, int W, int rank,
                                  int k, int n_chunks, int chunk_begin, int chunk_end, int dtype,
                                  void* const* peer_recv, lancet_stream_t stream);
+/* Incremental form of steps 1 and 3, for pipelines that also split the operators IN FRONT of the layer into token
+ * chunks (the reference's forward partition of non-MoE operators, partition_exprs.cc:1709-1795 with the range search
+ * of lancet_optimization.cc:1203-1345): the gate probabilities of chunk c+1 do not exist yet when chunk c travels.
+ * lancet_moe_gate_chunks_p2p gates chunks [chunk_begin, chunk_end) from gate_rows = their rows only
+ * ([(chunk_end-chunk_begin)*Sp][E]), starting from row chunk_begin of capused_chain (the chunks must be gated in
+ * order), writes the usual slices of gates_s / idx_loc / capused_chain / elems and publishes the new chain rows to
+ * the owners.  lancet_moe_stage_window gives the row window of ONE stage covering those chunks (row_begin / row_end
+ * int32 [W*LE]) as soon as its barrier has been passed; counts is written when chunk_end == n_chunks.
+ * Results are identical to the all-at-once calls. */
+int lancet_moe_gate_chunks_p2p(const void* gate_rows, int gate_dtype, float capacity_factor, int S, int M, int LE, int W,
+                               int rank, int k, int n_chunks, int chunk_begin, int chunk_end, void* gates_s,
+                               int32_t* idx_loc, int32_t* capused_chain, uint64_t* elems, void* const* peer_chain,
+                               void* ws, size_t ws_bytes, lancet_stream_t stream);
+int lancet_moe_stage_window(const int32_t* chain, int W, int LE, int n_chunks, int row_align, int chunk_begin,
+                            int chunk_end, int32_t* row_begin, int32_t* row_end, int32_t* counts,
+                            lancet_stream_t stream);
 int lancet_moe_stage_windows(const int32_t* chain, int W, int LE, int n_chunks, int row_align, int32_t* row_begin,
                              int32_t* row_end, int32_t* counts, lancet_stream_t stream);
 /* As lancet_moe_combine_chunked, gathering rows from the owners' expert output buffers.  With
@@ -386,6 +402,18 @@ int lancet_moe_combine_bwd_p2p(const void* dout, const void* gates_s, const int3
 size_t lancet_grouped_bias_grad_workspace_bytes(int LE, int N);
 int lancet_grouped_bias_grad(const void* dY, void* db, int groups, int LE, int C, int N, const int32_t* counts,
                              int dtype, void* ws, size_t ws_bytes, lancet_stream_t stream);
+
+/* ---- gate projection -----------------------------------------------------------------------------
+ * probs [S,E] float32 = softmax(h [S,M] * wg [E,M]^T): the Linear(bias = False) + softmax in front of moe_encode
+ * (Gate module, models/benchmark/pytorch/utils.py:565-573; TopKGate.forward, docker/resources/sharded_moe.py:370-390),
+ * which the reference leaves to library GEMM and softmax operators.  One warp per token in a fixed order, fp32
+ * accumulation: a token's probabilities do not depend on how the tokens are split into calls, which is what lets a
+ * chunked pipeline reproduce the unchunked routing bit for bit.  E <= 64.  The backward form returns
+ * dlogits [S,E] float32 (for the weight gradient dlogits^T * h, left to the caller) and dh [S,M] in `dtype`. */
+int lancet_gate_softmax(const void* h, int dtype, const float* wg, float* probs, int S, int M, int E,
+                        lancet_stream_t stream);
+int lancet_gate_softmax_bwd(const float* probs, const float* dprobs, const float* wg, float* dlogits, void* dh,
+                            int dtype, int S, int M, int E, lancet_stream_t stream);
 
 /* ---- scheduling knobs and a plain copy ----------------------------------------------------------
  * No counterpart in the reference, whose kernels take whatever grid the library picks.  The static

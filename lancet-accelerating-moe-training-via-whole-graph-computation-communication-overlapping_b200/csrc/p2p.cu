@@ -282,8 +282,9 @@ __global__ void p2p_barrier_kernel(PeerTable flags, int W, int my_rank, unsigned
 // Staged exchange: every rank tells the owners, before the first row travels, how the rows of its block
 // will arrive: tables.ptr[owner] is int32 [W][n1][LE], entry (source, c, le) = rows of (source, expert) placed
 // by the chunks before c (n1 = n_chunks + 1 entries; the last is the total).
-__global__ void publish_chain_kernel(const int32_t* __restrict__ chain, PeerTable tables, int n1, int E, int LE, int my_rank) {
-  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n1 * E; i += gridDim.x * blockDim.x) {
+__global__ void publish_chain_kernel(const int32_t* __restrict__ chain, PeerTable tables, int n1, int E, int LE, int my_rank,
+                                     int row_begin, int row_end) {
+  for (int i = row_begin * E + blockIdx.x * blockDim.x + threadIdx.x; i < row_end * E; i += gridDim.x * blockDim.x) {
     const int c = i / E, e = i - c * E;
     const int owner = e / LE, le = e - owner * LE;
     static_cast<int32_t*>(tables.ptr[owner])[((size_t)my_rank * n1 + c) * LE + le] = chain[i];
@@ -305,6 +306,21 @@ __global__ void stage_windows_kernel(const int32_t* __restrict__ chain, int W, i
     row_begin[i] = c == 0 ? 0 : lo / align * align;
     row_end[i] = c == n - 1 ? hi : hi / align * align;
     if (c == 0 && counts) counts[g] = col[(size_t)n * LE];
+  }
+}
+
+// The same for one stage that covers chunks [c0, c1), computable as soon as the chain entries up to c1 are known
+// (incremental gating: chunk c is gated, published and sent before chunk c+1 is gated).
+__global__ void stage_window_kernel(const int32_t* __restrict__ chain, int W, int LE, int n, int align, int c0, int c1,
+                                    int32_t* __restrict__ row_begin, int32_t* __restrict__ row_end, int32_t* __restrict__ counts) {
+  const int G = W * LE, n1 = n + 1;
+  for (int g = blockIdx.x * blockDim.x + threadIdx.x; g < G; g += gridDim.x * blockDim.x) {
+    const int src = g / LE, le = g - src * LE;
+    const int32_t* col = chain + (size_t)src * n1 * LE + le;
+    const int lo = col[(size_t)c0 * LE], hi = col[(size_t)c1 * LE];
+    row_begin[g] = c0 == 0 ? 0 : lo / align * align;
+    row_end[g] = c1 == n ? hi : hi / align * align;
+    if (c1 == n && counts) counts[g] = hi;
   }
 }
 
@@ -510,8 +526,62 @@ int lancet_moe_gate_chunked_p2p(const void* gate, int gate_dtype, float capacity
                        elems, ws, 1, st, capused_chain);
   if (rc != LANCET_OK) return rc;
   const int n1 = n_chunks + 1;
-  publish_chain_kernel<<<1, 256, 0, st>>>(capused_chain, t, n1, E, LE, rank);
+  publish_chain_kernel<<<1, 256, 0, st>>>(capused_chain, t, n1, E, LE, rank, 0, n1);
   return launch_status("publish_chain_kernel");
+}
+
+int lancet_moe_gate_chunks_p2p(const void* gate_rows, int gate_dtype, float capacity_factor, int S, int M, int LE, int W, int rank,
+                               int k, int n_chunks, int chunk_begin, int chunk_end, void* gates_s, int32_t* idx_loc,
+                               int32_t* capused_chain, uint64_t* elems, void* const* peer_chain, void* ws, size_t ws_bytes,
+                               lancet_stream_t stream) {
+  LANCET_REQUIRE(W >= 1 && W <= kMaxPeers && rank >= 0 && rank < W && LE >= 1, LANCET_ERR_INVALID,
+                 "lancet_moe_gate_chunks_p2p: bad world %d / rank %d / local experts %d", W, rank, LE);
+  LANCET_REQUIRE(n_chunks >= 1 && S >= 0 && S % n_chunks == 0, LANCET_ERR_INVALID,
+                 "lancet_moe_gate_chunks_p2p: S=%d is not divisible into %d chunks", S, n_chunks);
+  LANCET_REQUIRE(chunk_begin >= 0 && chunk_begin < chunk_end && chunk_end <= n_chunks, LANCET_ERR_INVALID,
+                 "lancet_moe_gate_chunks_p2p: bad chunk range [%d, %d) of %d", chunk_begin, chunk_end, n_chunks);
+  LANCET_REQUIRE((k == 1 || k == 2) && M >= 0 && valid_dtype(gate_dtype), LANCET_ERR_INVALID,
+                 "lancet_moe_gate_chunks_p2p: bad k=%d, M=%d or dtype", k, M);
+  LANCET_REQUIRE(peer_chain && capused_chain && elems && ws && (S == 0 || (gate_rows && gates_s && idx_loc)), LANCET_ERR_NULL,
+                 "lancet_moe_gate_chunks_p2p: null pointer argument");
+  const int E = LE * W;
+  const int Sp = S / n_chunks;
+  const int nsub = chunk_end - chunk_begin;
+  const int C = lancet_moe_capacity(Sp, E, capacity_factor * n_chunks, k);
+  LANCET_REQUIRE(C >= 0 && (long long)E * C < (1ll << 31), LANCET_ERR_INVALID,
+                 "lancet_moe_gate_chunks_p2p: capacity %d out of range", C);
+  LANCET_REQUIRE(E >= k && k * E <= 1024 && (long long)n_chunks * k * E <= 8192, LANCET_ERR_INVALID,
+                 "lancet_moe_gate_chunks_p2p: k*E=%d or n_chunks*k*E too large", k * E);
+  LANCET_REQUIRE(ws_bytes >= gate_workspace_bytes(nsub * Sp, E, k, nsub) && aligned(ws, 16), LANCET_ERR_INVALID,
+                 "lancet_moe_gate_chunks_p2p: workspace too small or unaligned");
+  PeerTable t;
+  for (int i = 0; i < kMaxPeers; ++i) t.ptr[i] = i < W ? peer_chain[i] : nullptr;
+  for (int i = 0; i < W; ++i)
+    LANCET_REQUIRE(t.ptr[i] && aligned(t.ptr[i], 4), LANCET_ERR_NULL, "lancet_moe_gate_chunks_p2p: chain table %d is null or unaligned", i);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // the chunks see the capacity used by the chunks before them: row chunk_begin of the chain (row 0 = zeros, written here)
+  const int32_t* in_cap = chunk_begin == 0 ? nullptr : capused_chain + (size_t)chunk_begin * E;
+  float* gs = static_cast<float*>(gates_s) + (size_t)chunk_begin * k * Sp;
+  int rc = gate_launch(gate_rows, gate_dtype, nsub * Sp, E, k, nsub, in_cap, C, M, gs, LANCET_F32,
+                       idx_loc + (size_t)chunk_begin * 2 * k * Sp, capused_chain + (size_t)(chunk_begin + 1) * E,
+                       elems + (size_t)chunk_begin * E, ws, 1, st, chunk_begin == 0 ? capused_chain : nullptr);
+  if (rc != LANCET_OK) return rc;
+  publish_chain_kernel<<<1, 256, 0, st>>>(capused_chain, t, n_chunks + 1, E, LE, rank, chunk_begin == 0 ? 0 : chunk_begin + 1,
+                                          chunk_end + 1);
+  return launch_status("publish_chain_kernel");
+}
+
+int lancet_moe_stage_window(const int32_t* chain, int W, int LE, int n_chunks, int row_align, int chunk_begin, int chunk_end,
+                            int32_t* row_begin, int32_t* row_end, int32_t* counts, lancet_stream_t stream) {
+  LANCET_REQUIRE(W >= 1 && W <= kMaxPeers && LE >= 1 && n_chunks >= 1 && row_align >= 1, LANCET_ERR_INVALID,
+                 "lancet_moe_stage_window: bad world %d / local experts %d / chunks %d / alignment %d", W, LE, n_chunks, row_align);
+  LANCET_REQUIRE(chunk_begin >= 0 && chunk_begin < chunk_end && chunk_end <= n_chunks, LANCET_ERR_INVALID,
+                 "lancet_moe_stage_window: bad chunk range [%d, %d) of %d", chunk_begin, chunk_end, n_chunks);
+  LANCET_REQUIRE(chain && row_begin && row_end, LANCET_ERR_NULL, "lancet_moe_stage_window: null pointer argument");
+  const int G = W * LE;
+  stage_window_kernel<<<(G + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(chain, W, LE, n_chunks, row_align, chunk_begin,
+                                                                                      chunk_end, row_begin, row_end, counts);
+  return launch_status("stage_window_kernel");
 }
 
 int lancet_moe_dispatch_rows_p2p(const void* x, const int32_t* idx_loc, int S, int M, int C, int LE, int W, int rank, int k,

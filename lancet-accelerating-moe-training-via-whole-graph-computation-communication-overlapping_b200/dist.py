@@ -170,6 +170,8 @@ class DistChunkedMoE:
                                       torch.int32, d) for i in range(2)]
         self.win_begin = torch.zeros((n_chunks, G), dtype=torch.int32, device=d)
         self.win_end = torch.zeros((n_chunks, G), dtype=torch.int32, device=d)
+        self.swin_begin = torch.zeros((n_chunks, G), dtype=torch.int32, device=d)   # per stage, incremental protocol
+        self.swin_end = torch.zeros((n_chunks, G), dtype=torch.int32, device=d)
         if self.fabric.real and self.W > 1:
             torch.cuda.synchronize(d)
             self.fabric.dist.barrier(group=self.fabric.group)
@@ -228,6 +230,33 @@ class DistChunkedMoE:
             _ptr(gate), _DT[gate.dtype], self.cf, self.S, self.M, self.LE, self.W, self.rank, self.k, self.n,
             _ptr(self.gates_s), _ptr(self.idx_loc), _ptr(self.capused), _ptr(self.elems), self.peer_chain[self.parity],
             _ptr(self.ws), self.ws.numel(), _stream(gate)))
+
+    def stage_gate_chunks(self, gate_rows, c0, c1):
+        """Incremental form of stage_gate: gate chunks [c0, c1) from the probabilities of their tokens only (the
+        chunks must come in order, after `begin_step`) and tell the owners where their rows will lie."""
+        check(_capi.lib().lancet_moe_gate_chunks_p2p(
+            _ptr(gate_rows), _DT[gate_rows.dtype], self.cf, self.S, self.M, self.LE, self.W, self.rank, self.k, self.n, c0, c1,
+            _ptr(self.gates_s), _ptr(self.idx_loc), _ptr(self.capused), _ptr(self.elems), self.peer_chain[self.parity],
+            _ptr(self.ws), self.ws.numel(), _stream(gate_rows)))
+
+    def begin_step(self):
+        """Switch to the other set of receive buffers (stage_gate does this itself)."""
+        self.parity ^= 1
+
+    def stage_window(self, slot, c0, c1):
+        """Row window of the stage covering chunks [c0, c1), valid once that stage's barrier has been passed.
+        Returns (row_begin, row_end) int32 [W*LE]; the last stage also fills the row totals."""
+        cnt = self.counts[self.parity]
+        check(_capi.lib().lancet_moe_stage_window(_ptr(self.chain[self.parity]), self.W, self.LE, self.n, 128, c0, c1,
+                                                  _ptr(self.swin_begin[slot]), _ptr(self.swin_end[slot]), _ptr(cnt),
+                                                  _stream(cnt)))
+        return self.swin_begin[slot], self.swin_end[slot]
+
+    def zero_tail(self, buf=None):
+        """Zero the rows of `buf` (default: the receive buffer) past each block's row total."""
+        buf = self.recv[self.parity] if buf is None else buf
+        cnt = self.counts[self.parity]
+        check(_capi.lib().lancet_moe_zero_tail(_ptr(buf), _ptr(cnt), self.M, self.C, self.W * self.LE, _DT[self.dtype], _stream(cnt)))
 
     def stage_dispatch(self, x, c0, c1=None):
         """Scatter the rows of chunks [c0, c1) into the owners' receive buffers (follow with barrier())."""

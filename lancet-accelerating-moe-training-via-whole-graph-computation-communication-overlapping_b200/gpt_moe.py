@@ -6,16 +6,17 @@ blocks run on the library's fused layer, the optimizer step on its LANS op."""
 import torch
 import torch.nn.functional as F
 
-from .autograd import MoE
-from .ops import LansState, lans
+from . import _capi
+from .autograd import DeferredGrads, DeferredLinear, MoE
+from .ops import LansState, gemm_status, lans
 
 
 class Attention(torch.nn.Module):
-    def __init__(self, m, nh):
+    def __init__(self, m, nh, linear=torch.nn.Linear):
         super().__init__()
         self.nh = nh
-        self.qkv = torch.nn.Linear(m, 3 * m)
-        self.proj = torch.nn.Linear(m, m)
+        self.qkv = linear(m, 3 * m)
+        self.proj = linear(m, m)
 
     def forward(self, x):
         B, T, M = x.shape
@@ -25,23 +26,30 @@ class Attention(torch.nn.Module):
 
 
 class Block(torch.nn.Module):
-    def __init__(self, m, nh, ffn):
+    def __init__(self, m, nh, ffn, linear=torch.nn.Linear, fused_moe=False):
         super().__init__()
         self.ln1, self.ln2 = torch.nn.LayerNorm(m), torch.nn.LayerNorm(m)
-        self.attn = Attention(m, nh)
+        self.attn = Attention(m, nh, linear)
         self.ffn = ffn
+        self.fused_moe = fused_moe and isinstance(ffn, MoE)
 
     def forward(self, x):
         x = x + self.attn(self.ln1(x))
+        if self.fused_moe:
+            return self.ffn.block_forward(x, self.ln2)       # layer norm, gate and residual inside the chunk pipeline
         return x + self.ffn(self.ln2(x))
 
 
 class GPTMoE(torch.nn.Module):
     def __init__(self, vocab, m, nh, nl, seq, batch, ffn_dim, world_experts, k=2, capacity_factor=1.25, n_chunks=4,
-                 device="cuda", fabric=None, group=None, seed=0, act="gelu"):
+                 device="cuda", fabric=None, group=None, seed=0, act="gelu", pipeline=False):
         """act: activation of every FFN; the reference's GPT-2 uses ReLU (models/benchmark/pytorch/nlp.py:161-165),
-        its BERT / ViT GELU (:137-141)."""
+        its BERT / ViT GELU (:137-141).  pipeline: the MoE blocks run layer norm, gate projection and residual add
+        inside the layer's chunk pipeline, and the dense layers queue their weight gradients (DeferredLinear) so that
+        they run under the next MoE layer's returning exchange; the trainer joins the queue before the optimizer."""
         super().__init__()
+        linear = DeferredLinear if pipeline else torch.nn.Linear
+        self.pipeline = bool(pipeline)
         torch.manual_seed(seed)
         self.emb = torch.nn.Embedding(vocab, m)
         self.pos = torch.nn.Embedding(seq, m)
@@ -49,11 +57,11 @@ class GPTMoE(torch.nn.Module):
         for i in range(nl):
             if i % 2 == 1:
                 ffn = MoE(seq * batch, m, ffn_dim, world_experts, k, capacity_factor, n_chunks, torch.bfloat16, device, 2,
-                          fabric=fabric, group=group, seed=seed + i, act=act)
+                          fabric=fabric, group=group, seed=seed + i, act=act, pipeline=pipeline)
             else:
-                ffn = torch.nn.Sequential(torch.nn.Linear(m, ffn_dim), torch.nn.ReLU() if act == "relu" else torch.nn.GELU(),
-                                          torch.nn.Linear(ffn_dim, m))
-            blocks.append(Block(m, nh, ffn))
+                ffn = torch.nn.Sequential(linear(m, ffn_dim), torch.nn.ReLU() if act == "relu" else torch.nn.GELU(),
+                                          linear(ffn_dim, m))
+            blocks.append(Block(m, nh, ffn, linear, fused_moe=pipeline))
         self.blocks = torch.nn.ModuleList(blocks)
         self.ln = torch.nn.LayerNorm(m)
         torch.nn.init.normal_(self.emb.weight, std=0.02)
@@ -85,8 +93,10 @@ class LansTrainer:
     """One training step: forward, backward, gradient average of the replicated parameters across ranks
     (torch.distributed, outside this library's scope), LANS update through the library."""
 
-    def __init__(self, model, lr=1e-3, group=None):
+    def __init__(self, model, lr=1e-3, group=None, overlap_dw=True):
         self.model = model
+        self.overlap_dw = overlap_dw
+        self.device = next(model.parameters()).device
         self.params = [p for p in model.parameters()]
         expert_ids = {id(p) for p in model.expert_parameters()}
         self.shared = [p for p in self.params if id(p) not in expert_ids]
@@ -105,6 +115,10 @@ class LansTrainer:
         self.step_no += 1
         loss = self.model(ids)
         loss.backward()
+        # weight gradients still queued (dense blocks after the last MoE layer of the backward pass) and those running on
+        # the side stream must be complete before they are averaged and applied
+        DeferredGrads.join(self.device if self.device.type == "cuda" else None)
+        self.check_status()
         if self.world > 1:
             flat = torch._utils._flatten_dense_tensors([p.grad for p in self.shared])
             torch.distributed.all_reduce(flat, group=self.group)
@@ -117,3 +131,18 @@ class LansTrainer:
         for g in self.grads:
             g.zero_()
         return loss.detach()
+
+    def check_status(self):
+        """Bounded device-side waits (flag barriers between ranks, pipeline barriers of the expert GEMM) only record
+        that they ran out and let the kernels go on: read the status words once per step, before the update, and raise
+        LancetError(LANCET_ERR_TIMEOUT) instead of applying gradients computed from incomplete rows."""
+        words = [b.ffn.layer.moe.status for b in self.model.blocks if isinstance(b.ffn, MoE)]
+        if self.device.type == "cuda":
+            words.append(gemm_status(self.device))
+        if not words:
+            return
+        bad = torch.stack([w.reshape(-1)[0] for w in words]).cpu()      # one small copy; the step synchronises here anyway
+        for i, v in enumerate(bad.tolist()):
+            if v != 0:
+                raise _capi.LancetError(_capi.ERR_TIMEOUT, "a bounded wait ran out during this step (status word %d = %d): "
+                                        "a peer did not arrive; the optimizer step was skipped" % (i, v))

@@ -83,14 +83,14 @@ class MoELayer:
         self.moe.stage_gate(gate)
 
     def _window(self, c):
-        c0, c1 = self.stage_chunks[c]
-        return self.win_begin[c0], self.win_end[c1 - 1]
+        return self._win[c]
 
     def fwd_stage_dispatch(self, c):
         self.moe.stage_dispatch(self._x, *self.stage_chunks[c])
 
     def fwd_prepare(self):
         self.win_begin, self.win_end, self.cnt = self.moe.stage_prepare()
+        self._win = [(self.win_begin[c0], self.win_end[c1 - 1]) for c0, c1 in self.stage_chunks]
         self.x_e = self.moe.recv[self.moe.parity].view(self.G, self.C, self.M)
 
     def fwd_stage_experts_1(self, c):
@@ -114,6 +114,7 @@ class MoELayer:
         if getattr(self, "comm", None) is None:
             self.comm = torch.cuda.Stream(device=self.device)
             self.aux = torch.cuda.Stream(device=self.device, priority=-1)
+            self.post_stream = torch.cuda.Stream(device=self.device)
         return torch.cuda.current_stream(self.device), self.aux, self.comm
 
     def forward_pipelined(self, x, gate):
@@ -156,6 +157,72 @@ class MoELayer:
         self._fwd_schedule = "staged"
         return self.moe.out
 
+    # ---- pipelined forward with the neighbouring operators in the same chunk pipeline --------------------------
+    def forward_chunked(self, pre, post=None):
+        """The staged forward for callers that also split the operators in front of and behind the layer into the
+        same token chunks (the reference's forward partition of non-MoE operators,
+        src/pass/dist_optimization/partition_exprs.cc:1709-1795): the gate probabilities of stage s+1 need not exist
+        when the rows of stage s start to travel.
+
+        pre(c0, c1), called on the current stream stage by stage, returns (rows [tokens, M], gate [tokens, E] float32)
+        of the tokens of chunks [c0, c1): whatever produces the layer's input (layer norm, gate projection) runs for
+        stage s+1 while the rows of stage s cross NVLink.  post(c0, c1, out_rows), if given, is called on a side
+        stream as soon as the combined output of those tokens is complete (residual add under the remaining
+        exchange stages).  Gating is chained chunk by chunk and the owners learn each stage's row layout just before
+        its rows arrive; results are bit-identical to `forward` on the concatenated inputs."""
+        n = len(self.stage_chunks)
+        main, aux, comm = self._streams()
+        moe, Sp = self.moe, self.moe.Sp
+        if getattr(self, "x_in", None) is None:
+            self.x_in = torch.empty((self.S, self.M), dtype=moe.dtype, device=self.device)
+        self._limits(True)
+        moe.begin_step()
+        arrived = []
+        for c0, c1 in self.stage_chunks:
+            rows, gate = pre(c0, c1)
+            dst = self.x_in[c0 * Sp:c1 * Sp]
+            if rows.data_ptr() != dst.data_ptr():
+                dst.copy_(rows)
+            moe.stage_gate_chunks(gate, c0, c1)
+            ready = main.record_event()
+            with torch.cuda.stream(comm):
+                comm.wait_event(ready)
+                moe.stage_dispatch(self.x_in, c0, c1)
+                moe.barrier()
+                arrived.append(comm.record_event())
+        self._x = self.x_in
+        self.x_e = moe.recv[moe.parity].view(self.G, self.C, self.M)
+        self.cnt = moe.counts[moe.parity]
+        self._win = [None] * n
+        for s in range(n):
+            main.wait_event(arrived[s])
+            self._win[s] = moe.stage_window(s, *self.stage_chunks[s])
+            if s == n - 1:
+                moe.zero_tail()          # the row totals are known with the last stage
+            self.fwd_stage_experts_1(s)
+            half = main.record_event()
+            with torch.cuda.stream(aux):
+                aux.wait_event(half)
+                self.fwd_stage_experts_2(s)
+                done = aux.record_event()
+            if s >= 1 or n == 1:
+                with torch.cuda.stream(comm):
+                    comm.wait_event(done)
+                    moe.barrier()
+                    for t in ([s - 1] if n > 1 else []) + ([s] if s == n - 1 else []):
+                        rows = self.fwd_stage_combine(t)
+                        if post is not None:
+                            ev = comm.record_event()
+                            with torch.cuda.stream(self.post_stream):
+                                self.post_stream.wait_event(ev)
+                                post(*self.stage_chunks[t], rows)
+        main.wait_stream(aux)
+        main.wait_stream(comm)
+        main.wait_stream(self.post_stream)
+        self._limits(False)
+        self._fwd_schedule = "staged"
+        return moe.out
+
     # ---- pipelined backward ----
     def bwd_stage_combine(self, dout, c):
         self.moe.stage_combine_backward(dout, *self.stage_chunks[c])
@@ -185,7 +252,10 @@ class MoELayer:
     def bwd_stage_dispatch(self, c):
         return self.moe.stage_dispatch_backward(*self.stage_chunks[c])
 
-    def backward_pipelined(self, dout):
+    def backward_pipelined(self, dout, post=None):
+        """post(c0, c1, dx_rows, dgates), if given, is called on a side stream as soon as the input gradient and the gate
+        gradients of the tokens of chunks [c0, c1) are complete (backward of the operators in front of the layer, chunk
+        by chunk, under the remaining exchange stages)."""
         if self._fwd_schedule != "staged":
             raise RuntimeError("backward_pipelined needs the row windows of forward_pipelined of the same step "
                                "(the last forward ran the %s schedule)" % self._fwd_schedule)
@@ -213,14 +283,19 @@ class MoELayer:
                 with torch.cuda.stream(comm):
                     comm.wait_event(done)
                     self.moe.barrier()
-                    if n > 1:
-                        self.bwd_stage_dispatch(c - 1)
-                    if c == n - 1:
-                        self.bwd_stage_dispatch(c)
+                    for t in ([c - 1] if n > 1 else []) + ([c] if c == n - 1 else []):
+                        rows = self.bwd_stage_dispatch(t)
+                        if post is not None:
+                            ev = comm.record_event()
+                            c0, c1 = self.stage_chunks[t]
+                            with torch.cuda.stream(self.post_stream):
+                                self.post_stream.wait_event(ev)
+                                post(c0, c1, rows, self.moe.dgates[c0:c1])
         # the weight gradients have no consumer before the optimizer: they run under the last gathers
         self.bwd_weights()
         main.wait_stream(aux)
         main.wait_stream(comm)
+        main.wait_stream(self.post_stream)
         self._limits(False)
         self._fwd_schedule = None
         return self.moe.dx, self.moe.dgates

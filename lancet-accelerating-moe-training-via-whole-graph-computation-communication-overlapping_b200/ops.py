@@ -252,6 +252,34 @@ def lans(tensor_list, step, learning_rate=1e-3, beta1=0.9, beta2=0.999, eps=1e-6
     return tensor_list
 
 
+def gate_softmax(h, wg, out=None):
+    """probs [S,E] float32 = softmax(h @ wg.T): the gate projection in front of `moe_encode` (Gate module of the
+    reference, models/benchmark/pytorch/utils.py:565-573), one warp per token in a fixed order, so that a token's
+    probabilities do not depend on which other tokens are in the call.  h [S,M] float32/float16/bfloat16, wg [E,M] float32."""
+    _require_cuda(h, wg, out)
+    S, M = h.shape
+    E = wg.shape[0]
+    if wg.dtype != torch.float32 or wg.shape[1] != M:
+        raise TypeError("gate_softmax: wg must be float32 [E, M]")
+    out = torch.empty((S, E), dtype=torch.float32, device=h.device) if out is None else out
+    check(_capi.lib().lancet_gate_softmax(_ptr(h), _dt(h), _ptr(wg), _ptr(out), S, M, E, _stream(h)))
+    return out
+
+
+def gate_softmax_bwd(probs, dprobs, wg, dtype):
+    """Returns (dlogits [S,E] float32, dh [S,M] in `dtype`) of `gate_softmax`; the weight gradient is dlogits.T @ h."""
+    _require_cuda(probs, dprobs, wg)
+    S, E = probs.shape
+    M = wg.shape[1]
+    if probs.dtype != torch.float32 or dprobs.dtype != torch.float32 or wg.dtype != torch.float32:
+        raise TypeError("gate_softmax_bwd: probs, dprobs and wg must be float32")
+    dlogits = torch.empty_like(probs)
+    dh = torch.empty((S, M), dtype=dtype, device=probs.device)
+    check(_capi.lib().lancet_gate_softmax_bwd(_ptr(probs), _ptr(dprobs), _ptr(wg), _ptr(dlogits), _ptr(dh), _DT[dtype], S, M, E,
+                                              _stream(probs)))
+    return dlogits, dh
+
+
 ACT = {None: 0, "none": 0, "relu": 1, "gelu": 2, "gelu_tanh": 3}
 _gemm_status = {}
 

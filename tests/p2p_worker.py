@@ -60,6 +60,31 @@ def main():
     assert int(LB.gemm_status(dev).item()) == 0
     dist.barrier()
     layer.moe.close()
+    # the block with layer norm, gate projection and residual add inside the chunk pipeline (incremental gating: the
+    # owners learn each stage's row layout just before its rows arrive) against the unchunked block, across two ranks
+    res = []
+    for pipeline in (False, True):
+        moe = LB.MoE(2048, 256, 512, E, k=2, capacity_factor=1.25, n_chunks=4, dtype=torch.bfloat16, device=dev, local_experts=LE,
+                     seed=7, pipeline=pipeline)
+        torch.manual_seed(5)
+        ln = torch.nn.LayerNorm(256).to(dev)
+        with torch.no_grad():
+            moe.wg.weight.copy_(torch.randn_like(moe.wg.weight) * 0.2)
+        g = torch.Generator(device=dev).manual_seed(400 + rank)
+        bx = torch.randn((2048, 256), device=dev, generator=g).requires_grad_(True)
+        bdy = torch.randn((2048, 256), device=dev, generator=g)
+        for step in range(2):
+            for p in list(moe.parameters()) + [bx]:
+                p.grad = None
+            by = moe.block_forward(bx, ln)
+            by.backward(bdy)
+        torch.cuda.synchronize()
+        moe.layer.moe.check()
+        res.append((by.detach().clone(), bx.grad.clone(), moe.w1.grad.clone(), moe.w2.grad.clone()))
+        dist.barrier()
+        moe.layer.moe.close()
+    for a, b in zip(*res):
+        assert torch.equal(a, b)
     # stand-alone _all_to_all over NCCL: rank r sends rows filled with r+1, expects row i = i+1
     # (tests/python/distributed/test_alltoall.py:22-59 of the reference)
     comm = LB.Communicator(dev)
