@@ -51,7 +51,11 @@ class GPTMoE(torch.nn.Module):
         linear = DeferredLinear if pipeline else torch.nn.Linear
         self.pipeline = bool(pipeline)
         torch.manual_seed(seed)
-        self.emb = torch.nn.Embedding(vocab, m)
+        # the tied output projection is a GEMM with the vocabulary as one extent: an odd size (50257) forces the library
+        # onto an unaligned legacy kernel that costs a third of the step, so the table is padded to a multiple of 128
+        # rows; the extra rows are never indexed and their logits are dropped before the loss
+        self.vocab = vocab
+        self.emb = torch.nn.Embedding((vocab + 127) // 128 * 128, m)
         self.pos = torch.nn.Embedding(seq, m)
         blocks = []
         for i in range(nl):
@@ -81,7 +85,7 @@ class GPTMoE(torch.nn.Module):
             for b in self.blocks:
                 x = b(x)
             logits = F.linear(self.ln(x), self.emb.weight)         # tied output embedding
-        return F.cross_entropy(logits[:, :-1].reshape(-1, logits.shape[-1]).float(), ids[:, 1:].reshape(-1))
+        return F.cross_entropy(logits[:, :-1, :self.vocab].float().reshape(-1, self.vocab), ids[:, 1:].reshape(-1))
 
     def close(self):
         for b in self.blocks:
