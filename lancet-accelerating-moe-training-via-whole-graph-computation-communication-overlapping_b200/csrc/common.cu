@@ -67,7 +67,8 @@ int sm_count() {
   return cached[dev];
 }
 
-static int g_exchange_ctas = 0, g_gemm_ctas = 0;
+static int g_exchange_ctas = 0, g_gemm_ctas = 0, g_gemm_paired = 1;
+bool gemm_paired_enabled() { return __atomic_load_n(&g_gemm_paired, __ATOMIC_RELAXED) != 0; }
 int exchange_cta_limit() { return __atomic_load_n(&g_exchange_ctas, __ATOMIC_RELAXED); }
 int gemm_cta_limit() { return __atomic_load_n(&g_gemm_ctas, __ATOMIC_RELAXED); }
 
@@ -78,6 +79,11 @@ int lancet_set_cta_limits(int exchange_ctas, int gemm_ctas) {
   if (exchange_ctas < 0 || gemm_ctas < 0) return lancet::fail(LANCET_ERR_INVALID, "lancet_set_cta_limits: negative limit");
   __atomic_store_n(&lancet::g_exchange_ctas, exchange_ctas, __ATOMIC_RELAXED);
   __atomic_store_n(&lancet::g_gemm_ctas, gemm_ctas, __ATOMIC_RELAXED);
+  return LANCET_OK;
+}
+
+int lancet_set_gemm_paired(int on) {
+  __atomic_store_n(&lancet::g_gemm_paired, on ? 1 : 0, __ATOMIC_RELAXED);
   return LANCET_OK;
 }
 

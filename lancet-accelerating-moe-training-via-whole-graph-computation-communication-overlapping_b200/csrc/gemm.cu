@@ -12,7 +12,14 @@
 // counts[g] rows of a group are live: tiles past them are skipped, which is what the reference's
 // count-aware path intended (cublas/matmul.cc:221-247, commented out there).
 //
-// One persistent CTA per SM walks a static list of 128 x 256 output tiles.  Warp 0 is the TMA
+// Two forms of the kernel.  In the paired form (the default whenever the shape allows it) the two CTAs of a
+// thread-block cluster share one 256 x 256 output tile through tcgen05.mma.cta_group::2: each CTA stages its own 128
+// rows of A and its own 128 of the 256 columns' worth of B (32 KB per pipeline stage instead of 48, six stages instead
+// of four), the even CTA issues the MMAs for both, and every CTA keeps its 128 x 256 half of the accumulator in its
+// own TMEM.  Half the B bytes per FLOP pass through shared memory, which is what limits the single-CTA form.  All TMA
+// loads are plain (no cluster multicast): each CTA fetches its own operands and signals the even CTA's barrier.
+//
+// Single-CTA form: one persistent CTA per SM walks a static list of 128 x 256 output tiles.  Warp 0 is the TMA
 // producer (cp.async.bulk.tensor into 128-byte-swizzled shared memory, 4 stages of 64-wide K
 // blocks), warp 1 issues tcgen05.mma (one thread) into one of two 256-column TMEM accumulators,
 // warps 2-9 are the epilogue (tcgen05.ld, bias + activation, 16-byte stores; two warps per TMEM lane quadrant), so the epilogue of
@@ -26,14 +33,21 @@
 namespace lancet {
 namespace gemm {
 
-constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
+constexpr int BM = 128, BN = 256, BK = 64;
 constexpr int UMMA_K = 16;
 constexpr int A_STAGE_BYTES = BM * BK * 2;   // 16 KB
-constexpr int B_STAGE_BYTES = BN * BK * 2;   // 32 KB
-constexpr int SMEM_DATA = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES);
 constexpr int MAX_GROUPS = 1024;              // row-parallel forms keep a per-group tile table in shared memory
 constexpr int SCHED_BYTES = (2 * MAX_GROUPS + 1) * 4;
-constexpr int SMEM_BYTES = SMEM_DATA + 1024 /*alignment slack*/ + 256 /*barriers*/ + SCHED_BYTES;
+// CTA2 = the paired form: a CTA holds B for 128 of the tile's 256 columns
+template <bool CTA2>
+struct Cfg {
+  static constexpr int STAGES = CTA2 ? 6 : 4;
+  static constexpr int B_COLS = CTA2 ? BN / 2 : BN;          // output columns whose B operand this CTA stages
+  static constexpr int B_STAGE_BYTES = B_COLS * BK * 2;       // 16 or 32 KB
+  static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+  static constexpr int SMEM_DATA = STAGES * STAGE_BYTES;
+  static constexpr int SMEM_BYTES = SMEM_DATA + 1024 /*alignment slack*/ + 256 /*barriers*/ + SCHED_BYTES;
+};
 constexpr int EPI_WARPS = 8;                 // two warps per TMEM lane quadrant, each takes half of the columns
 constexpr int THREADS = 64 + 32 * EPI_WARPS; // warps: 0 TMA, 1 MMA, 2.. epilogue
 constexpr int TMEM_COLS = 512;               // two accumulators of BN fp32 columns
@@ -59,6 +73,7 @@ struct Params {
   void* preact;           // EPI_ACT: optional copy of the pre-activation; EPI_DACT: the saved pre-activation (input)
   int act;                // 0 none, 1 relu, 2 gelu (erf), 3 gelu (tanh)
   int epi;
+  int paired;             // host side: launch the paired (two CTAs per 256 x 256 tile) form
   int* status;
 };
 
@@ -113,6 +128,50 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
       "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
       ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
+}
+// Paired form: the same loads, completing on the mbarrier of the even CTA of the pair (`bar` is a shared::cluster
+// address made with leader_addr); no multicast, every CTA loads its own operands.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of the same shared-memory offset in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t cluster_addr(uint32_t local, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accum) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accum)
+      : "memory");
+}
+// arrives (once the MMAs issued so far have completed) on the barrier at this offset in both CTAs of the pair
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(bar), "h"((unsigned short)3)
+               : "memory");
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -173,10 +232,10 @@ __device__ __forceinline__ uint64_t smem_desc_mn_sw128(uint32_t addr) {
 }
 
 template <typename T>
-__device__ __forceinline__ uint32_t instr_desc(bool a_mn, bool b_mn) {
+__device__ __forceinline__ uint32_t instr_desc(bool a_mn, bool b_mn, int m_rows) {
   const uint32_t fmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;  // 0 = f16, 1 = bf16
   return (1u << 4) | (fmt << 7) | (fmt << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) |
-         ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);  // D = f32
+         ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(m_rows >> 4) << 24);  // D = f32; 128 rows, or 256 over a CTA pair
 }
 
 // erf(|x| / sqrt 2) and exp(-x^2 / 2) from one reciprocal, one exp2 and a degree-5 polynomial (Abramowitz & Stegun
@@ -211,7 +270,7 @@ __device__ __forceinline__ float dactivate(float x) {
 }
 
 struct Tile {
-  int group, mt, nt, rows;  // rows = live rows of the group
+  int group, mt, nt, rows;  // mt = this CTA's 128-row tile; rows = live rows of the group
 };
 
 // Number of 64-row reduction blocks of group g (MODE_REDUCE).
@@ -225,10 +284,11 @@ __device__ __forceinline__ int group_row_blocks(const Params& p, int g) {
 }
 
 // Row-parallel forms walk a compacted list of the live tiles only: group g contributes the m-tiles
-// [lo[g], lo[g] + (pref[g+1] - pref[g])) of its row window, each times n_tiles column tiles, ordered
-// (group, band of BAND m-tiles, n-tile, m-tile in band) so that a band of A stays in L2 against a sweep of B.
+// [lo[g], lo[g] + nm[g]) of its row window, each times n_tiles column tiles, ordered
+// (group, band of BAND m-units, n-tile, m-unit in band) so that a band of A stays in L2 against a sweep of B.
+// An m-unit is one 128-row tile, or in the paired form two consecutive ones (the second may lie past the live rows).
 struct Sched {
-  const int* pref;  // [groups + 1] exclusive prefix of live m-tiles
+  const int* pref;  // [groups + 1] exclusive prefix of live m-units
   const int* lo;    // [groups] first live m-tile
   int g;            // group of the previous tile of this walker (tile indices only grow)
 };
@@ -238,15 +298,16 @@ __device__ __forceinline__ int live_tiles(const Params& p, const Sched& sc) {
   return MODE == MODE_REDUCE ? p.total_tiles : sc.pref[p.groups] * p.n_tiles;
 }
 
-template <int MODE>
-__device__ __forceinline__ Tile decode_tile(const Params& p, Sched& sc, int t) {
+template <int MODE, bool CTA2>
+__device__ __forceinline__ Tile decode_tile(const Params& p, Sched& sc, int t, int rank) {
   Tile tl;
   if (MODE == MODE_REDUCE) {
-    // tiles_per_group = m_tiles * n_tiles per expert; `group` holds the expert index
+    // tiles_per_group = m_units * n_tiles per expert; `group` holds the expert index
     tl.group = t / p.tiles_per_group;
     const int r = t - tl.group * p.tiles_per_group;
     tl.nt = r / p.m_tiles;
-    tl.mt = r - tl.nt * p.m_tiles;
+    const int mu = r - tl.nt * p.m_tiles;
+    tl.mt = CTA2 ? 2 * mu + rank : mu;
     tl.rows = p.Mout;
     return tl;
   }
@@ -261,7 +322,8 @@ __device__ __forceinline__ Tile decode_tile(const Params& p, Sched& sc, int t) {
   r -= band * band_tiles;
   const int m_in_band = min(BAND, nm - band * BAND);
   tl.nt = r / m_in_band;
-  tl.mt = sc.lo[g] + band * BAND + (r - tl.nt * m_in_band);
+  const int mu = band * BAND + (r - tl.nt * m_in_band);
+  tl.mt = sc.lo[g] + (CTA2 ? 2 * mu + rank : mu);
   int rows = p.C;
   if (p.counts) {
     rows = p.counts[g];
@@ -294,26 +356,34 @@ __device__ __forceinline__ int tile_k_blocks(const Params& p, const Tile& tl) {
 // ACT is a template parameter: with the activation chosen at run time inside the element loop every element
 // became its own chain of basic blocks, the 32 independent chains of a lane could not be interleaved, and the
 // GELU epilogue (latency-bound, 1.5 ms against 1.1 ms without it) held the tensor pipe back.
-template <typename T, int MODE, bool B_MN, int EPI, int ACT>
+template <typename T, int MODE, bool B_MN, int EPI, int ACT, bool CTA2>
 __global__ void __launch_bounds__(THREADS, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, Params p) {
+  using C = Cfg<CTA2>;
+  constexpr int STAGES = C::STAGES;
+  constexpr int B_STAGE_BYTES = C::B_STAGE_BYTES;
   constexpr bool A_MN = (MODE == MODE_REDUCE);
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   unsigned char* sA = smem;
   unsigned char* sB = smem + STAGES * A_STAGE_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SMEM_DATA);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::SMEM_DATA);
   // barriers: full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2]
   const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + STAGES);
   const uint32_t bar_tfull = smem_u32(bars + 2 * STAGES), bar_tempty = smem_u32(bars + 2 * STAGES + 2);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  int* s_pref = reinterpret_cast<int*>(smem + SMEM_DATA + 256);
+  int* s_pref = reinterpret_cast<int*>(smem + C::SMEM_DATA + 256);
   int* s_lo = s_pref + MAX_GROUPS + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // paired form: rank of this CTA in its pair; the even CTA (leader) issues the MMAs and owns the barriers that
+  // gather both CTAs' loads and both CTAs' epilogues
+  const int rank = CTA2 ? (int)cluster_ctarank() : 0;
+  const int worker = CTA2 ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int n_workers = CTA2 ? (int)(gridDim.x >> 1) : (int)gridDim.x;
   if (MODE == MODE_ROWS && warp == 2) {
-    // live m-tiles of every group and their exclusive prefix (warp scan, 32 groups a round)
+    // live m-units of every group and their exclusive prefix (warp scan, 32 groups a round)
     int carry = 0;
     for (int base = 0; base < p.groups; base += 32) {
       const int g = base + lane;
@@ -330,6 +400,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
         nm = (rows + BM - 1) / BM - lo;
         nm = nm < 0 ? 0 : nm;
+        if (CTA2) nm = (nm + 1) >> 1;
       }
       int incl = nm;
 #pragma unroll
@@ -352,50 +423,75 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar_tfull + 8 * b, 1);
-      mbar_init(bar_tempty + 8 * b, EPI_WARPS);
+      mbar_init(bar_tempty + 8 * b, CTA2 ? 2 * EPI_WARPS : EPI_WARPS);
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if (CTA2) {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if (CTA2) cluster_sync_all();   // the peer's barriers exist before anything signals them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
-    // ---------------- TMA producer ----------------
+    // ---------------- TMA producer (one per CTA; in the paired form each CTA loads its own halves) ----------------
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
       Sched sc{s_pref, s_lo, 0};
       const int n_live = live_tiles<MODE>(p, sc);
-      for (int t = blockIdx.x; t < n_live && ok; t += gridDim.x) {
-        const Tile tl = decode_tile<MODE>(p, sc, t);
+      const int b_col_off = CTA2 ? rank * (BN / 2) : 0;   // this CTA's share of the tile's columns (B operand)
+      for (int t = worker; t < n_live && ok; t += n_workers) {
+        const Tile tl = decode_tile<MODE, CTA2>(p, sc, t, rank);
         if (MODE == MODE_ROWS) {
           const int e = tl.group % p.LE;
           const int a_row = tl.group * p.C + tl.mt * BM;
           const int k_blocks = (p.K + BK - 1) / BK;
           for (int kb = 0; kb < k_blocks; ++kb) {
             if (!(ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, p.status, 1))) break;
-            const uint32_t full = bar_full + 8 * stage;
-            mbar_expect_tx(full, A_STAGE_BYTES + B_STAGE_BYTES);
-            if (p.interleaved)
-              tma_load_3d(smem_u32(sA + stage * A_STAGE_BYTES), &tmA, full, kb * BK, tl.group, tl.mt * BM);
-            else
-              tma_load_2d(smem_u32(sA + stage * A_STAGE_BYTES), &tmA, full, kb * BK, a_row);
+            const uint32_t a_dst = smem_u32(sA + stage * A_STAGE_BYTES);
             const uint32_t b_dst = smem_u32(sB + stage * B_STAGE_BYTES);
-            if (!B_MN) {
-              tma_load_2d(b_dst, &tmB, full, kb * BK, e * p.N + tl.nt * BN);
-            } else {
+            if (!CTA2) {
+              const uint32_t full = bar_full + 8 * stage;
+              mbar_expect_tx(full, C::STAGE_BYTES);
+              if (p.interleaved)
+                tma_load_3d(a_dst, &tmA, full, kb * BK, tl.group, tl.mt * BM);
+              else
+                tma_load_2d(a_dst, &tmA, full, kb * BK, a_row);
+              if (!B_MN) {
+                tma_load_2d(b_dst, &tmB, full, kb * BK, e * p.N + tl.nt * BN);
+              } else {
 #pragma unroll
-              for (int j = 0; j < BN / 64; ++j)
-                tma_load_2d(b_dst + j * BOX_BYTES, &tmB, full, tl.nt * BN + j * 64, e * p.K + kb * BK);
+                for (int j = 0; j < BN / 64; ++j)
+                  tma_load_2d(b_dst + j * BOX_BYTES, &tmB, full, tl.nt * BN + j * 64, e * p.K + kb * BK);
+              }
+            } else {
+              if (rank == 0) mbar_expect_tx(bar_full + 8 * stage, 2 * C::STAGE_BYTES);   // both CTAs' bytes
+              const uint32_t full = cluster_addr(bar_full + 8 * stage, 0);
+              if (p.interleaved)
+                tma_load_3d_pair(a_dst, &tmA, full, kb * BK, tl.group, tl.mt * BM);
+              else
+                tma_load_2d_pair(a_dst, &tmA, full, kb * BK, a_row);
+              if (!B_MN) {
+                tma_load_2d_pair(b_dst, &tmB, full, kb * BK, e * p.N + tl.nt * BN + b_col_off);
+              } else {
+#pragma unroll
+                for (int j = 0; j < BN / 128; ++j)
+                  tma_load_2d_pair(b_dst + j * BOX_BYTES, &tmB, full, tl.nt * BN + b_col_off + j * 64, e * p.K + kb * BK);
+              }
             }
             if (++stage == STAGES) { stage = 0; phase ^= 1; }
           }
@@ -404,14 +500,25 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             const int nb = group_row_blocks(p, g);
             for (int rb = 0; rb < nb; ++rb) {
               if (!(ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, p.status, 1))) break;
-              const uint32_t full = bar_full + 8 * stage;
-              mbar_expect_tx(full, A_STAGE_BYTES + B_STAGE_BYTES);
               const uint32_t a_dst = smem_u32(sA + stage * A_STAGE_BYTES);
               const uint32_t b_dst = smem_u32(sB + stage * B_STAGE_BYTES);
+              if (!CTA2) {
+                const uint32_t full = bar_full + 8 * stage;
+                mbar_expect_tx(full, C::STAGE_BYTES);
 #pragma unroll
-              for (int j = 0; j < BM / 64; ++j) tma_load_3d(a_dst + j * BOX_BYTES, &tmA, full, tl.mt * BM + j * 64, rb * BK, g);
+                for (int j = 0; j < BM / 64; ++j) tma_load_3d(a_dst + j * BOX_BYTES, &tmA, full, tl.mt * BM + j * 64, rb * BK, g);
 #pragma unroll
-              for (int j = 0; j < BN / 64; ++j) tma_load_3d(b_dst + j * BOX_BYTES, &tmB, full, tl.nt * BN + j * 64, rb * BK, g);
+                for (int j = 0; j < BN / 64; ++j) tma_load_3d(b_dst + j * BOX_BYTES, &tmB, full, tl.nt * BN + j * 64, rb * BK, g);
+              } else {
+                if (rank == 0) mbar_expect_tx(bar_full + 8 * stage, 2 * C::STAGE_BYTES);
+                const uint32_t full = cluster_addr(bar_full + 8 * stage, 0);
+#pragma unroll
+                for (int j = 0; j < BM / 64; ++j)
+                  tma_load_3d_pair(a_dst + j * BOX_BYTES, &tmA, full, tl.mt * BM + j * 64, rb * BK, g);
+#pragma unroll
+                for (int j = 0; j < BN / 128; ++j)
+                  tma_load_3d_pair(b_dst + j * BOX_BYTES, &tmB, full, tl.nt * BN + b_col_off + j * 64, rb * BK, g);
+              }
               if (++stage == STAGES) { stage = 0; phase ^= 1; }
             }
           }
@@ -419,9 +526,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
     }
   } else if (warp == 1) {
-    // ---------------- MMA issuer ----------------
-    if (lane == 0) {
-      const uint32_t idesc = instr_desc<T>(A_MN, B_MN);
+    // ---------------- MMA issuer (paired form: the even CTA only) ----------------
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = instr_desc<T>(A_MN, B_MN, CTA2 ? 2 * BM : BM);
       int stage = 0;
       uint32_t phase = 0;
       int buf = 0;
@@ -429,8 +536,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       bool ok = true;
       Sched sc{s_pref, s_lo, 0};
       const int n_live = live_tiles<MODE>(p, sc);
-      for (int t = blockIdx.x; t < n_live && ok; t += gridDim.x) {
-        const Tile tl = decode_tile<MODE>(p, sc, t);
+      for (int t = worker; t < n_live && ok; t += n_workers) {
+        const Tile tl = decode_tile<MODE, CTA2>(p, sc, t, rank);
         // an empty reduction (weight-gradient form, all counts zero) still hands the accumulator over:
         // the epilogue masks its contents to zero
         const int k_blocks = tile_k_blocks<MODE>(p, tl);
@@ -447,13 +554,17 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             // K-major: 16 elements further inside the 128-byte row; MN-major: 16 reduction rows = two 1024-byte atoms
             const uint64_t adesc = A_MN ? smem_desc_mn_sw128(a_addr + k * 2048) : smem_desc_k_sw128(a_addr + k * UMMA_K * 2);
             const uint64_t bdesc = B_MN ? smem_desc_mn_sw128(b_addr + k * 2048) : smem_desc_k_sw128(b_addr + k * UMMA_K * 2);
-            umma_f16(tmem_d, adesc, bdesc, idesc, (kb | k) ? 1u : 0u);
+            if (CTA2)
+              umma_f16_pair(tmem_d, adesc, bdesc, idesc, (kb | k) ? 1u : 0u);
+            else
+              umma_f16(tmem_d, adesc, bdesc, idesc, (kb | k) ? 1u : 0u);
           }
-          umma_commit(bar_empty + 8 * stage);  // frees the stage when these MMAs have read it
+          // frees the stage (in both CTAs of a pair) when these MMAs have read it
+          if (CTA2) umma_commit_pair(bar_empty + 8 * stage); else umma_commit(bar_empty + 8 * stage);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
-        umma_commit(bar_tfull + 8 * buf);      // accumulator complete
+        if (CTA2) umma_commit_pair(bar_tfull + 8 * buf); else umma_commit(bar_tfull + 8 * buf);   // accumulator complete
         tphase[buf] ^= 1;
         buf ^= 1;
       }
@@ -471,8 +582,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const T* bias = static_cast<const T*>(p.bias);
     Sched sc{s_pref, s_lo, 0};
     const int n_live = live_tiles<MODE>(p, sc);
-    for (int t = blockIdx.x; t < n_live && ok; t += gridDim.x) {
-      const Tile tl = decode_tile<MODE>(p, sc, t);
+    for (int t = worker; t < n_live && ok; t += n_workers) {
+      const Tile tl = decode_tile<MODE, CTA2>(p, sc, t, rank);
       // row-parallel forms always reduce over K >= 1; only the weight-gradient form can meet an empty
       // reduction, whose accumulator holds stale values: they are masked to zero bit-wise (no branch in
       // the hot loop: extra control flow here made the compiler serialise the epilogue)
@@ -548,7 +659,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
+      if (lane == 0) {
+        // the MMA issuer (even CTA of a pair) may overwrite this accumulator once both CTAs' epilogues have read it
+        if (CTA2) mbar_arrive_cluster(cluster_addr(bar_tempty + 8 * buf, 0)); else mbar_arrive(bar_tempty + 8 * buf);
+      }
       tphase[buf] ^= 1;
       buf ^= 1;
     }
@@ -563,9 +677,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
     __syncthreads();
   }
+  if (CTA2) cluster_sync_all();   // the peer no longer signals this CTA's barriers or reads its shared memory
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    if (CTA2)
+      asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    else
+      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
   }
 }
 
@@ -689,22 +807,53 @@ static int make_map3(CUtensorMap* map, const void* base, uint64_t groups, uint64
   return LANCET_OK;
 }
 
-template <typename T, int MODE, bool B_MN, int EPI, int ACT>
-static int launch_a(const CUtensorMap& tmA, const CUtensorMap& tmB, const Params& p, const char* name, cudaStream_t st) {
+template <typename T, int MODE, bool B_MN, int EPI, int ACT, bool CTA2>
+static int launch_f(const CUtensorMap& tmA, const CUtensorMap& tmB, const Params& p, const char* name, cudaStream_t st) {
+  constexpr int SMEM_BYTES = Cfg<CTA2>::SMEM_BYTES;
+  auto kernel = grouped_gemm_kernel<T, MODE, B_MN, EPI, ACT, CTA2>;
   static bool attr_set = false;
   if (!attr_set) {
-    LANCET_CUDA(cudaFuncSetAttribute(grouped_gemm_kernel<T, MODE, B_MN, EPI, ACT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     SMEM_BYTES));
+    LANCET_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
     attr_set = true;
   }
   int grid = sm_count();
   if (gemm_cta_limit() > 0 && gemm_cta_limit() < grid) grid = gemm_cta_limit();
-  if (grid > p.total_tiles) grid = p.total_tiles;
+  // total_tiles counts the units one worker takes at a time: a tile, or in the paired form a 256-row pair of tiles
+  const long long max_ctas = (long long)p.total_tiles * (CTA2 ? 2 : 1);
+  if (grid > max_ctas) grid = (int)max_ctas;
+  if (CTA2) grid &= ~1;
+  if (grid < (CTA2 ? 2 : 1)) grid = CTA2 ? 2 : 1;
   {
     ProfScope prof(name, st);
-    grouped_gemm_kernel<T, MODE, B_MN, EPI, ACT><<<grid, THREADS, SMEM_BYTES, st>>>(tmA, tmB, p);
+    if (CTA2) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3((unsigned)grid);
+      cfg.blockDim = dim3(THREADS);
+      cfg.dynamicSmemBytes = SMEM_BYTES;
+      cfg.stream = st;
+      cudaLaunchAttribute attr;
+      attr.id = cudaLaunchAttributeClusterDimension;
+      attr.val.clusterDim.x = 2;
+      attr.val.clusterDim.y = 1;
+      attr.val.clusterDim.z = 1;
+      cfg.attrs = &attr;
+      cfg.numAttrs = 1;
+      cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, p);
+      if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(LANCET_ERR_CUDA, "launch of %s (paired form) failed: %s", name, cudaGetErrorString(e));
+      }
+    } else {
+      kernel<<<grid, THREADS, SMEM_BYTES, st>>>(tmA, tmB, p);
+    }
   }
   return launch_status(name);
+}
+
+template <typename T, int MODE, bool B_MN, int EPI, int ACT>
+static int launch_a(const CUtensorMap& tmA, const CUtensorMap& tmB, const Params& p, const char* name, cudaStream_t st) {
+  if (p.paired) return launch_f<T, MODE, B_MN, EPI, ACT, true>(tmA, tmB, p, name, st);
+  return launch_f<T, MODE, B_MN, EPI, ACT, false>(tmA, tmB, p, name, st);
 }
 
 // Only the combinations that exist are instantiated: the forward form takes any activation, the data-gradient form
@@ -751,7 +900,9 @@ static int rows_common(const char* fn, const void* A, const void* B, void* D, in
   LANCET_REQUIRE((long long)groups * C < (1ll << 31) && (long long)LE * N < (1ll << 31) && (long long)LE * K < (1ll << 31),
                  LANCET_ERR_INVALID, "%s: row counts exceed 2^31", fn);
   p->groups = groups; p->LE = LE; p->C = C; p->N = N; p->K = K; p->Mout = 0;
+  p->paired = gemm_paired_enabled() ? 1 : 0;
   p->m_tiles = (C + BM - 1) / BM;
+  if (p->paired) p->m_tiles = (p->m_tiles + 1) / 2;
   p->n_tiles = N / BN;
   p->tiles_per_group = p->m_tiles * p->n_tiles;
   const long long total = (long long)p->tiles_per_group * groups;
@@ -782,7 +933,7 @@ int lancet_grouped_gemm_nt_window(const void* A, const void* B, void* D, const v
   p.counts = row_end; p.row_lo = row_begin; p.bias = bias; p.D = D; p.preact = preact; p.epi = EPI_ACT;
   CUtensorMap tmA, tmB;
   if (int rc = make_map(&tmA, A, (uint64_t)groups * C, (uint64_t)K, BM, dtype)) return rc;
-  if (int rc = make_map(&tmB, B, (uint64_t)LE * N, (uint64_t)K, BN, dtype)) return rc;
+  if (int rc = make_map(&tmB, B, (uint64_t)LE * N, (uint64_t)K, p.paired ? BN / 2 : BN, dtype)) return rc;
   if (preact)
     return launch<MODE_ROWS, false, EPI_ACT_PRE>(tmA, tmB, p, dtype, "grouped_gemm_nt_kernel", static_cast<cudaStream_t>(stream));
   return launch<MODE_ROWS, false, EPI_ACT>(tmA, tmB, p, dtype, "grouped_gemm_nt_kernel", static_cast<cudaStream_t>(stream));
@@ -836,7 +987,8 @@ int lancet_grouped_gemm_tn(const void* A, const void* B, void* D, int groups, in
                  "lancet_grouped_gemm_tn: row counts exceed 2^31");
   Params p;
   p.groups = groups; p.LE = LE; p.C = C; p.N = N; p.K = 0; p.Mout = Mout;
-  p.m_tiles = Mout / BM; p.n_tiles = N / BN;
+  p.paired = (gemm_paired_enabled() && Mout % (2 * BM) == 0) ? 1 : 0;
+  p.m_tiles = Mout / (p.paired ? 2 * BM : BM); p.n_tiles = N / BN;
   p.tiles_per_group = p.m_tiles * p.n_tiles;
   p.total_tiles = p.tiles_per_group * LE;
   p.counts = counts; p.row_lo = nullptr; p.interleaved = 0; p.bias = nullptr; p.D = D; p.preact = nullptr; p.act = 0;
@@ -881,7 +1033,7 @@ int lancet_sparse_expert_matmul_nt(const void* data, const void* weight, void* o
   CUtensorMap tmA, tmB;
   // data [C][G][M]: dimension order (M, G, C), one group and 128 rows of it per box
   if (int rc = make_map3(&tmA, data, (uint64_t)C, (uint64_t)G, (uint64_t)M, dtype, 1, BM)) return rc;
-  if (int rc = make_map(&tmB, weight, (uint64_t)N, (uint64_t)M, BN, dtype)) return rc;
+  if (int rc = make_map(&tmB, weight, (uint64_t)N, (uint64_t)M, p.paired ? BN / 2 : BN, dtype)) return rc;
   const int rc = dtype == LANCET_BF16
                      ? launch_t<__nv_bfloat16, MODE_ROWS, false, EPI_ACT>(tmA, tmB, p, "sparse_expert_matmul_nt_kernel", st)
                      : launch_t<__half, MODE_ROWS, false, EPI_ACT>(tmA, tmB, p, "sparse_expert_matmul_nt_kernel", st);

@@ -253,3 +253,47 @@ def test_sparse_expert_matmul_nt(C, G, M, N, elements, stride, offset, scale, dt
     scale_ = np.abs(ref).max() + 1e-6
     assert np.abs(got - ref).max() <= 1e-2 * scale_          # 16-bit operands, fp32 accumulation
     check_status()
+
+
+@pytest.mark.parametrize("C,counts_kind", [(2560, "full"), (640, "ragged"), (384, "odd")])
+def test_paired_and_single_cta_forms_agree_bit_for_bit(C, counts_kind):
+    """The two-CTA form (tcgen05 cta_group::2, 256 x 256 tile per CTA pair) and the single-CTA form run the same
+    contraction in the same order per output element: forward, data-gradient and weight-gradient forms must agree exactly."""
+    L = _capi.lib()
+    groups, LE, M, H = 8, 2, 512, 1024
+    g = torch.Generator(device=DEV).manual_seed(C)
+    x = torch.randn((groups, C, M), device=DEV, generator=g).bfloat16()
+    w1 = (torch.randn((LE, H, M), device=DEV, generator=g) * 0.05).bfloat16()
+    b1 = (torch.randn((LE, H), device=DEV, generator=g) * 0.1).bfloat16()
+    dy = torch.randn((groups, C, H), device=DEV, generator=g).bfloat16()
+    counts = None
+    if counts_kind == "ragged":
+        counts = torch.randint(0, C + 1, (groups,), device=DEV, generator=g, dtype=torch.int32)
+        counts[1] = C
+        counts[2] = 0
+    elif counts_kind == "odd":
+        counts = torch.tensor([384, 129, 128, 1, 0, 257, 300, 383], device=DEV, dtype=torch.int32)   # odd tile counts: dead second halves
+    res = []
+    try:
+        for paired in (1, 0):
+            _capi.check(L.lancet_set_gemm_paired(paired))
+            h = torch.zeros((groups, C, H), dtype=torch.bfloat16, device=DEV)
+            pre = torch.zeros_like(h)
+            LB.grouped_gemm_nt(x, w1, bias=b1, counts=counts, act="gelu", out=h, preact=pre)
+            dx = torch.zeros_like(x)
+            LB.grouped_gemm_nn(dy, w1, counts=counts, out=dx)
+            dh = torch.zeros_like(h)
+            LB.grouped_gemm_nn(x, w1.transpose(1, 2).contiguous(), counts=counts, act="gelu", preact=pre, out=dh)
+            dw = torch.zeros_like(w1)
+            LB.grouped_gemm_tn(dy, x, LE, counts=counts, out=dw)
+            torch.cuda.synchronize()
+            check_status()
+            res.append((h, pre, dx, dh, dw))
+    finally:
+        _capi.check(L.lancet_set_gemm_paired(1))
+    for a, b in zip(*res):
+        assert torch.equal(a, b)
+    # and the paired results are right: spot check the forward against float32
+    want = reference(x, w1, b1, "gelu")
+    n0 = C if counts is None else int(counts[0])
+    assert torch.allclose(res[0][0][0, :n0].float(), want[0, :n0], rtol=1e-2, atol=1e-2 * float(want.abs().max()))
