@@ -175,6 +175,8 @@ int lancet_moe_combine_chunked(const void* expert_out, const void* gates_s, int 
  * batch; the outputs describe partition `partition_id` of n_partitions (Sp = S_orig/n_partitions
  * tokens): gates_s [Sp], idx_loc [2,Sp] with (-1,-1) for dropped tokens, out_capused / out_elems [E].
  * Each expert keeps its C highest-gate tokens of the whole batch; ties go to the lower token index.
+ * One block per expert selects the C-th best gate with a radix select and assigns locations with prefix counts:
+ * the cost grows linearly with S_orig (about five passes over each expert's tokens), any S_orig is accepted.
  * lancet_moe_encode_bpr is the whole `raf.op.cuda.moe_encode_batch_prioritized` op: capacity
  * (int)(cf * ceil(Sp / E)), gating, then dispatch of the partition's rows of x [S_orig, M]. */
 size_t lancet_moe_gate_bpr_workspace_bytes(int S_orig, int E);

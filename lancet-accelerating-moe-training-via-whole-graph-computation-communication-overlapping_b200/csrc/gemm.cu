@@ -51,7 +51,7 @@ struct Cfg {
 constexpr int EPI_WARPS = 8;                 // two warps per TMEM lane quadrant, each takes half of the columns
 constexpr int THREADS = 64 + 32 * EPI_WARPS; // warps: 0 TMA, 1 MMA, 2.. epilogue
 constexpr int TMEM_COLS = 512;               // two accumulators of BN fp32 columns
-constexpr int BAND = 16;                     // m-tiles per band (L2 reuse of A against a sweep of B)
+constexpr int MAX_BAND = 16;                 // upper bound of the m-units per band (L2 reuse of A against a sweep of B)
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
 
 // MODE_ROWS:   D[g] (C x N) = epilogue(A[g] (C x K) * op(B[e])), tiles over (group, m-tile, n-tile), reduction over K.
@@ -65,6 +65,7 @@ struct Params {
   int groups, LE, C, N, K;
   int Mout;               // MODE_REDUCE: output rows per expert
   int m_tiles, n_tiles, tiles_per_group, total_tiles;
+  int band;               // MODE_ROWS: m-units per band of the tile order
   const int32_t* counts;  // [groups] live rows (end of the row window), or null
   const int32_t* row_lo;  // [groups] first row of the window (rounded down to a tile boundary), or null; MODE_ROWS only
   int interleaved;        // MODE_ROWS: A, D and preact are [C][groups][.] (row c of group g at c * groups + g) instead of [groups][C][.]
@@ -285,7 +286,7 @@ __device__ __forceinline__ int group_row_blocks(const Params& p, int g) {
 
 // Row-parallel forms walk a compacted list of the live tiles only: group g contributes the m-tiles
 // [lo[g], lo[g] + nm[g]) of its row window, each times n_tiles column tiles, ordered
-// (group, band of BAND m-units, n-tile, m-unit in band) so that a band of A stays in L2 against a sweep of B.
+// (group, band of p.band m-units, n-tile, m-unit in band) so that a band of A stays in L2 against a sweep of B.
 // An m-unit is one 128-row tile, or in the paired form two consecutive ones (the second may lie past the live rows).
 struct Sched {
   const int* pref;  // [groups + 1] exclusive prefix of live m-units
@@ -303,10 +304,18 @@ __device__ __forceinline__ Tile decode_tile(const Params& p, Sched& sc, int t, i
   Tile tl;
   if (MODE == MODE_REDUCE) {
     // tiles_per_group = m_units * n_tiles per expert; `group` holds the expert index
+    // the index that runs fastest is the one with fewer tiles, so that the tiles in flight at any time form a
+    // block as square as possible in (m, n) and share the most operand slabs through L2
     tl.group = t / p.tiles_per_group;
     const int r = t - tl.group * p.tiles_per_group;
-    tl.nt = r / p.m_tiles;
-    const int mu = r - tl.nt * p.m_tiles;
+    int mu;
+    if (p.n_tiles < p.m_tiles) {
+      mu = r / p.n_tiles;
+      tl.nt = r - mu * p.n_tiles;
+    } else {
+      tl.nt = r / p.m_tiles;
+      mu = r - tl.nt * p.m_tiles;
+    }
     tl.mt = CTA2 ? 2 * mu + rank : mu;
     tl.rows = p.Mout;
     return tl;
@@ -317,12 +326,12 @@ __device__ __forceinline__ Tile decode_tile(const Params& p, Sched& sc, int t, i
   tl.group = g;
   int r = t - sc.pref[g] * p.n_tiles;
   const int nm = sc.pref[g + 1] - sc.pref[g];
-  const int band_tiles = BAND * p.n_tiles;
+  const int band_tiles = p.band * p.n_tiles;
   const int band = r / band_tiles;
   r -= band * band_tiles;
-  const int m_in_band = min(BAND, nm - band * BAND);
+  const int m_in_band = min(p.band, nm - band * p.band);
   tl.nt = r / m_in_band;
-  const int mu = band * BAND + (r - tl.nt * m_in_band);
+  const int mu = band * p.band + (r - tl.nt * m_in_band);
   tl.mt = sc.lo[g] + (CTA2 ? 2 * mu + rank : mu);
   int rows = p.C;
   if (p.counts) {
@@ -912,6 +921,13 @@ static int rows_common(const char* fn, const void* A, const void* B, void* D, in
   p->act = act;
   p->row_lo = nullptr;
   p->interleaved = 0;
+  // A band of m-units is swept against all column tiles of an expert: the band's rows of A (band x rows x K) and the
+  // expert's B (N x K) should stay in L2 together.  About 20 MB for the band keeps both resident beside the outputs.
+  {
+    const long long unit_bytes = (long long)(p->paired ? 2 * BM : BM) * K * 2;
+    long long band = (20ll << 20) / (unit_bytes > 0 ? unit_bytes : 1);
+    p->band = (int)(band < 2 ? 2 : (band > MAX_BAND ? MAX_BAND : band));
+  }
   return LANCET_OK;
 }
 
@@ -991,6 +1007,7 @@ int lancet_grouped_gemm_tn(const void* A, const void* B, void* D, int groups, in
   p.m_tiles = Mout / (p.paired ? 2 * BM : BM); p.n_tiles = N / BN;
   p.tiles_per_group = p.m_tiles * p.n_tiles;
   p.total_tiles = p.tiles_per_group * LE;
+  p.band = 1;
   p.counts = counts; p.row_lo = nullptr; p.interleaved = 0; p.bias = nullptr; p.D = D; p.preact = nullptr; p.act = 0;
   p.epi = EPI_ACT;
   p.status = status;

@@ -8,10 +8,9 @@
 // tokens get (-1, -1).
 //
 // No global sort is needed: tokens are bucketed per expert in token order (reusing the gating
-// passes), every token counts the tokens of its own bucket that beat it, and a second count over the
-// bucket gives the final location.  The work is sum_e n_e^2 comparisons (n_e tokens chose expert e),
-// about S_orig^2 / E for balanced routing, served from L1/L2; this favours the batch sizes the
-// reference uses this gate with (10^4 tokens).
+// passes); one block per expert then finds the gate value of its C-th best token with a radix select
+// (four 8-bit rounds) and hands out the locations with block-wide prefix counts, all in about five
+// passes over the bucket, so the cost grows linearly with the batch.
 #include "common.cuh"
 
 namespace lancet {
@@ -37,52 +36,131 @@ bpr_bucket_kernel(const int32_t* __restrict__ il_all, const float* __restrict__ 
   }
 }
 
-// keep[pos] = 1 when fewer than C tokens of the same bucket have priority over this one.
-__global__ void __launch_bounds__(256)
-bpr_rank_kernel(const float* __restrict__ list_gate, const int32_t* __restrict__ list_exp, const int32_t* __restrict__ e_off,
-                const int32_t* __restrict__ n_e, int S, int C, unsigned char* __restrict__ keep) {
-  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < S; i += gridDim.x * blockDim.x) {
-    const int e = list_exp[i];
-    const int b = e_off[e], n = n_e[e];
-    const float g = list_gate[i];
-    int rank = 0;
-    // inside a bucket, list order is token order: an equal gate earlier in the list wins the tie
-    for (int j = b; j < i; ++j) rank += (list_gate[j] >= g) ? 1 : 0;
-    for (int j = i + 1; j < b + n; ++j) rank += (list_gate[j] > g) ? 1 : 0;
-    keep[i] = rank < C ? 1 : 0;
-  }
+// Order-preserving map of a float onto an unsigned integer (larger gate = larger key); -0 counts as +0.
+__device__ __forceinline__ uint32_t bpr_key(float g) {
+  if (g == 0.0f) g = 0.0f;
+  const uint32_t b = __float_as_uint(g);
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
 }
 
-__global__ void __launch_bounds__(256)
-bpr_locate_kernel(const float* __restrict__ list_gate, const int32_t* __restrict__ list_tok, const int32_t* __restrict__ list_exp,
-                  const int32_t* __restrict__ e_off, const int32_t* __restrict__ n_e, const unsigned char* __restrict__ keep,
-                  int S_orig, int Sp, int part_off, int C, int M, void* __restrict__ gates_out, int gates_dtype,
-                  int32_t* __restrict__ idx_loc, int32_t* __restrict__ out_capused, uint64_t* __restrict__ out_elems) {
-  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < S_orig; i += gridDim.x * blockDim.x) {
-    const int e = list_exp[i];
-    const int b = e_off[e];
-    const int tok = list_tok[i];
-    const bool in_part = tok >= part_off && tok < part_off + Sp;
-    const bool last = (i == b + n_e[e] - 1);
-    if (!in_part && !last) continue;
-    int before = 0;
-    for (int j = b; j < i; ++j) {
-      const int t = list_tok[j];
-      before += (keep[j] && t >= part_off && t < part_off + Sp) ? 1 : 0;
+constexpr int kBprThreads = 1024;
+
+// Inclusive block scan of one int per thread (1024 threads); returns the inclusive prefix, *total = block sum.
+__device__ __forceinline__ int bpr_block_scan(int v, int* warp_sums, int* total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int x = v;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const int y = __shfl_up_sync(0xffffffffu, x, d);
+    if (lane >= d) x += y;
+  }
+  __syncthreads();   // warp_sums may still be read from the previous call
+  if (lane == 31) warp_sums[warp] = x;
+  __syncthreads();
+  if (warp == 0) {
+    int w = warp_sums[lane];
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int y = __shfl_up_sync(0xffffffffu, w, d);
+      if (lane >= d) w += y;
     }
-    const bool mine = keep[i] && in_part;
+    warp_sums[lane] = w;
+  }
+  __syncthreads();
+  *total = warp_sums[31];
+  return x + (warp > 0 ? warp_sums[warp - 1] : 0);
+}
+
+// One block per expert.  Its bucket (the tokens that chose it, in token order) keeps the C tokens with the largest
+// gate, an equal gate earlier in the batch first:
+//   1. radix select, four rounds of 8 bits over the order-preserving keys, finds the key T of the C-th kept token and
+//      how many tokens with exactly that key are kept (the first `need_eq` of them in token order);
+//   2. one pass in token order decides keep = key > T, or key == T and fewer than need_eq equal keys came before, and
+//      gives every kept token of partition `partition_id` its location = kept tokens of the partition before it.
+// Work per bucket is about five passes over its tokens (the earlier form compared every pair of tokens of a bucket).
+__global__ void __launch_bounds__(kBprThreads)
+bpr_select_locate_kernel(const float* __restrict__ list_gate, const int32_t* __restrict__ list_tok,
+                         const int32_t* __restrict__ e_off, const int32_t* __restrict__ n_e, int Sp, int part_off, int C, int M,
+                         void* __restrict__ gates_out, int gates_dtype, int32_t* __restrict__ idx_loc,
+                         int32_t* __restrict__ out_capused, uint64_t* __restrict__ out_elems) {
+  __shared__ int hist[256];
+  __shared__ int warp_sums[32];
+  __shared__ uint32_t s_prefix;
+  __shared__ int s_need;
+  const int e = blockIdx.x;
+  const int b = e_off[e], n = n_e[e];
+  const float* g = list_gate + b;
+  const int32_t* tok = list_tok + b;
+  // ---- 1. threshold key ----
+  uint32_t T = 0;           // keys >= T ... all kept when the bucket is not over capacity
+  int need_eq = n;          // how many tokens with key == T are kept
+  bool select = n > C;
+  if (select && C == 0) {
+    T = 0xffffffffu;
+    need_eq = 0;
+    select = false;
+  }
+  if (select) {
+    if (threadIdx.x == 0) { s_prefix = 0; s_need = C; }
+    __syncthreads();
+    for (int shift = 24; shift >= 0; shift -= 8) {
+      for (int i = threadIdx.x; i < 256; i += kBprThreads) hist[i] = 0;
+      __syncthreads();
+      const uint32_t prefix = s_prefix;
+      const uint32_t mask = shift == 24 ? 0u : (0xffffffffu << (shift + 8));
+      for (int i = threadIdx.x; i < n; i += kBprThreads) {
+        const uint32_t k = bpr_key(g[i]);
+        if ((k & mask) == prefix) atomicAdd(&hist[(k >> shift) & 255], 1);
+      }
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        int need = s_need, d = 255;
+        for (; d > 0; --d) {              // from the largest digit down: where does the need-th token fall
+          if (hist[d] >= need) break;
+          need -= hist[d];
+        }
+        s_prefix = prefix | ((uint32_t)d << shift);
+        s_need = need;
+      }
+      __syncthreads();
+    }
+    T = s_prefix;
+    need_eq = s_need;
+  }
+  // ---- 2. keep decisions and locations, in token order ----
+  int carry_eq = 0, carry_loc = 0;
+  for (int base = 0; base < n; base += kBprThreads) {
+    const int i = base + threadIdx.x;
+    const bool valid = i < n;
+    uint32_t k = 0;
+    int t = 0;
+    float gv = 0.f;
+    if (valid) {
+      gv = g[i];
+      k = bpr_key(gv);
+      t = tok[i];
+    }
+    const bool is_eq = valid && k == T;
+    int tot_eq;
+    const int eq_incl = bpr_block_scan(is_eq ? 1 : 0, warp_sums, &tot_eq);
+    const bool keep = valid && (k > T || (is_eq && carry_eq + eq_incl - 1 < need_eq));
+    const bool in_part = valid && t >= part_off && t < part_off + Sp;
+    int tot_loc;
+    const int loc_incl = bpr_block_scan((keep && in_part) ? 1 : 0, warp_sums, &tot_loc);
     if (in_part) {
-      const int s = tok - part_off;
+      const int s = t - part_off;
+      const bool mine = keep;
       idx_loc[s] = mine ? e : -1;
-      idx_loc[Sp + s] = mine ? before : -1;
-      store_from_float(gates_out, gates_dtype, s, list_gate[i]);
+      idx_loc[Sp + s] = mine ? carry_loc + loc_incl - 1 : -1;
+      store_from_float(gates_out, gates_dtype, s, gv);
     }
-    if (last) {  // the last token of a bucket knows the bucket's kept count in this partition
-      int cnt = before + (mine ? 1 : 0);
-      if (cnt > C) cnt = C;
-      out_capused[e] = cnt;
-      out_elems[e] = (uint64_t)cnt * (uint64_t)M;
-    }
+    carry_eq += tot_eq;
+    carry_loc += tot_loc;
+  }
+  if (threadIdx.x == 0) {
+    const int cnt = carry_loc > C ? C : carry_loc;
+    out_capused[e] = cnt;
+    out_elems[e] = (uint64_t)cnt * (uint64_t)M;
   }
 }
 
@@ -150,18 +228,15 @@ int lancet_moe_gate_bpr(const void* gate, int gate_dtype, int S_orig, int E, int
   int32_t* ltok = reinterpret_cast<int32_t*>(w + L.ltok);
   int32_t* lexp = reinterpret_cast<int32_t*>(w + L.lexp);
   int32_t* eoff = reinterpret_cast<int32_t*>(w + L.eoff);
-  unsigned char* keep = reinterpret_cast<unsigned char*>(w + L.keep);
   long long blocks = ((long long)S_orig + 255) / 256;
   const long long cap = (long long)sm_count() * 8;
   if (blocks > cap) blocks = cap;
   bpr_bucket_kernel<<<(int)blocks, 256, (size_t)E * sizeof(int), st>>>(il_all, gates_all, n_e, S_orig, E, lgate, ltok, lexp, eoff);
   if (int s = launch_status("bpr_bucket_kernel")) return s;
-  bpr_rank_kernel<<<(int)blocks, 256, 0, st>>>(lgate, lexp, eoff, n_e, S_orig, C, keep);
-  if (int s = launch_status("bpr_rank_kernel")) return s;
   const int Sp = S_orig / n_partitions;
-  bpr_locate_kernel<<<(int)blocks, 256, 0, st>>>(lgate, ltok, lexp, eoff, n_e, keep, S_orig, Sp, Sp * partition_id, C, M,
-                                                 out_gates_s, gates_dtype, out_idx_loc, out_capused, out_elems);
-  return launch_status("bpr_locate_kernel");
+  bpr_select_locate_kernel<<<E, kBprThreads, 0, st>>>(lgate, ltok, eoff, n_e, Sp, Sp * partition_id, C, M, out_gates_s, gates_dtype,
+                                                      out_idx_loc, out_capused, out_elems);
+  return launch_status("bpr_select_locate_kernel");
 }
 
 int lancet_moe_encode_bpr(const void* x, const void* gate, int gate_dtype, int n_partitions, int partition_id,

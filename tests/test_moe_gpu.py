@@ -317,14 +317,16 @@ def test_redispatch_expert_input():
 
 @pytest.mark.parametrize("S,E,M,n,cf,dt", [(1024, 32, 128, 1, 1.0, "f32"), (2048, 64, 128, 1, 1.0, "f32"),
                                            (2048, 32, 16, 2, 2.0, "f32"), (2048, 64, 8, 4, 4.0, "f16"),
-                                           (999, 3, 8, 1, 1.0, "f32"), (1200, 8, 8, 3, 1.5, "f32")])
+                                           (999, 3, 8, 1, 1.0, "f32"), (1200, 8, 8, 3, 1.5, "f32"),
+                                           (65536, 2, 8, 4, 0.5, "f32"),     # two large buckets, half of the tokens dropped
+                                           (40000, 5, 8, 1, 0.25, "f16")])
 def test_batch_prioritized_routing(S, E, M, n, cf, dt):
     """Shapes of tests/python/op/cuda/test_cuda_moe.py:160-327 of the reference (gate ~ U[0,1), seed 0),
     plus ragged ones and a case with many ties."""
     rng = np.random.default_rng(0)
     x = torch.from_numpy(rng.standard_normal((S, M)).astype(np.float32)).to(TDT[dt])
     gate = rng.random((S, E), dtype=np.float32)
-    if S == 999:
+    if S in (999, 40000):
         gate = np.round(gate * 4) / 4                # heavy ties: resolved towards the lower token index
     x_np = x.float().numpy() if dt != "f32" else x.numpy()
     for pid in range(n):
