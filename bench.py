@@ -642,7 +642,7 @@ def run_moe(args):
             torch.cuda.empty_cache()
             workloads["ffn"] = leg_ffn(args, ctx, steps=10)
             torch.cuda.empty_cache()
-        workloads["layer"] = leg_layer(args, ctx, steps=10)
+        workloads["layer"] = leg_layer(args, ctx, steps=20)
         if peer is not None:
             workloads["peerbw"] = peer
     else:
