@@ -425,9 +425,11 @@ int lancet_gate_softmax_bwd(const float* probs, const float* dprobs, const float
  * grouped GEMM (0 = no cap).  Process-wide; change it between steps, not while launches are being issued
  * from another thread. */
 int lancet_set_cta_limits(int exchange_ctas, int gemm_ctas);
-/* Grouped GEMM: 1 (default) = two CTAs of a cluster share a 256 x 256 tile (tcgen05 cta_group::2) whenever the
- * shape allows it, 0 = always the single-CTA 128 x 256 form.  Same results bit for bit; for A/B timing. */
-int lancet_set_gemm_paired(int on);
+/* Grouped GEMM form, for A/B timing (same results bit for bit).  Bit 0: 1 (default) = two CTAs of a cluster share a
+ * 256 x 256 tile (tcgen05 cta_group::2) whenever the shape allows it, 0 = always the single-CTA 128 x 256 form.
+ * Bit 1: 0 (default) = the tile walk visits all (source, expert) groups of one expert before the next expert's, so
+ * that an expert's weights stay in L2; 1 = groups in index order. */
+int lancet_set_gemm_paired(int mode);
 /* cudaMemcpyAsync(dst, src, bytes) with the kind inferred from the pointers; dst or src may be a peer
  * mapping from lancet_symm_open (copy-engine transfer over NVLink; the bandwidth yardstick of bench.py). */
 int lancet_peer_copy(void* dst, const void* src, size_t bytes, lancet_stream_t stream);

@@ -68,7 +68,8 @@ int sm_count() {
 }
 
 static int g_exchange_ctas = 0, g_gemm_ctas = 0, g_gemm_paired = 1;
-bool gemm_paired_enabled() { return __atomic_load_n(&g_gemm_paired, __ATOMIC_RELAXED) != 0; }
+bool gemm_paired_enabled() { return (__atomic_load_n(&g_gemm_paired, __ATOMIC_RELAXED) & 1) != 0; }
+int gemm_option(int bit) { return (__atomic_load_n(&g_gemm_paired, __ATOMIC_RELAXED) >> bit) & 1; }
 int exchange_cta_limit() { return __atomic_load_n(&g_exchange_ctas, __ATOMIC_RELAXED); }
 int gemm_cta_limit() { return __atomic_load_n(&g_gemm_ctas, __ATOMIC_RELAXED); }
 
@@ -83,7 +84,7 @@ int lancet_set_cta_limits(int exchange_ctas, int gemm_ctas) {
 }
 
 int lancet_set_gemm_paired(int on) {
-  __atomic_store_n(&lancet::g_gemm_paired, on ? 1 : 0, __ATOMIC_RELAXED);
+  __atomic_store_n(&lancet::g_gemm_paired, on, __ATOMIC_RELAXED);
   return LANCET_OK;
 }
 

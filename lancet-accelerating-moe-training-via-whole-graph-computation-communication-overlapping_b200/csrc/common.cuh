@@ -66,6 +66,7 @@ int sm_count();
 // 0 = no cap.  A schedule that runs an exchange stage next to a GEMM gives each a share of the SMs with them.
 int exchange_cta_limit();
 int gemm_cta_limit();
+int gemm_option(int bit);      // experiment switches, bit >= 1 of the value given to lancet_set_gemm_paired
 bool gemm_paired_enabled();   // lancet_set_gemm_paired: the two-CTA form of the grouped GEMM (default on)
 
 template <typename T>

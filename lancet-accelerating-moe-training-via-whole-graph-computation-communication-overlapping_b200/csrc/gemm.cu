@@ -66,6 +66,7 @@ struct Params {
   int Mout;               // MODE_REDUCE: output rows per expert
   int m_tiles, n_tiles, tiles_per_group, total_tiles;
   int band;               // MODE_ROWS: m-units per band of the tile order
+  int expert_major;       // MODE_ROWS: walk all groups of an expert before the next expert's
   const int32_t* counts;  // [groups] live rows (end of the row window), or null
   const int32_t* row_lo;  // [groups] first row of the window (rounded down to a tile boundary), or null; MODE_ROWS only
   int interleaved;        // MODE_ROWS: A, D and preact are [C][groups][.] (row c of group g at c * groups + g) instead of [groups][C][.]
@@ -289,10 +290,18 @@ __device__ __forceinline__ int group_row_blocks(const Params& p, int g) {
 // (group, band of p.band m-units, n-tile, m-unit in band) so that a band of A stays in L2 against a sweep of B.
 // An m-unit is one 128-row tile, or in the paired form two consecutive ones (the second may lie past the live rows).
 struct Sched {
-  const int* pref;  // [groups + 1] exclusive prefix of live m-units
-  const int* lo;    // [groups] first live m-tile
-  int g;            // group of the previous tile of this walker (tile indices only grow)
+  const int* pref;  // [groups + 1] exclusive prefix of live m-units, by position in the walk
+  const int* lo;    // [groups] first live m-tile, by position
+  int g;            // position of the previous tile of this walker (tile indices only grow)
 };
+
+// The walk visits all groups of one expert before the next expert's (group index = source * LE + expert), so that
+// an expert's weights are fetched from DRAM once and stay in L2 while every source's rows are multiplied with them.
+__device__ __forceinline__ int group_at(const Params& p, int pos) {
+  if (!p.expert_major) return pos;
+  const int per = p.groups / p.LE;
+  return (pos % per) * p.LE + pos / per;
+}
 
 template <int MODE>
 __device__ __forceinline__ int live_tiles(const Params& p, const Sched& sc) {
@@ -323,7 +332,7 @@ __device__ __forceinline__ Tile decode_tile(const Params& p, Sched& sc, int t, i
   int g = sc.g;
   while (t >= sc.pref[g + 1] * p.n_tiles) ++g;
   sc.g = g;
-  tl.group = g;
+  tl.group = group_at(p, g);
   int r = t - sc.pref[g] * p.n_tiles;
   const int nm = sc.pref[g + 1] - sc.pref[g];
   const int band_tiles = p.band * p.n_tiles;
@@ -335,7 +344,7 @@ __device__ __forceinline__ Tile decode_tile(const Params& p, Sched& sc, int t, i
   tl.mt = sc.lo[g] + (CTA2 ? 2 * mu + rank : mu);
   int rows = p.C;
   if (p.counts) {
-    rows = p.counts[g];
+    rows = p.counts[tl.group];
     rows = rows < 0 ? 0 : (rows > p.C ? p.C : rows);
   }
   tl.rows = rows;
@@ -395,16 +404,17 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     // live m-units of every group and their exclusive prefix (warp scan, 32 groups a round)
     int carry = 0;
     for (int base = 0; base < p.groups; base += 32) {
-      const int g = base + lane;
+      const int g = base + lane;            // position in the walk
       int lo = 0, nm = 0;
       if (g < p.groups) {
+        const int grp = group_at(p, g);
         int rows = p.C;
         if (p.counts) {
-          rows = p.counts[g];
+          rows = p.counts[grp];
           rows = rows < 0 ? 0 : (rows > p.C ? p.C : rows);
         }
         if (p.row_lo) {
-          lo = p.row_lo[g];
+          lo = p.row_lo[grp];
           lo = (lo < 0 ? 0 : lo) / BM;
         }
         nm = (rows + BM - 1) / BM - lo;
@@ -910,6 +920,7 @@ static int rows_common(const char* fn, const void* A, const void* B, void* D, in
                  LANCET_ERR_INVALID, "%s: row counts exceed 2^31", fn);
   p->groups = groups; p->LE = LE; p->C = C; p->N = N; p->K = K; p->Mout = 0;
   p->paired = gemm_paired_enabled() ? 1 : 0;
+  p->expert_major = gemm_option(1) ? 0 : 1;
   p->m_tiles = (C + BM - 1) / BM;
   if (p->paired) p->m_tiles = (p->m_tiles + 1) / 2;
   p->n_tiles = N / BN;
@@ -1008,6 +1019,7 @@ int lancet_grouped_gemm_tn(const void* A, const void* B, void* D, int groups, in
   p.tiles_per_group = p.m_tiles * p.n_tiles;
   p.total_tiles = p.tiles_per_group * LE;
   p.band = 1;
+  p.expert_major = 0;
   p.counts = counts; p.row_lo = nullptr; p.interleaved = 0; p.bias = nullptr; p.D = D; p.preact = nullptr; p.act = 0;
   p.epi = EPI_ACT;
   p.status = status;
