@@ -191,14 +191,16 @@ class NvlinkCounter:
 
     def __init__(self, index):
         self.h = None
+        self.why = None
         try:
             import pynvml
             pynvml.nvmlInit()
             self.nv = pynvml
             self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
             self.read()
-        except Exception:
+        except Exception as e:
             self.h = None
+            self.why = "NVML unavailable: %s" % e
 
     def read(self):
         if self.h is None:
@@ -208,10 +210,12 @@ class NvlinkCounter:
             out = []
             for v in vals:
                 if v.nvmlReturn != 0:
+                    self.why = "NVML field %d: return code %d" % (v.fieldId, v.nvmlReturn)
                     return None
                 out.append(int(v.value.ullVal) * 1024)
             return tuple(out)
-        except Exception:
+        except Exception as e:
+            self.why = "NVML field query failed: %s" % e
             return None
 
 
@@ -624,7 +628,9 @@ def run_moe(args):
             plan.dispatch(xs[i % 2], gates[i % 2])
         ctx.sync()
         c1 = nvc.read()
-        if c0 is not None and c1 is not None:
+        if c0 is None or c1 is None:
+            nv_traffic = {"tx_bytes_per_launch": None, "rx_bytes_per_launch": None, "source": nvc.why}
+        else:
             nv_traffic = {"tx_bytes_per_launch": (c1[0] - c0[0]) / n_iter, "rx_bytes_per_launch": (c1[1] - c0[1]) / n_iter,
                           "source": "NVML NVLink data throughput counters of GPU %d over %d dispatch launches" % (ctx.local_rank, n_iter)}
     cap_all = plan.capused.cpu().numpy()
@@ -682,7 +688,7 @@ def run_moe(args):
                          "peak_kind": ("measured in this run: all ranks to all peers, best of copy engines and store kernel"
                                        if peer else "earlier peer-copy measurement"),
                          "frac_of_nominal_900": nv / NVLINK_NOMINAL_GBS, "bytes_per_launch": nv_bytes, "hbm_achieved": achieved,
-                         "traffic": nv_traffic["tx_bytes_per_launch"] if nv_traffic else None,
+                         "traffic": nv_traffic["tx_bytes_per_launch"] if nv_traffic else None,   # NVLink bytes sent per launch (NVML)
                          "traffic_detail": nv_traffic})
         if world == 1:
             # dram read + write bytes per launch from the ncu capture of this workload

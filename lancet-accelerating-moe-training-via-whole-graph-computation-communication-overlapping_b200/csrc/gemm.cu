@@ -744,28 +744,57 @@ __global__ void nelements_to_rows_kernel(const uint64_t* __restrict__ nelem, int
 
 // Bias gradient of an expert layer: db[e][n] = sum over the groups g of expert e and their live rows r of dY[g][r][n].
 // Two deterministic stages: partial sums over row slices, then a sum over the slices in fixed order.
-constexpr int kColsumSplits = 64;
+// Stage 1: a block owns 256 columns (8 per lane, 16-byte loads) and one row slice; each of its 8 warps walks its rows
+// four at a time (four independent 16-byte loads in flight per lane), the warps' sums are added in warp order.
+constexpr int kColsumSplits = 32;
+constexpr int kColsumCols = 256;
 template <typename T>
 __global__ void __launch_bounds__(256)
 colsum_partial_kernel(const T* __restrict__ dY, const int32_t* __restrict__ counts, int groups, int LE, int C, int N,
                       float* __restrict__ partial) {
-  __shared__ float red[4][64];
-  const int col = blockIdx.x * 64 + (threadIdx.x & 63);
-  const int lane_r = threadIdx.x >> 6;            // 4 row lanes
+  __shared__ float red[8][kColsumCols];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int col = blockIdx.x * kColsumCols + lane * 8;
   const int split = blockIdx.y, e = blockIdx.z;
-  float acc = 0.f;
-  if (col < N) {
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+  if (col < N) {   // N is a multiple of 8 here: a lane's 8 columns are all inside or all outside
+    const int stride = kColsumSplits * 8;
     for (int g = e; g < groups; g += LE) {
       int rows = counts ? counts[g] : C;
       rows = rows < 0 ? 0 : (rows > C ? C : rows);
       const T* base = dY + (size_t)g * C * N + col;
-      for (int r = split * 4 + lane_r; r < rows; r += kColsumSplits * 4) acc += Num<T>::to_f(base[(size_t)r * N]);
+      int r = split * 8 + warp;
+      for (; r + 3 * stride < rows; r += 4 * stride) {
+        uint4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) v[u] = __ldcs(reinterpret_cast<const uint4*>(base + (size_t)(r + u * stride) * N));
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const T* h = reinterpret_cast<const T*>(&v[u]);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[i] += Num<T>::to_f(h[i]);
+        }
+      }
+      for (; r < rows; r += stride) {
+        const uint4 v = __ldcs(reinterpret_cast<const uint4*>(base + (size_t)r * N));
+        const T* h = reinterpret_cast<const T*>(&v);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] += Num<T>::to_f(h[i]);
+      }
     }
   }
-  red[lane_r][threadIdx.x & 63] = acc;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) red[warp][lane * 8 + i] = acc[i];
   __syncthreads();
-  if (lane_r == 0 && col < N)
-    partial[((size_t)e * kColsumSplits + split) * N + col] = (red[0][threadIdx.x] + red[1][threadIdx.x]) + (red[2][threadIdx.x] + red[3][threadIdx.x]);
+  const int c = blockIdx.x * kColsumCols + threadIdx.x;
+  if (c < N) {
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) t += red[w][threadIdx.x];
+    partial[((size_t)e * kColsumSplits + split) * N + c] = t;
+  }
 }
 
 template <typename T>
@@ -1089,7 +1118,9 @@ int lancet_grouped_bias_grad(const void* dY, void* db, int groups, int LE, int C
                  "lancet_grouped_bias_grad: workspace too small");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   float* partial = static_cast<float*>(ws);
-  const dim3 grid1((N + 63) / 64, kColsumSplits, LE);
+  LANCET_REQUIRE(N % 8 == 0 && aligned(dY, 16), LANCET_ERR_INVALID,
+                 "lancet_grouped_bias_grad: N=%d must be a multiple of 8 and dY 16-byte aligned", N);
+  const dim3 grid1((N + kColsumCols - 1) / kColsumCols, kColsumSplits, LE);
   const int grid2 = (LE * N + 255) / 256;
   if (dtype == LANCET_BF16) {
     colsum_partial_kernel<__nv_bfloat16><<<grid1, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(dY), counts, groups, LE, C, N, partial);

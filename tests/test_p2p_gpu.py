@@ -170,3 +170,37 @@ def test_peer_dispatch_rejects_unaligned_rows():
         plan.dispatch(x, gate)
     assert ei.value.code == 1 and "16 bytes" in str(ei.value)
     torch.cuda.synchronize()
+
+
+def test_cta_limits_and_peer_copy():
+    """Grid caps change how many CTAs run, never the result; lancet_peer_copy is a plain asynchronous copy."""
+    import ctypes
+    from lancet_b200 import _capi
+    L = _capi.lib()
+    W, n = 2, 1 << 16
+    shared = {}
+    ops = [LB.SymmAllToAll(n * 4, DEV, fabric=LB.LocalFabric(W, r, shared)) for r in range(W)]
+    xs = [torch.randn((W, n // W), device=DEV) for _ in range(W)]
+    outs = []
+    try:
+        for cap in (0, 3, 1000):
+            _capi.check(L.lancet_set_cta_limits(cap, 0))
+            for r in range(W):
+                ops[r].recv_view(xs[r]).zero_()
+            for r in range(W):
+                ops[r].send(xs[r])
+            torch.cuda.synchronize()
+            outs.append([ops[r].recv_view(xs[r]).clone() for r in range(W)])
+    finally:
+        _capi.check(L.lancet_set_cta_limits(0, 0))
+    for o in outs[1:]:
+        for a, b in zip(o, outs[0]):
+            assert torch.equal(a, b)
+    assert L.lancet_set_cta_limits(-1, 0) == 1
+    src = torch.randn(1000, device=DEV)
+    dst = torch.zeros(1000, device=DEV)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    _capi.check(L.lancet_peer_copy(ctypes.c_void_p(dst.data_ptr()), ctypes.c_void_p(src.data_ptr()), 4000, stream))
+    torch.cuda.synchronize()
+    assert torch.equal(src, dst)
+    assert L.lancet_peer_copy(None, ctypes.c_void_p(src.data_ptr()), 16, stream) == 2
