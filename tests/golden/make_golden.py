@@ -18,6 +18,8 @@ Two more families:
     profile hook, so every stored vector was computed by the reference's code.  For the
     small cases the dense dispatch and combine einsums of MOELayer.forward (:476-478,
     :512-514) are stored too.
+  * top2chain_ref_*.npz: `top2gating` called on each of n consecutive token chunks (choices, locations before
+    the capacity mask, probabilities per chunk), for checking the chained top-2 gate chunk by chunk.
   * chain_ref_*.npz: FakeMoeEncodeOp called on consecutive token chunks with each
     call's used capacity fed to the next one, the way the partition pass chains field 2
     of moe_encode (src/pass/dist_optimization/partition_exprs.cc:1784-1792).  With a
@@ -169,6 +171,31 @@ def run_top2_case(sm, name, S, E, M, cf, seed, dense, spread=0.0):
     print("top2", name, "C", rec["C"], "dropped", int((rec["kept1"] == 0).sum()), int((rec["kept2"] == 0).sum()))
 
 
+def run_top2_chain_case(sm, name, S, E, n, seed, spread):
+    """The reference's top-2 gate on each of n consecutive token chunks: per chunk its choices, its locations before the
+    capacity mask and its gate probabilities.  The reference has no chained top-2 operator; a test combines these
+    per-chunk vectors with the CUDA operator's chaining rules (tutel_moe_dispatch.cu:199-201, :207-209)."""
+    g = torch.Generator().manual_seed(seed)
+    logits = torch.randn(S, E, generator=g) + spread * torch.linspace(-1.0, 1.0, E)
+    Sp = S // n
+    rows = torch.arange(Sp)
+    rec = dict(S=S, E=E, n=n, seed=seed, logits=logits.numpy())
+    idx1, idx2, l1, l2, gates = [], [], [], [], []
+    for c in range(n):
+        _, loc = call_with_locals(sm.top2gating, logits[c * Sp:(c + 1) * Sp], 1.0)
+        i1, i2 = loc["indices1_s"], loc["indices2_s"]
+        g_wo1 = loc["gates"].masked_fill(torch.nn.functional.one_hot(i1, E).bool(), float("-inf"))
+        assert torch.equal(torch.argmax(g_wo1, dim=1), i2), "softmax rounding tie: pick another seed"
+        idx1.append(i1.numpy().astype(np.int32))
+        idx2.append(i2.numpy().astype(np.int32))
+        l1.append(loc["locations1"][rows, i1].numpy().astype(np.int32))
+        l2.append(loc["locations2"][rows, i2].numpy().astype(np.int32))
+        gates.append(loc["gates"].numpy())
+    rec.update(idx1=np.stack(idx1), idx2=np.stack(idx2), loc1_all=np.stack(l1), loc2_all=np.stack(l2), gate=np.concatenate(gates))
+    np.savez_compressed(os.path.join(HERE, f"top2chain_ref_{name}.npz"), **rec)
+    print("top2chain", name, "chunks", n)
+
+
 def run_chain_case(ref, name, S, E, M, n, seed, first_used=None):
     """n consecutive chunks of S//n tokens through FakeMoeEncodeOp, used capacity chained.  `first_used` = "random"
     starts the chain from a used capacity drawn in [0, C] per expert (as left by earlier partitions) instead of zero."""
@@ -221,6 +248,8 @@ def main():
     run_top2_case(sm, "s512_e4", 512, 4, 8, 1.25, 12, dense=True)
     run_top2_case(sm, "rag_s193_e5", 193, 5, 4, 1.25, 13, dense=True, spread=0.6)
     run_top2_case(sm, "s256_e8_cf05", 256, 8, 4, 0.5, 14, dense=True)
+    run_top2_chain_case(sm, "s4096_e4_n4", 4096, 4, 4, 15, 0.5)
+    run_top2_chain_case(sm, "s2048_e16_n4", 2048, 16, 4, 16, 0.6)
 
 
 if __name__ == "__main__":

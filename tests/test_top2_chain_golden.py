@@ -14,6 +14,7 @@ from oracle import moe_oracle as O
 HERE = os.path.dirname(__file__)
 TOP2 = sorted(glob.glob(os.path.join(HERE, "golden", "top2_ref_*.npz")))
 CHAIN = sorted(glob.glob(os.path.join(HERE, "golden", "chain_ref_*.npz")))
+TOP2CHAIN = sorted(glob.glob(os.path.join(HERE, "golden", "top2chain_ref_*.npz")))
 ids = lambda p: os.path.basename(p)[:-4]
 
 
@@ -68,6 +69,56 @@ def test_oracle_chained_used_capacity_matches_reference_operator(path):
         used = cap
 
 
+def expected_top2_chain(rec, cf):
+    """What n chained top-2 encodes must give, assembled from the reference gate's per-chunk vectors (choices, locations
+    before the capacity mask, probabilities: docker/resources/sharded_moe.py:253-324) and the CUDA operator's chaining
+    rules: a choice is dropped when loc >= C - used[e] (tutel_moe_dispatch.cu:199-201), used[e] grows by the tokens routed
+    to e and saturates at C (:207-209), gates are g_j / clamp(sum of kept g, eps) (sharded_moe.py:306-312)."""
+    S, E, n = int(rec["S"]), int(rec["E"]), int(rec["n"])
+    Sp = S // n
+    C = O.capacity(Sp, E, cf * n, 2)
+    used = np.zeros(E, np.int64)
+    il = np.zeros((n, 4, Sp), np.int32)
+    gs = np.zeros((n, 2, Sp), np.float32)
+    chain = [used.copy()]
+    rows = np.arange(Sp)
+    for c in range(n):
+        gate = rec["gate"][c * Sp:(c + 1) * Sp]
+        raw, keep = [], []
+        for j, (idx, loc) in enumerate(((rec["idx1"][c], rec["loc1_all"][c]), (rec["idx2"][c], rec["loc2_all"][c]))):
+            k = loc < C - used[idx]
+            il[c, 2 * j] = np.where(k, idx, -1)
+            il[c, 2 * j + 1] = loc                       # per-call location; the shared-buffer row adds used[idx]
+            raw.append(np.where(k, gate[rows, idx], np.float32(0)).astype(np.float32))
+            keep.append(k)
+        denom = np.maximum(raw[0] + raw[1], np.float32(np.finfo(np.float32).eps)).astype(np.float32)
+        gs[c, 0], gs[c, 1] = raw[0] / denom, raw[1] / denom
+        cnt = np.bincount(rec["idx1"][c], minlength=E) + np.bincount(rec["idx2"][c], minlength=E)
+        base = used.copy()
+        used = np.minimum(used + cnt, C)
+        chain.append(used.copy())
+        il[c, 1] += base[rec["idx1"][c]].astype(np.int32)
+        il[c, 3] += base[rec["idx2"][c]].astype(np.int32)
+    return C, il, gs, np.stack(chain).astype(np.int32)
+
+
+@pytest.mark.parametrize("path", TOP2CHAIN, ids=ids)
+def test_oracle_chained_top2_matches_reference_gate_per_chunk(path):
+    rec = np.load(path)
+    S, E, n = int(rec["S"]), int(rec["E"]), int(rec["n"])
+    Sp = S // n
+    C, il, gs, chain = expected_top2_chain(rec, 0.5)       # a tight capacity: later chunks lose choices
+    assert (il[:, 0] < 0).any() and (il[:, 2] < 0).any() and (il[0, 0] >= 0).all()
+    used = np.zeros(E, np.int32)
+    for c in range(n):
+        g, l, cap, _ = O.moe_gate(rec["gate"][c * Sp:(c + 1) * Sp], used, C, 8, 2)
+        np.testing.assert_array_equal(l[0::2], il[c, 0::2])
+        np.testing.assert_array_equal(l[1::2] + np.where(True, used[np.stack([rec["idx1"][c], rec["idx2"][c]])], 0), il[c, 1::2])
+        np.testing.assert_array_equal(g, gs[c])
+        used = cap
+        np.testing.assert_array_equal(used, chain[c + 1])
+
+
 # ---- the same vectors against the CUDA kernels -----------------------------------------------------------------
 DEV = "cuda:0"
 
@@ -119,3 +170,21 @@ def test_gpu_chained_used_capacity_matches_reference_operator(path):
         base = np.take_along_axis(rec["used_in"], first, axis=1)
         np.testing.assert_array_equal(il[:, 1] - base, rec["idx_loc"][:, 1])
         np.testing.assert_array_equal(plan.gates_s.cpu().numpy().reshape(n, -1), rec["gates_s"])
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("path", TOP2CHAIN, ids=ids)
+@pytest.mark.parametrize("cf", [0.5, 1.25])
+def test_gpu_chained_top2_matches_reference_gate_per_chunk(path, cf):
+    """The configuration the headline benchmark runs (top-2, chained chunks, one launch for all chunks) against vectors
+    assembled from the reference gate's own per-chunk outputs."""
+    import lancet_b200 as LB
+    rec = np.load(path)
+    S, E, n = int(rec["S"]), int(rec["E"]), int(rec["n"])
+    C, il, gs, chain = expected_top2_chain(rec, cf)
+    plan = LB.ChunkedMoE(S, 8, E, 2, cf, n, torch.float16, device=DEV)
+    assert plan.C == C
+    plan.dispatch(torch.zeros((S, 8), dtype=torch.float16, device=DEV), cu(rec["gate"]))
+    np.testing.assert_array_equal(plan.idx_loc.cpu().numpy(), il)
+    np.testing.assert_array_equal(plan.gates_s.cpu().numpy(), gs)
+    np.testing.assert_array_equal(plan.capused.cpu().numpy(), chain)
