@@ -106,7 +106,21 @@ class LansTrainer:
         self.shared = [p for p in self.params if id(p) not in expert_ids]
         self.m = [torch.zeros_like(p) for p in self.params]
         self.v = [torch.zeros_like(p) for p in self.params]
-        self.grads = [torch.zeros_like(p) for p in self.params]
+        # gradients live in two flat buffers (replicated parameters, then this rank's experts): one all-reduce and one
+        # memset per step instead of a flatten / unflatten copy and a fill per tensor
+        def flat_views(ps):
+            sizes = [(p.numel() + 3) // 4 * 4 for p in ps]                 # keep every view 16-byte aligned
+            flat = torch.zeros(sum(sizes), dtype=torch.float32, device=self.device) if ps else None
+            views, off = [], 0
+            for p, n in zip(ps, sizes):
+                views.append(flat[off:off + p.numel()].view_as(p))
+                off += n
+            return flat, views
+        experts = [p for p in self.params if id(p) in expert_ids]
+        self.flat_shared, gs = flat_views(self.shared)
+        self.flat_expert, ge = flat_views(experts)
+        by_id = {id(p): g for p, g in zip(self.shared + experts, gs + ge)}
+        self.grads = [by_id[id(p)] for p in self.params]
         for p, g in zip(self.params, self.grads):
             p.grad = g
         self.state = LansState(self.grads, [p.data for p in self.params], self.m, self.v)
@@ -123,17 +137,14 @@ class LansTrainer:
         # the side stream must be complete before they are averaged and applied
         DeferredGrads.join(self.device if self.device.type == "cuda" else None)
         self.check_status()
-        if self.world > 1:
-            flat = torch._utils._flatten_dense_tensors([p.grad for p in self.shared])
-            torch.distributed.all_reduce(flat, group=self.group)
-            flat.div_(self.world)
-            for g, f in zip([p.grad for p in self.shared], torch._utils._unflatten_dense_tensors(flat, [p.grad for p in self.shared])):
-                g.copy_(f)
+        if self.world > 1 and self.flat_shared is not None:
+            torch.distributed.all_reduce(self.flat_shared, op=torch.distributed.ReduceOp.AVG, group=self.group)
         with torch.no_grad():
             lans(self.grads + [p.data for p in self.params] + self.m + self.v, self.step_no, learning_rate=self.lr,
                  state=self.state)
-        for g in self.grads:
-            g.zero_()
+        for flat in (self.flat_shared, self.flat_expert):
+            if flat is not None:
+                flat.zero_()
         return loss.detach()
 
     def check_status(self):
