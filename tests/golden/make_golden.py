@@ -144,8 +144,13 @@ def call_with_locals(fn, *args):
 def run_top2_case(sm, name, S, E, M, cf, seed, dense, spread=0.0):
     g = torch.Generator().manual_seed(seed)
     # `spread` tilts the logits towards the higher-numbered experts, so that their loads exceed the capacity and choices drop
-    logits = torch.randn(S, E, generator=g) + spread * torch.linspace(-1.0, 1.0, E)
+    logits = (torch.randn(S, E, generator=g) + spread * torch.linspace(-1.0, 1.0, E)).requires_grad_(True)
     (l_aux, combine, mask, exp_counts), loc = call_with_locals(sm.top2gating, logits, cf)
+    # gradient of the normalised gates with respect to the gate probabilities, by autograd through the reference's code
+    d_gs = torch.randn(2, S, generator=g)
+    (d_gate,) = torch.autograd.grad([loc["gates1_s"], loc["gates2_s"]], [loc["gates"]], [d_gs[0], d_gs[1]], retain_graph=True)
+    logits = logits.detach()
+    combine, loc = combine.detach(), {k: (v.detach() if torch.is_tensor(v) else v) for k, v in loc.items()}
     gates = loc["gates"]
     rows = torch.arange(S)
     i1, i2 = loc["indices1_s"], loc["indices2_s"]
@@ -160,6 +165,7 @@ def run_top2_case(sm, name, S, E, M, cf, seed, dense, spread=0.0):
         kept1=loc["mask1"].sum(dim=1).numpy().astype(np.int32), kept2=loc["mask2"].sum(dim=1).numpy().astype(np.int32),
         loc1_s=loc["locations1_s"].numpy().astype(np.int32), loc2_s=loc["locations2_s"].numpy().astype(np.int32),
         gates1_s=loc["gates1_s"].numpy(), gates2_s=loc["gates2_s"].numpy(), exp_counts=exp_counts.numpy().astype(np.int64),
+        d_gates_s=d_gs.numpy(), d_gate=d_gate.numpy(),
     )
     if dense:
         x = torch.randn(S, M, generator=g)

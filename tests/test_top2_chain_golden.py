@@ -52,6 +52,9 @@ def test_oracle_top2_matches_reference_gate(path):
         np.testing.assert_array_equal(disp, rec["disp"])          # 0/1 mask times x summed with zeros: exact
         out = O.moe_decode_fwd(rec["eo"], gs, il)
         np.testing.assert_allclose(out, rec["out"], rtol=1e-5, atol=1e-6)
+    # gradient of the normalised gates w.r.t. the gate probabilities: autograd through the reference's own code
+    dg = O.moe_encode_dg_top2(rec["d_gates_s"], il, rec["gate"], E)
+    np.testing.assert_allclose(dg, rec["d_gate"], rtol=1e-5, atol=1e-6 * float(np.abs(rec["d_gate"]).max()))
 
 
 @pytest.mark.parametrize("path", CHAIN, ids=ids)
@@ -136,6 +139,8 @@ def test_gpu_top2_matches_reference_gate(path):
     cap0 = torch.zeros(E, dtype=torch.int32, device=DEV)
     gs, il, cap, elems = LB.moe_gate(cu(rec["gate"]), cap0, C, M, k=2)
     check_top2(rec, gs.cpu().numpy().reshape(2, S), il.cpu().numpy(), cap.cpu().numpy())
+    dg = LB.moe_encode_dg(cu(rec["d_gates_s"]), il, E, gate=cu(rec["gate"]))
+    np.testing.assert_allclose(dg.cpu().numpy(), rec["d_gate"], rtol=1e-5, atol=1e-6 * float(np.abs(rec["d_gate"]).max()))
     if "x" in rec.files:
         g1, il1, cap1, el1, disp = LB.moe_encode(cu(rec["x"]), cu(rec["gate"]), cap0, float(rec["cf"]), k=2)
         assert tuple(disp.shape) == (E, C, M)
