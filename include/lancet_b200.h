@@ -259,9 +259,11 @@ int lancet_moe_dispatch_chunked_p2p(const void* x, const void* gate, int gate_dt
  * 2. lancet_moe_dispatch_rows_p2p scatters the rows of chunks [chunk_begin, chunk_end) (x [S][M] and
  *    idx_loc [n][2k][Sp] are the whole arrays); follow each stage with lancet_p2p_barrier.
  * 3. lancet_moe_stage_windows (on the owner, after the first barrier) turns its chain table into the row
- *    windows of every stage, row_begin / row_end int32 [n][W*LE], aligned to row_align rows (128 for the
- *    grouped GEMM): stage c covers the whole row_align-row tiles that have fully arrived with chunks 0..c and
- *    that earlier stages did not cover; the last stage ends at the total.  counts (nullable, int32 [W*LE])
+ *    windows of every stage, row_begin / row_end int32 [n][W*LE] (row_align = 128 for the grouped GEMM):
+ *    stage c ends at max(floor(chain[c+1] / row_align) * row_align, chain[c]), i.e. it covers the whole tiles that
+ *    have arrived with chunks 0..c and in any case every row of the chunks before c, whose tokens are combined
+ *    right after it; it begins at the tile that holds the previous stage's end (a tile left partial is computed
+ *    again, with the same values); the last stage ends at the total.  counts (nullable, int32 [W*LE])
  *    receives the totals.
  * Combine, its backward and the dispatch backward run per chunk through the existing calls on sub-arrays
  * (gates_s + c*k*Sp, idx_loc + c*2k*Sp, out + c*Sp*M, S = Sp, n_chunks = 1). */
@@ -279,14 +281,15 @@ int lancet_moe_dispatch_rows_p2p(const void* x, const int32_t* idx_loc, int S, i
  * ([(chunk_end-chunk_begin)*Sp][E]), starting from row chunk_begin of capused_chain (the chunks must be gated in
  * order), writes the usual slices of gates_s / idx_loc / capused_chain / elems and publishes the new chain rows to
  * the owners.  lancet_moe_stage_window gives the row window of ONE stage covering those chunks (row_begin / row_end
- * int32 [W*LE]) as soon as its barrier has been passed; counts is written when chunk_end == n_chunks.
+ * int32 [W*LE]; prev_chunk_begin = first chunk of the stage before it, ignored for the first stage) as soon as its
+ * barrier has been passed; counts is written when chunk_end == n_chunks.
  * Results are identical to the all-at-once calls. */
 int lancet_moe_gate_chunks_p2p(const void* gate_rows, int gate_dtype, float capacity_factor, int S, int M, int LE, int W,
                                int rank, int k, int n_chunks, int chunk_begin, int chunk_end, void* gates_s,
                                int32_t* idx_loc, int32_t* capused_chain, uint64_t* elems, void* const* peer_chain,
                                void* ws, size_t ws_bytes, lancet_stream_t stream);
-int lancet_moe_stage_window(const int32_t* chain, int W, int LE, int n_chunks, int row_align, int chunk_begin,
-                            int chunk_end, int32_t* row_begin, int32_t* row_end, int32_t* counts,
+int lancet_moe_stage_window(const int32_t* chain, int W, int LE, int n_chunks, int row_align, int prev_chunk_begin,
+                            int chunk_begin, int chunk_end, int32_t* row_begin, int32_t* row_end, int32_t* counts,
                             lancet_stream_t stream);
 int lancet_moe_stage_windows(const int32_t* chain, int W, int LE, int n_chunks, int row_align, int32_t* row_begin,
                              int32_t* row_end, int32_t* counts, lancet_stream_t stream);

@@ -143,8 +143,8 @@ SIGNATURES = {
     "lancet_moe_gate_chunks_p2p": (c_int, [c_void_p, c_int, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                            c_int, c_void_p, c_void_p, c_void_p, c_void_p, ctypes.POINTER(c_void_p), c_void_p,
                                            c_size_t, c_void_p]),
-    "lancet_moe_stage_window": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
-                                        c_void_p]),
+    "lancet_moe_stage_window": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                                        c_void_p, c_void_p]),
     "lancet_gate_softmax": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "lancet_gate_softmax_bwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                         c_void_p]),

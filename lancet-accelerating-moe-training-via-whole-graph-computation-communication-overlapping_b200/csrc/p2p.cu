@@ -292,8 +292,16 @@ __global__ void publish_chain_kernel(const int32_t* __restrict__ chain, PeerTabl
 }
 
 // Row windows of the pipeline stages on the owner's side.  Stage c may work on the rows of group g = (source, le)
-// that have arrived with chunks 0..c and form whole tiles of `align` rows: [begin, end) with
-// begin = floor(chain[c] / align) * align, end = floor(chain[c+1] / align) * align; the last stage ends at the total.
+// that have arrived with chunks 0..c and form whole tiles of `align` rows, and must cover every row of the chunks
+// before c (their tokens are combined right after stage c): end_c = max(floor(chain[c+1] / align) * align, chain[c]),
+// begin_c = the tile that holds end_{c-1} (a tile a stage leaves partial is computed again by the next one, with
+// the same values); the last stage ends at the total.
+__device__ __forceinline__ int stage_end(const int32_t* col, int LE, int n, int align, int c0, int c1) {
+  const int hi = col[(size_t)c1 * LE];
+  if (c1 == n) return hi;
+  const int lo = col[(size_t)c0 * LE], al = hi / align * align;
+  return al > lo ? al : lo;
+}
 __global__ void stage_windows_kernel(const int32_t* __restrict__ chain, int W, int LE, int n, int align,
                                      int32_t* __restrict__ row_begin, int32_t* __restrict__ row_end,
                                      int32_t* __restrict__ counts) {
@@ -302,25 +310,23 @@ __global__ void stage_windows_kernel(const int32_t* __restrict__ chain, int W, i
     const int c = i / G, g = i - c * G;
     const int src = g / LE, le = g - src * LE;
     const int32_t* col = chain + (size_t)src * n1 * LE + le;
-    const int lo = col[(size_t)c * LE], hi = col[(size_t)(c + 1) * LE];
-    row_begin[i] = c == 0 ? 0 : lo / align * align;
-    row_end[i] = c == n - 1 ? hi : hi / align * align;
+    row_begin[i] = c == 0 ? 0 : stage_end(col, LE, n, align, c - 1, c) / align * align;
+    row_end[i] = stage_end(col, LE, n, align, c, c + 1);
     if (c == 0 && counts) counts[g] = col[(size_t)n * LE];
   }
 }
 
 // The same for one stage that covers chunks [c0, c1), computable as soon as the chain entries up to c1 are known
 // (incremental gating: chunk c is gated, published and sent before chunk c+1 is gated).
-__global__ void stage_window_kernel(const int32_t* __restrict__ chain, int W, int LE, int n, int align, int c0, int c1,
+__global__ void stage_window_kernel(const int32_t* __restrict__ chain, int W, int LE, int n, int align, int prev_c0, int c0, int c1,
                                     int32_t* __restrict__ row_begin, int32_t* __restrict__ row_end, int32_t* __restrict__ counts) {
   const int G = W * LE, n1 = n + 1;
   for (int g = blockIdx.x * blockDim.x + threadIdx.x; g < G; g += gridDim.x * blockDim.x) {
     const int src = g / LE, le = g - src * LE;
     const int32_t* col = chain + (size_t)src * n1 * LE + le;
-    const int lo = col[(size_t)c0 * LE], hi = col[(size_t)c1 * LE];
-    row_begin[g] = c0 == 0 ? 0 : lo / align * align;
-    row_end[g] = c1 == n ? hi : hi / align * align;
-    if (c1 == n && counts) counts[g] = hi;
+    row_begin[g] = c0 == 0 ? 0 : stage_end(col, LE, n, align, prev_c0, c0) / align * align;
+    row_end[g] = stage_end(col, LE, n, align, c0, c1);
+    if (c1 == n && counts) counts[g] = col[(size_t)n * LE];
   }
 }
 
@@ -571,16 +577,18 @@ int lancet_moe_gate_chunks_p2p(const void* gate_rows, int gate_dtype, float capa
   return launch_status("publish_chain_kernel");
 }
 
-int lancet_moe_stage_window(const int32_t* chain, int W, int LE, int n_chunks, int row_align, int chunk_begin, int chunk_end,
-                            int32_t* row_begin, int32_t* row_end, int32_t* counts, lancet_stream_t stream) {
+int lancet_moe_stage_window(const int32_t* chain, int W, int LE, int n_chunks, int row_align, int prev_chunk_begin, int chunk_begin,
+                            int chunk_end, int32_t* row_begin, int32_t* row_end, int32_t* counts, lancet_stream_t stream) {
   LANCET_REQUIRE(W >= 1 && W <= kMaxPeers && LE >= 1 && n_chunks >= 1 && row_align >= 1, LANCET_ERR_INVALID,
                  "lancet_moe_stage_window: bad world %d / local experts %d / chunks %d / alignment %d", W, LE, n_chunks, row_align);
   LANCET_REQUIRE(chunk_begin >= 0 && chunk_begin < chunk_end && chunk_end <= n_chunks, LANCET_ERR_INVALID,
                  "lancet_moe_stage_window: bad chunk range [%d, %d) of %d", chunk_begin, chunk_end, n_chunks);
+  LANCET_REQUIRE(chunk_begin == 0 || (prev_chunk_begin >= 0 && prev_chunk_begin < chunk_begin), LANCET_ERR_INVALID,
+                 "lancet_moe_stage_window: the previous stage must start before chunk %d (got %d)", chunk_begin, prev_chunk_begin);
   LANCET_REQUIRE(chain && row_begin && row_end, LANCET_ERR_NULL, "lancet_moe_stage_window: null pointer argument");
   const int G = W * LE;
-  stage_window_kernel<<<(G + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(chain, W, LE, n_chunks, row_align, chunk_begin,
-                                                                                      chunk_end, row_begin, row_end, counts);
+  stage_window_kernel<<<(G + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      chain, W, LE, n_chunks, row_align, prev_chunk_begin, chunk_begin, chunk_end, row_begin, row_end, counts);
   return launch_status("stage_window_kernel");
 }
 

@@ -104,6 +104,8 @@ class LocalFabric:
 class DistChunkedMoE:
     """Chunk-chained top-k dispatch and combine with the all-to-all fused into the kernels."""
 
+    ROW_ALIGN = 128     # stage windows of the staged exchange end on whole tiles of the grouped GEMM
+
     def __init__(self, S, M, k=2, capacity_factor=1.25, n_chunks=4, dtype=torch.float16, device="cuda",
                  local_experts=2, fabric=None, group=None, timeout_s=5.0, remote_zero=False, train=False):
         self.device = torch.device(device)
@@ -243,11 +245,12 @@ class DistChunkedMoE:
         """Switch to the other set of receive buffers (stage_gate does this itself)."""
         self.parity ^= 1
 
-    def stage_window(self, slot, c0, c1):
-        """Row window of the stage covering chunks [c0, c1), valid once that stage's barrier has been passed.
-        Returns (row_begin, row_end) int32 [W*LE]; the last stage also fills the row totals."""
+    def stage_window(self, slot, c0, c1, prev_c0=-1):
+        """Row window of the stage covering chunks [c0, c1), valid once that stage's barrier has been passed; prev_c0 is
+        the first chunk of the stage before it.  Returns (row_begin, row_end) int32 [W*LE]; the last stage also fills
+        the row totals."""
         cnt = self.counts[self.parity]
-        check(_capi.lib().lancet_moe_stage_window(_ptr(self.chain[self.parity]), self.W, self.LE, self.n, 128, c0, c1,
+        check(_capi.lib().lancet_moe_stage_window(_ptr(self.chain[self.parity]), self.W, self.LE, self.n, self.ROW_ALIGN, prev_c0, c0, c1,
                                                   _ptr(self.swin_begin[slot]), _ptr(self.swin_end[slot]), _ptr(cnt),
                                                   _stream(cnt)))
         return self.swin_begin[slot], self.swin_end[slot]
@@ -272,7 +275,7 @@ class DistChunkedMoE:
         cnt = self.counts[self.parity]
         if buf is None:
             buf = self.recv[self.parity]
-            check(L.lancet_moe_stage_windows(_ptr(self.chain[self.parity]), self.W, self.LE, self.n, 128,
+            check(L.lancet_moe_stage_windows(_ptr(self.chain[self.parity]), self.W, self.LE, self.n, self.ROW_ALIGN,
                                              _ptr(self.win_begin), _ptr(self.win_end), _ptr(cnt), _stream(cnt)))
         check(L.lancet_moe_zero_tail(_ptr(buf), _ptr(cnt), self.M, self.C, self.W * self.LE, _DT[self.dtype], _stream(cnt)))
         return self.win_begin, self.win_end, cnt

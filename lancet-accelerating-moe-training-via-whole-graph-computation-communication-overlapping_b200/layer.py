@@ -91,6 +91,8 @@ class MoELayer:
     def fwd_prepare(self):
         self.win_begin, self.win_end, self.cnt = self.moe.stage_prepare()
         self._win = [(self.win_begin[c0], self.win_end[c1 - 1]) for c0, c1 in self.stage_chunks]
+        # (per-chunk windows: a stage of several chunks begins where its first chunk's window begins, which is at or
+        # before the tile holding the previous stage's end, and ends where its last chunk's window ends)
         self.x_e = self.moe.recv[self.moe.parity].view(self.G, self.C, self.M)
 
     def fwd_stage_experts_1(self, c):
@@ -196,7 +198,7 @@ class MoELayer:
         self._win = [None] * n
         for s in range(n):
             main.wait_event(arrived[s])
-            self._win[s] = moe.stage_window(s, *self.stage_chunks[s])
+            self._win[s] = moe.stage_window(s, *self.stage_chunks[s], prev_c0=self.stage_chunks[s - 1][0] if s else -1)
             if s == n - 1:
                 moe.zero_tail()          # the row totals are known with the last stage
             self.fwd_stage_experts_1(s)

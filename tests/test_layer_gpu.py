@@ -143,7 +143,9 @@ def _run_staged(layers, xs, gates, douts, n):
 
 
 @pytest.mark.parametrize("W,k,n,S,stages", [(2, 2, 4, 2048, None), (1, 2, 4, 4096, 2), (2, 1, 2, 1024, None),
-                                             (4, 2, 1, 512, None), (2, 2, 4, 1024, 1)])
+                                             (4, 2, 1, 512, None), (2, 2, 4, 1024, 1),
+                                             (2, 2, 8, 512, None),       # 64 tokens per chunk: blocks grow by less than a tile per chunk
+                                             (4, 1, 4, 256, 2)])
 def test_staged_pipeline_is_bit_identical(W, k, n, S, stages):
     """The staged exchange + row-window GEMMs give exactly the results of the unpipelined layer."""
     M, H, LE, cf = 256, 512, 2, 1.25
@@ -167,7 +169,7 @@ def test_staged_pipeline_is_bit_identical(W, k, n, S, stages):
         assert torch.equal(got[1][r][1], ref[1][r][1]), "dgates[%d]" % r
         for a, b, name in zip(got[2][r], ref[2][r], ("dw1", "dw2", "db1", "db2")):
             assert torch.equal(a, b), "%s[%d]" % (name, r)
-    # the windows equal the CPU restatement and tile the live rows of every block exactly once
+    # the windows equal the CPU restatement and cover the live rows of every block without gaps
     from oracle import moe_oracle as O
     for l in layers:
         ob, oe, oc = O.stage_windows(l.moe.chain[l.moe.parity].cpu().numpy(), 128)
@@ -175,7 +177,7 @@ def test_staged_pipeline_is_bit_identical(W, k, n, S, stages):
         assert (l.cnt.cpu().numpy() == oc).all()
         lo, hi, cnt = l.win_begin.cpu().numpy(), l.win_end.cpu().numpy(), l.cnt.cpu().numpy()
         assert (lo[0] == 0).all() and (hi[-1] == cnt).all()
-        assert (lo[1:] == hi[:-1]).all() and (lo % 128 == 0).all()
+        assert (lo[1:] == hi[:-1] // 128 * 128).all() and (lo % 128 == 0).all()
     assert int(LB.gemm_status(torch.device(DEV)).item()) == 0
 
 

@@ -209,7 +209,21 @@ def test_stage_windows_tile_every_block_once():
     chain = np.concatenate([np.zeros((W, 1, LE), np.int64), np.cumsum(steps, axis=1)], axis=1)
     b, e, cnt = O.stage_windows(chain, 128)
     assert (b[0] == 0).all() and (e[-1] == cnt).all() and (cnt == chain[:, n].reshape(-1)).all()
-    assert (b[1:] == e[:-1]).all() and (b % 128 == 0).all() and (e[:-1] % 128 == 0).all()
+    assert (b[1:] == e[:-1] // 128 * 128).all() and (b % 128 == 0).all()   # a stage starts at the tile holding the previous end
     for c in range(n - 1):
         assert (e[c] <= chain[:, c + 1].reshape(-1)).all()           # nothing that has not arrived yet
         assert (chain[:, c + 1].reshape(-1) - e[c] < 128).all()      # and every whole tile that has
+        assert (e[c] >= chain[:, c].reshape(-1)).all()               # and every row of the chunks before c
+        aligned = e[c] % 128 == 0
+        assert (aligned | (e[c] == chain[:, c].reshape(-1))).all()
+
+
+def test_stage_windows_complete_earlier_chunks_when_chunks_are_smaller_than_a_tile():
+    """A block that receives fewer rows than a tile per chunk: the combine of chunk c-1 follows stage c, so stage c must
+    end at or after the last row of chunk c-1 even when no further whole tile has arrived."""
+    chain = np.array([[[0], [100], [300], [350], [420]]])              # one source, one expert, 4 chunks
+    b, e, cnt = O.stage_windows(chain, 128)
+    np.testing.assert_array_equal(e[:, 0], [0, 256, 300, 420])         # stage 2: floor(350/128)*128 = 256 < 300 -> 300
+    np.testing.assert_array_equal(b[:, 0], [0, 0, 256, 256])           # stage 3 recomputes the tile stage 2 left partial
+    for c in range(1, 4):
+        assert e[c, 0] >= chain[0, c, 0]
