@@ -562,6 +562,17 @@ def run_moe(args):
     ctx.sync()
     k_ms, k_n = ctypes.c_double(0), ctypes.c_longlong(0)
     _capi.check(L.lancet_profile_end(ctypes.byref(k_ms), ctypes.byref(k_n)))
+    # the dominant kernel alone, launched back to back (no event pair around every launch): the duration without the
+    # bracket's launch gap.  The routing table of the last step is reused; the two input sets alternate (128 MiB read and
+    # 160 MiB written per pair of launches: more than the 126 MB L2)
+    b2b_us = None
+    if world == 1:
+        def scatter_burst():
+            for i in range(K):
+                plan.scatter(xs[i % 2])
+        scatter_burst()
+        ms_b2b, _ = timed_bursts(ctx, scatter_burst, K, target_s=0.1)
+        b2b_us = ms_b2b * 1e3
 
     # ---- end to end: pinned host inputs in, combined output back, every step ---------------------
     # Three streams, double-buffered device tensors: the host->device copy of step i+1 and the device->host copy
@@ -694,6 +705,9 @@ def run_moe(args):
             # dram read + write bytes per launch from the ncu capture of this workload
             # (profiles/moe_dispatch_combine_S16384_M2048_ncu_full.txt)
             roof["traffic"] = 177.2e6
+            if b2b_us:
+                roof["back_to_back_launch_us"] = b2b_us
+                roof["frac_back_to_back"] = bytes_per_launch / (b2b_us * 1e-6) / 1e9 / hbm_peak
     line = {
         "metric": "moe_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K,
         "warmup": warm, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",

@@ -165,6 +165,11 @@ int lancet_moe_dispatch_chunked(const void* x, const void* gate, int gate_dtype,
                                 int32_t* idx_loc, int32_t* capused_chain, uint64_t* elems, void* dispatched,
                                 void* ws, size_t ws_bytes, lancet_stream_t stream);
 /* Combine for outputs of lancet_moe_dispatch_chunked: out [S,M]. */
+/* The scatter of lancet_moe_dispatch_chunked alone, for a table that is already gated (idx_loc [n][2k][Sp] with
+ * shared-buffer rows, capused_chain [n+1][E] as that call wrote them): moves another [S,M] tensor with the same routing,
+ * the role of a second launch_encode_forward on the same indices_locations (kernel_util.cuh:36-39). */
+int lancet_moe_scatter_chunked(const void* x, const int32_t* idx_loc, const int32_t* capused_chain, void* dispatched,
+                               int S, int M, int C, int E, int k, int n_chunks, int dtype, lancet_stream_t stream);
 int lancet_moe_combine_chunked(const void* expert_out, const void* gates_s, int gates_dtype,
                                const int32_t* idx_loc, int S, int M, int C, int E, int k, int n_chunks, int dtype,
                                void* out, lancet_stream_t stream);

@@ -65,6 +65,8 @@ SIGNATURES = {
     "lancet_moe_dispatch_chunked": (c_int, [c_void_p, c_void_p, c_int, c_float, c_int, c_int, c_int, c_int, c_int, c_int,
                                             c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t,
                                             c_void_p]),
+    "lancet_moe_scatter_chunked": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                           c_void_p]),
     "lancet_moe_combine_chunked": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                            c_int, c_void_p, c_void_p]),
     "lancet_symm_alloc": (c_int, [c_size_t, ctypes.POINTER(c_void_p), ctypes.c_char_p]),

@@ -50,6 +50,21 @@ int lancet_moe_dispatch_chunked(const void* x, const void* gate, int gate_dtype,
                          dtype, 0, st);
 }
 
+int lancet_moe_scatter_chunked(const void* x, const int32_t* idx_loc, const int32_t* capused_chain, void* dispatched, int S,
+                               int M, int C, int E, int k, int n_chunks, int dtype, lancet_stream_t stream) {
+  LANCET_REQUIRE(n_chunks >= 1 && S >= 0 && S % n_chunks == 0, LANCET_ERR_INVALID,
+                 "lancet_moe_scatter_chunked: S=%d is not divisible into %d chunks", S, n_chunks);
+  LANCET_REQUIRE((k == 1 || k == 2) && E >= k && M >= 0 && C >= 0 && (long long)E * C < (1ll << 31) && valid_dtype(dtype),
+                 LANCET_ERR_INVALID, "lancet_moe_scatter_chunked: bad sizes E=%d k=%d M=%d C=%d or dtype", E, k, M, C);
+  if ((size_t)E * C * M == 0) return LANCET_OK;
+  LANCET_REQUIRE(capused_chain && dispatched && (S == 0 || (x && idx_loc)), LANCET_ERR_NULL,
+                 "lancet_moe_scatter_chunked: null pointer argument");
+  LANCET_REQUIRE(aligned(x, dtype_bytes(dtype)) && aligned(dispatched, dtype_bytes(dtype)), LANCET_ERR_INVALID,
+                 "lancet_moe_scatter_chunked: data pointers are not aligned to the element size");
+  return dispatch_launch(idx_loc, k, nullptr, capused_chain + (size_t)n_chunks * E, nullptr, x, dispatched, S, S / n_chunks, M, C,
+                         E, dtype, 0, static_cast<cudaStream_t>(stream));
+}
+
 int lancet_moe_combine_chunked(const void* expert_out, const void* gates_s, int gates_dtype, const int32_t* idx_loc,
                                int S, int M, int C, int E, int k, int n_chunks, int dtype, void* out,
                                lancet_stream_t stream) {

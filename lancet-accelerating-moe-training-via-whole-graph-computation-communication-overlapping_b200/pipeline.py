@@ -44,6 +44,13 @@ class ChunkedMoE:
             _ptr(self.dispatched), _ptr(self.ws), self.ws.numel(), _stream(x)))
         return self.dispatched
 
+    def scatter(self, x, out=None):
+        """Move another [S, M] tensor with the routing of the last `dispatch` (no gating)."""
+        out = self.dispatched if out is None else out
+        check(_capi.lib().lancet_moe_scatter_chunked(_ptr(x), _ptr(self.idx_loc), _ptr(self.capused), _ptr(out), self.S, self.M,
+                                                     self.C, self.E, self.k, self.n, _DT[x.dtype], _stream(x)))
+        return out
+
     def combine(self, expert_out=None, out=None):
         eo = self.dispatched if expert_out is None else expert_out
         out = self.out if out is None else out

@@ -337,3 +337,30 @@ def test_batch_prioritized_routing(S, E, M, n, cf, dt):
         np.testing.assert_array_equal(host(got[2]), want[2])
         np.testing.assert_array_equal(host(got[3]), want[3])
         np.testing.assert_array_equal(host(got[4]).astype(np.float32), want[4].astype(np.float32))
+
+
+def test_scatter_with_an_existing_routing_table():
+    """lancet_moe_scatter_chunked moves another tensor with the routing of the last chained dispatch."""
+    S, M, E, k, n = 4096, 64, 8, 2, 4
+    g = torch.Generator(device=DEV).manual_seed(3)
+    gate = torch.softmax(torch.randn((S, E), device=DEV, generator=g), dim=1)
+    x = torch.randn((S, M), device=DEV, generator=g).half()
+    y = torch.randn((S, M), device=DEV, generator=g).half()
+    plan = LB.ChunkedMoE(S, M, E, k, 1.0, n, torch.float16, device=DEV)
+    first = plan.dispatch(x, gate).clone()
+    other = torch.full_like(first, 7.0)
+    plan.scatter(y, out=other)
+    again = torch.full_like(first, 7.0)
+    plan.scatter(x, out=again)
+    assert torch.equal(again, first)                       # same rows, same zero padding
+    il = plan.idx_loc.cpu().numpy()
+    yh, oh = y.cpu().numpy(), other.cpu().numpy()
+    Sp = S // n
+    for c in range(n):
+        for j in range(k):
+            idx, loc = il[c, 2 * j], il[c, 2 * j + 1]
+            kept = idx >= 0
+            np.testing.assert_array_equal(oh[idx[kept], loc[kept]], yh[c * Sp:(c + 1) * Sp][kept])
+    used = plan.capused.cpu().numpy()[-1]
+    for e in range(E):
+        assert (oh[e, used[e]:] == 0).all()
