@@ -240,19 +240,29 @@ __device__ __forceinline__ uint32_t instr_desc(bool a_mn, bool b_mn, int m_rows)
          ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(m_rows >> 4) << 24);  // D = f32; 128 rows, or 256 over a CTA pair
 }
 
-// erf(|x| / sqrt 2) and exp(-x^2 / 2) from one reciprocal, one exp2 and a degree-5 polynomial (Abramowitz & Stegun
-// 7.1.26, absolute error 6e-7 in float32: three orders below the rounding of a 16-bit output).  The library erff costs
-// about twice the instructions, and the epilogue's FP32 work is what holds the first expert GEMM back.
-__device__ __forceinline__ void erf_exp_half_sq(float x, float* erf_abs, float* e) {
-  const float z = fabsf(x) * 0.70710678118654752f;
-  const float t = __fdividef(1.0f, fmaf(0.3275911f, z, 1.0f));
-  float poly = fmaf(1.061405429f, t, -1.453152027f);
-  poly = fmaf(poly, t, 1.421413741f);
-  poly = fmaf(poly, t, -0.284496736f);
-  poly = fmaf(poly, t, 0.254829592f);
-  poly *= t;
-  *e = __expf(-z * z);
-  *erf_abs = fmaf(-poly, *e, 1.0f);
+// Upper tail of the normal distribution and its density factor: q = Q(|x|) = 0.5 erfc(|x| / sqrt 2) and e = exp(-x^2 / 2),
+// from one reciprocal, one exp2 and a degree-5 polynomial (Abramowitz & Stegun 7.1.26, absolute error 3e-7 in q: three
+// orders below the rounding of a 16-bit output; the tail keeps its relative accuracy because q is formed as a product,
+// not as 1 - erf).  All constants are folded: 13 instructions for GELU, 14 for its derivative.  The library erff costs
+// about twice that, and at the power cap every FP32 instruction per output element shows in the GEMM's time.
+__device__ __forceinline__ float rcp_approx(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ void normal_tail(float x, float* q, float* e) {
+  const float t = rcp_approx(fmaf(0.3275911f * 0.70710678118654752f, fabsf(x), 1.0f));
+  float poly = fmaf(0.5f * 1.061405429f, t, 0.5f * -1.453152027f);
+  poly = fmaf(poly, t, 0.5f * 1.421413741f);
+  poly = fmaf(poly, t, 0.5f * -0.284496736f);
+  poly = fmaf(poly, t, 0.5f * 0.254829592f);
+  *e = ex2_approx(x * x * (-0.5f * 1.4426950408889634f));
+  *q = poly * (t * *e);
 }
 
 // Hardware tanh (one special-function instruction, relative error about 2^-11: below the rounding of a 16-bit output).
@@ -265,10 +275,10 @@ __device__ __forceinline__ float tanh_fast(float x) {
 template <int act>
 __device__ __forceinline__ float dactivate(float x) {
   if (act == 1) return x > 0.f ? 1.f : 0.f;
-  if (act == 2) {
-    float ea, e;
-    erf_exp_half_sq(x, &ea, &e);
-    return fmaf(0.5f, copysignf(ea, x), 0.5f) + x * 0.3989422804014327f * e;
+  if (act == 2) {   // Phi(x) + x phi(x); Phi(x) = 1 - q for x >= 0, q for x < 0
+    float q, e;
+    normal_tail(x, &q, &e);
+    return fmaf(x * e, 0.3989422804014327f, x >= 0.f ? 1.0f - q : q);
   }
   if (act == 3) {
     const float x2 = x * x;
@@ -361,10 +371,10 @@ __device__ __forceinline__ Tile decode_tile(const Params& p, Sched& sc, int t, i
 template <int act>
 __device__ __forceinline__ float activate(float v) {
   if (act == 1) return fmaxf(v, 0.f);
-  if (act == 2) {
-    float ea, e;
-    erf_exp_half_sq(v, &ea, &e);
-    return v * fmaf(0.5f, copysignf(ea, v), 0.5f);
+  if (act == 2) {   // v Phi(v) = relu(v) - |v| Q(|v|)
+    float q, e;
+    normal_tail(v, &q, &e);
+    return fmaf(-fabsf(v), q, fmaxf(v, 0.f));
   }
   if (act == 3) {   // tanh form: 0.5 v (1 + tanh(sqrt(2/pi) (v + 0.044715 v^3)))
     const float h = 0.5f * v;
