@@ -265,6 +265,45 @@ __device__ __forceinline__ void normal_tail(float x, float* q, float* e) {
   *q = poly * (t * *e);
 }
 
+// Two float32 values in one 64-bit register, for the packed FP32 instructions of this architecture (fma / mul .f32x2:
+// one instruction works on both halves).  The polynomial part of the GELU epilogue runs on element pairs with them.
+#define LANCET_GELU_PACKED 1
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pack2(float a, float b) {
+  f32x2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void unpack2(f32x2 v, float& a, float& b) { asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v)); }
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+  f32x2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
+  f32x2 d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ f32x2 splat2(float a) { return pack2(a, a); }
+
+// normal_tail for two values at once: the same operations in the same order per value (bit-identical to the scalar form).
+__device__ __forceinline__ void normal_tail2(float x0, float x1, float& q0, float& q1, float& e0, float& e1) {
+  const float t0 = rcp_approx(fmaf(0.3275911f * 0.70710678118654752f, fabsf(x0), 1.0f));
+  const float t1 = rcp_approx(fmaf(0.3275911f * 0.70710678118654752f, fabsf(x1), 1.0f));
+  const f32x2 t = pack2(t0, t1);
+  f32x2 poly = fma2(splat2(0.5f * 1.061405429f), t, splat2(0.5f * -1.453152027f));
+  poly = fma2(poly, t, splat2(0.5f * 1.421413741f));
+  poly = fma2(poly, t, splat2(0.5f * -0.284496736f));
+  poly = fma2(poly, t, splat2(0.5f * 0.254829592f));
+  const f32x2 x = pack2(x0, x1);
+  float a0, a1;
+  unpack2(mul2(mul2(x, x), splat2(-0.5f * 1.4426950408889634f)), a0, a1);
+  e0 = ex2_approx(a0);
+  e1 = ex2_approx(a1);
+  unpack2(mul2(poly, mul2(t, pack2(e0, e1))), q0, q1);
+}
+
 // Hardware tanh (one special-function instruction, relative error about 2^-11: below the rounding of a 16-bit output).
 __device__ __forceinline__ float tanh_fast(float x) {
   float y;
@@ -381,6 +420,32 @@ __device__ __forceinline__ float activate(float v) {
     return fmaf(h, tanh_fast(v * fmaf(0.0356774081f, v * v, 0.7978845608028654f)), h);
   }
   return v;
+}
+
+// Two outputs at a time: the erf GELU and its derivative share the packed polynomial, everything else is the scalar form.
+template <int act>
+__device__ __forceinline__ void activate_pair(float v0, float v1, float& o0, float& o1) {
+  if (act == 2 && LANCET_GELU_PACKED) {
+    float q0, q1, e0, e1;
+    normal_tail2(v0, v1, q0, q1, e0, e1);
+    o0 = fmaf(-fabsf(v0), q0, fmaxf(v0, 0.f));
+    o1 = fmaf(-fabsf(v1), q1, fmaxf(v1, 0.f));
+  } else {
+    o0 = activate<act>(v0);
+    o1 = activate<act>(v1);
+  }
+}
+template <int act>
+__device__ __forceinline__ void dactivate_pair(float x0, float x1, float& d0, float& d1) {
+  if (act == 2 && LANCET_GELU_PACKED) {
+    float q0, q1, e0, e1;
+    normal_tail2(x0, x1, q0, q1, e0, e1);
+    d0 = fmaf(x0 * e0, 0.3989422804014327f, x0 >= 0.f ? 1.0f - q0 : q0);
+    d1 = fmaf(x1 * e1, 0.3989422804014327f, x1 >= 0.f ? 1.0f - q1 : q1);
+  } else {
+    d0 = dactivate<act>(x0);
+    d1 = dactivate<act>(x1);
+  }
 }
 
 template <int MODE>
@@ -663,8 +728,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 #pragma unroll
             for (int q = 0; q < 4; ++q) reinterpret_cast<uint4*>(pre)[q] = pp[q];
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-              o[i] = Num<T>::from_f(__uint_as_float(r[i]) * dactivate<ACT>(Num<T>::to_f(pre[i])));
+            for (int i = 0; i < 32; i += 2) {
+              float d0, d1;
+              dactivate_pair<ACT>(Num<T>::to_f(pre[i]), Num<T>::to_f(pre[i + 1]), d0, d1);
+              o[i] = Num<T>::from_f(__uint_as_float(r[i]) * d0);
+              o[i + 1] = Num<T>::from_f(__uint_as_float(r[i + 1]) * d1);
+            }
           } else {
             alignas(16) T pre[32];
             alignas(16) T bv[32];
@@ -677,11 +746,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
               for (int q = 0; q < 4; ++q) reinterpret_cast<uint4*>(bv)[q] = __ldg(bp + q);
             }
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              float v = __uint_as_float(r[i]);
-              v += Num<T>::to_f(bv[i]);
-              pre[i] = Num<T>::from_f(v);
-              o[i] = Num<T>::from_f(activate<ACT>(v));
+            for (int i = 0; i < 32; i += 2) {
+              const float v0 = __uint_as_float(r[i]) + Num<T>::to_f(bv[i]);
+              const float v1 = __uint_as_float(r[i + 1]) + Num<T>::to_f(bv[i + 1]);
+              pre[i] = Num<T>::from_f(v0);
+              pre[i + 1] = Num<T>::from_f(v1);
+              float a0, a1;
+              activate_pair<ACT>(v0, v1, a0, a1);
+              o[i] = Num<T>::from_f(a0);
+              o[i + 1] = Num<T>::from_f(a1);
             }
             if (EPI == EPI_ACT_PRE) {
               uint4* dp = reinterpret_cast<uint4*>(PRE + out_row * p.N + col0);
