@@ -9,8 +9,10 @@ src/op/dialect/cuda/lans.cc:108-117.  The reference's per-tensor scratch slices
 overlap for three or more tensors (lans.cc:126-129 uses numels[i-1] instead of
 a prefix sum); this oracle implements the intended, non-overlapping semantics
 (NVIDIA apex FusedLANS, which tests/python/optim/test_lans.py:18-21 compares
-with).  apex is not available here, so LANS parity is pinned by the kernel
-source and by the float64 variant below only: PARITY UNPINNED by golden vectors.
+with).  apex is not available here.  Parity pin: tests/test_ref_kernels_gpu.py
+runs the reference's own multi_tensor_lans.cu (compiled unmodified by
+oracle/ref_build/build_ref.py) on the GPU and holds this oracle and the product's
+kernels to rel 1e-5 against it over consecutive steps and all flag combinations.
 """
 import numpy as np
 
