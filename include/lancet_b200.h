@@ -406,6 +406,16 @@ int lancet_moe_combine_bwd_p2p(const void* dout, const void* gates_s, const int3
                                void* const* peer_d_expert_out, void* const* peer_expert_out, void* dgates_s, int S,
                                int M, int C, int LE, int W, int rank, int k, int n_chunks, int dtype,
                                lancet_stream_t stream);
+/* The two halves of lancet_moe_combine_bwd_p2p as separate launches, for schedules that start the expert GEMMs as soon
+ * as the rows have been sent and compute the gate gradients beside them: part 1 = moe_decode_dx + _all_to_all
+ * (src/op/dialect/cuda/moe.cc:1345-1375; stores to the owners only, dgates_s is not touched), part 2 = moe_decode_dg
+ * (:1431-1461; loads of the owners' expert outputs only, peer_d_expert_out is not touched), part 0 = both in one pass.
+ * Same bits as the joint pass.  A caller of part 2 must not pass the step's last flag barrier before that launch has
+ * finished: the owners overwrite expert_out in their next forward pass. */
+int lancet_moe_combine_bwd_part_p2p(const void* dout, const void* gates_s, const int32_t* idx_loc,
+                                    void* const* peer_d_expert_out, void* const* peer_expert_out, void* dgates_s, int S,
+                                    int M, int C, int LE, int W, int rank, int k, int n_chunks, int dtype, int part,
+                                    lancet_stream_t stream);
 /* Bias gradient of an expert layer: db[e][:] = sum over the groups of expert e and their live rows of
  * dY[g][r][:]  (dY [groups][C][N], db [LE][N]); the reference gets it from the autodiff of nn.Linear's
  * bias add (a `sum` over rows).  ws: lancet_grouped_bias_grad_workspace_bytes(LE, N) bytes. */

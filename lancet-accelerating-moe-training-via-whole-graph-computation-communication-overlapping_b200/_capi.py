@@ -121,6 +121,9 @@ SIGNATURES = {
     "lancet_moe_combine_bwd_p2p": (c_int, [c_void_p, c_void_p, c_void_p, ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p),
                                            c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                            c_void_p]),
+    "lancet_moe_combine_bwd_part_p2p": (c_int, [c_void_p, c_void_p, c_void_p, ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p),
+                                                c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                                c_void_p]),
     "lancet_grouped_gemm_nt_window": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                               c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "lancet_grouped_gemm_nn_window": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,

@@ -170,7 +170,9 @@ combine_rows_peer_kernel(const float* __restrict__ gates, const int32_t* __restr
 //   d_expert_out[owner][row] = gates[j,s] * dout[s]      (peer store: the transpose of the forward gather)
 //   dgates[j,s]             = <expert_out[owner][row], dout[s]>   (peer load, fp32 accumulation)
 // One warp per token; the row of dout is read once and used for both.
-template <typename T, int N, int K>
+// PART 0: both halves in one pass (egress and ingress of the link busy at once); 1: only the rows sent to the owners;
+// 2: only the gate gradients.  The halves meet the elements in the same order as the joint pass: same bits.
+template <typename T, int N, int K, int PART>
 __global__ void __launch_bounds__(kP2PThreads)
 combine_bwd_peer_kernel(const float* __restrict__ gates, const int32_t* __restrict__ idx_loc, const T* __restrict__ dout,
                         PeerTable d_eo, PeerTable eo, float* __restrict__ dgates, int S, int Sp, int M, int C, int E, int LE,
@@ -214,10 +216,12 @@ combine_bwd_peer_kernel(const float* __restrict__ gates, const int32_t* __restri
       for (int j = 0; j < K; ++j) {
         if (!drow[j]) continue;
         P e[U];
+        if (PART != 1) {
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-          const int v = base + u * 32 + lane;
-          if (v < row_vecs) e[u] = erow[j][v];
+          for (int u = 0; u < U; ++u) {
+            const int v = base + u * 32 + lane;
+            if (v < row_vecs) e[u] = erow[j][v];
+          }
         }
 #pragma unroll
         for (int u = 0; u < U; ++u) {
@@ -227,19 +231,21 @@ combine_bwd_peer_kernel(const float* __restrict__ gates, const int32_t* __restri
 #pragma unroll
           for (int i = 0; i < N; ++i) {
             const float dv = Num<T>::to_f(d[u].v[i]);
-            o.v[i] = Num<T>::from_f(__fmul_rn(g[j], dv));
-            dot[j] = fmaf(Num<T>::to_f(e[u].v[i]), dv, dot[j]);
+            if (PART != 2) o.v[i] = Num<T>::from_f(__fmul_rn(g[j], dv));
+            if (PART != 1) dot[j] = fmaf(Num<T>::to_f(e[u].v[i]), dv, dot[j]);
           }
-          drow[j][v] = o;
+          if (PART != 2) drow[j][v] = o;
         }
       }
     }
+    if (PART != 1) {
 #pragma unroll
-    for (int j = 0; j < K; ++j) {
-      float t = dot[j];
+      for (int j = 0; j < K; ++j) {
+        float t = dot[j];
 #pragma unroll
-      for (int d = 16; d > 0; d >>= 1) t += __shfl_xor_sync(0xffffffffu, t, d);
-      if (lane == 0) dgates[il_index_p2p((int)s, Sp, K, j)] = t;
+        for (int d = 16; d > 0; d >>= 1) t += __shfl_xor_sync(0xffffffffu, t, d);
+        if (lane == 0) dgates[il_index_p2p((int)s, Sp, K, j)] = t;
+      }
     }
   }
 }
@@ -357,15 +363,22 @@ static int combine_p2p_t(const float* gates, const int32_t* idx_loc, const PeerT
 template <typename T>
 static int combine_bwd_p2p_t(const float* gates, const int32_t* idx_loc, const void* dout, const PeerTable& td,
                              const PeerTable& te, float* dgates, int S, int Sp, int M, int C, int E, int LE, int rank, int k,
-                             cudaStream_t st) {
+                             int part, cudaStream_t st) {
   constexpr int N = 16 / sizeof(T);
   ProfScope prof("combine_bwd_peer_kernel", st);
-  if (k == 1)
-    combine_bwd_peer_kernel<T, N, 1><<<p2p_grid(S), kP2PThreads, 0, st>>>(gates, idx_loc, static_cast<const T*>(dout), td, te,
-                                                                        dgates, S, Sp, M, C, E, LE, rank);
-  else
-    combine_bwd_peer_kernel<T, N, 2><<<p2p_grid(S), kP2PThreads, 0, st>>>(gates, idx_loc, static_cast<const T*>(dout), td, te,
-                                                                        dgates, S, Sp, M, C, E, LE, rank);
+#define LANCET_CB(KK, PP)                                                                                                      \
+  combine_bwd_peer_kernel<T, N, KK, PP><<<p2p_grid(S), kP2PThreads, 0, st>>>(gates, idx_loc, static_cast<const T*>(dout), td, \
+                                                                            te, dgates, S, Sp, M, C, E, LE, rank)
+  if (k == 1) {
+    if (part == 0) LANCET_CB(1, 0);
+    else if (part == 1) LANCET_CB(1, 1);
+    else LANCET_CB(1, 2);
+  } else {
+    if (part == 0) LANCET_CB(2, 0);
+    else if (part == 1) LANCET_CB(2, 1);
+    else LANCET_CB(2, 2);
+  }
+#undef LANCET_CB
   return launch_status("combine_bwd_peer_kernel");
 }
 }  // namespace lancet
@@ -668,9 +681,10 @@ int lancet_moe_combine_chunked_p2p(void* const* peer_expert_out, const void* gat
   return combine_p2p_t<__nv_bfloat16>(g, idx_loc, t, out, S, Sp, M, C, E, LE, rank, k, st);
 }
 
-int lancet_moe_combine_bwd_p2p(const void* dout, const void* gates_s, const int32_t* idx_loc, void* const* peer_d_expert_out,
-                               void* const* peer_expert_out, void* dgates_s, int S, int M, int C, int LE, int W, int rank, int k,
-                               int n_chunks, int dtype, lancet_stream_t stream) {
+int lancet_moe_combine_bwd_part_p2p(const void* dout, const void* gates_s, const int32_t* idx_loc, void* const* peer_d_expert_out,
+                                    void* const* peer_expert_out, void* dgates_s, int S, int M, int C, int LE, int W, int rank,
+                                    int k, int n_chunks, int dtype, int part, lancet_stream_t stream) {
+  LANCET_REQUIRE(part >= 0 && part <= 2, LANCET_ERR_INVALID, "lancet_moe_combine_bwd_part_p2p: part %d is not 0, 1 or 2", part);
   LANCET_REQUIRE(W >= 1 && W <= kMaxPeers && rank >= 0 && rank < W && LE >= 1, LANCET_ERR_INVALID,
                  "lancet_moe_combine_bwd_p2p: bad world %d / rank %d / local experts %d", W, rank, LE);
   LANCET_REQUIRE(n_chunks >= 1 && S >= 0 && S % n_chunks == 0, LANCET_ERR_INVALID,
@@ -694,8 +708,15 @@ int lancet_moe_combine_bwd_p2p(const void* dout, const void* gates_s, const int3
   const int E = LE * W, Sp = S / n_chunks;
   const float* g = static_cast<const float*>(gates_s);
   float* dg = static_cast<float*>(dgates_s);
-  if (dtype == LANCET_F32) return combine_bwd_p2p_t<float>(g, idx_loc, dout, td, te, dg, S, Sp, M, C, E, LE, rank, k, st);
-  if (dtype == LANCET_F16) return combine_bwd_p2p_t<__half>(g, idx_loc, dout, td, te, dg, S, Sp, M, C, E, LE, rank, k, st);
-  return combine_bwd_p2p_t<__nv_bfloat16>(g, idx_loc, dout, td, te, dg, S, Sp, M, C, E, LE, rank, k, st);
+  if (dtype == LANCET_F32) return combine_bwd_p2p_t<float>(g, idx_loc, dout, td, te, dg, S, Sp, M, C, E, LE, rank, k, part, st);
+  if (dtype == LANCET_F16) return combine_bwd_p2p_t<__half>(g, idx_loc, dout, td, te, dg, S, Sp, M, C, E, LE, rank, k, part, st);
+  return combine_bwd_p2p_t<__nv_bfloat16>(g, idx_loc, dout, td, te, dg, S, Sp, M, C, E, LE, rank, k, part, st);
+}
+
+int lancet_moe_combine_bwd_p2p(const void* dout, const void* gates_s, const int32_t* idx_loc, void* const* peer_d_expert_out,
+                               void* const* peer_expert_out, void* dgates_s, int S, int M, int C, int LE, int W, int rank, int k,
+                               int n_chunks, int dtype, lancet_stream_t stream) {
+  return lancet_moe_combine_bwd_part_p2p(dout, gates_s, idx_loc, peer_d_expert_out, peer_expert_out, dgates_s, S, M, C, LE, W, rank,
+                                         k, n_chunks, dtype, 0, stream);
 }
 }

@@ -104,7 +104,7 @@ class LocalFabric:
 class DistChunkedMoE:
     """Chunk-chained top-k dispatch and combine with the all-to-all fused into the kernels."""
 
-    ROW_ALIGN = 128     # stage windows of the staged exchange end on whole tiles of the grouped GEMM
+    ROW_ALIGN = 256     # stage windows of the staged exchange end on whole tiles of the grouped GEMM (256 rows per CTA pair)
 
     def __init__(self, S, M, k=2, capacity_factor=1.25, n_chunks=4, dtype=torch.float16, device="cuda",
                  local_experts=2, fabric=None, group=None, timeout_s=5.0, remote_zero=False, train=False):
@@ -268,16 +268,18 @@ class DistChunkedMoE:
             _ptr(x), _ptr(self.idx_loc), self.S, self.M, self.C, self.LE, self.W, self.rank, self.k, self.n, c0, c1,
             _DT[x.dtype], self.peer_recv[self.parity], _stream(x)))
 
-    def stage_prepare(self, buf=None):
-        """After the first barrier of a pass: row windows of every stage, row totals, zero-fill of the rows of
-        `buf` (default: the receive buffer) that no token owns.  Returns (win_begin, win_end, counts)."""
+    def stage_prepare(self, buf=None, zero=True):
+        """After the first barrier of a pass: row windows of every stage, row totals, and (zero=True) zero-fill of the
+        rows of `buf` (default: the receive buffer) that no token owns; callers that keep the zero-fill off their
+        critical path pass zero=False and call zero_tail on another stream.  Returns (win_begin, win_end, counts)."""
         L = _capi.lib()
         cnt = self.counts[self.parity]
         if buf is None:
             buf = self.recv[self.parity]
             check(L.lancet_moe_stage_windows(_ptr(self.chain[self.parity]), self.W, self.LE, self.n, self.ROW_ALIGN,
                                              _ptr(self.win_begin), _ptr(self.win_end), _ptr(cnt), _stream(cnt)))
-        check(L.lancet_moe_zero_tail(_ptr(buf), _ptr(cnt), self.M, self.C, self.W * self.LE, _DT[self.dtype], _stream(cnt)))
+        if zero:
+            check(L.lancet_moe_zero_tail(_ptr(buf), _ptr(cnt), self.M, self.C, self.W * self.LE, _DT[self.dtype], _stream(cnt)))
         return self.win_begin, self.win_end, cnt
 
     def stage_combine(self, c0, c1=None, out=None):
@@ -307,12 +309,14 @@ class DistChunkedMoE:
         return o
 
     # -- backward ------------------------------------------------------------------------------
-    def combine_backward_send(self, dout):
+    def combine_backward_send(self, dout, part=0):
         """Backward of combine, fused with the exchange: gate-weighted rows of dout go to the owners'
-        d_expert_out buffers, dgates = <expert output row, dout row>."""
-        check(_capi.lib().lancet_moe_combine_bwd_p2p(
+        d_expert_out buffers, dgates = <expert output row, dout row>.  part 1 sends the rows only, part 2 computes the
+        gate gradients only (a schedule can start the expert GEMMs after part 1 and run part 2 beside them; part 2 must
+        have finished before this rank passes the step's last barrier, because the owners then reuse expert_out)."""
+        check(_capi.lib().lancet_moe_combine_bwd_part_p2p(
             _ptr(dout), _ptr(self.gates_s), _ptr(self.idx_loc), self.peer_deo, self.peer_eo, _ptr(self.dgates), self.S,
-            self.M, self.C, self.LE, self.W, self.rank, self.k, self.n, _DT[self.dtype], _stream(dout)))
+            self.M, self.C, self.LE, self.W, self.rank, self.k, self.n, _DT[self.dtype], part, _stream(dout)))
 
     def combine_backward_finish(self):
         """Meet the peers, zero the rows of d_expert_out that no token owns; returns (d_expert_out, dgates)."""

@@ -88,8 +88,17 @@ class MoELayer:
     def fwd_stage_dispatch(self, c):
         self.moe.stage_dispatch(self._x, *self.stage_chunks[c])
 
-    def fwd_prepare(self):
-        self.win_begin, self.win_end, self.cnt = self.moe.stage_prepare()
+    def _zero_tail_aside(self, buf=None):
+        """The rows past each block's total are read by nothing in the layer (every GEMM is count-aware); they are zeroed
+        for the buffer's contract, on a side stream, so that the first expert GEMM need not wait for it."""
+        main = torch.cuda.current_stream(self.device)
+        ev = main.record_event()
+        with torch.cuda.stream(self.post_stream):
+            self.post_stream.wait_event(ev)
+            self.moe.zero_tail(buf)
+
+    def fwd_prepare(self, zero=True):
+        self.win_begin, self.win_end, self.cnt = self.moe.stage_prepare(zero=zero)
         self._win = [(self.win_begin[c0], self.win_end[c1 - 1]) for c0, c1 in self.stage_chunks]
         # (per-chunk windows: a stage of several chunks begins where its first chunk's window begins, which is at or
         # before the tile holding the previous stage's end, and ends where its last chunk's window ends)
@@ -115,17 +124,16 @@ class MoELayer:
     def _streams(self):
         if getattr(self, "comm", None) is None:
             self.comm = torch.cuda.Stream(device=self.device)
-            self.aux = torch.cuda.Stream(device=self.device, priority=-1)
             self.post_stream = torch.cuda.Stream(device=self.device)
-        return torch.cuda.current_stream(self.device), self.aux, self.comm
+        return torch.cuda.current_stream(self.device), self.comm
 
     def forward_pipelined(self, x, gate):
-        """Three streams: `comm` carries the exchange stages and the flag barriers (one fixed order on every
-        rank), the current stream the first expert GEMM of every stage, `aux` the second one: the first GEMM of
-        stage c+1 does not depend on the second of stage c, so its CTAs fill the SMs that the other's last,
-        partial wave of tiles leaves idle."""
+        """Two streams: `comm` carries the exchange stages and the flag barriers, the current stream the expert GEMMs,
+        both in one fixed order on every rank.  (With the two GEMMs of a stage on two compute streams the persistent
+        kernels race for the SMs, the ranks end up in different orders and every flag barrier then waits for the
+        slowest: measured at 2 GPUs, up to 0.9 ms of barrier wait per step against 0.1 ms of idle last waves saved.)"""
         n = len(self.stage_chunks)
-        main, aux, comm = self._streams()
+        main, comm = self._streams()
         self._limits(True)
         self.fwd_gate(x, gate)
         comm.wait_stream(main)
@@ -136,15 +144,13 @@ class MoELayer:
                 self.moe.barrier()
                 arrived.append(comm.record_event())
         main.wait_event(arrived[0])
-        self.fwd_prepare()
+        self.fwd_prepare(zero=False)
+        self._zero_tail_aside()
         for c in range(n):
             main.wait_event(arrived[c])
             self.fwd_stage_experts_1(c)
-            half = main.record_event()
-            with torch.cuda.stream(aux):
-                aux.wait_event(half)
-                self.fwd_stage_experts_2(c)
-                done = aux.record_event()
+            self.fwd_stage_experts_2(c)
+            done = main.record_event()
             if c >= 1 or n == 1:
                 with torch.cuda.stream(comm):
                     comm.wait_event(done)
@@ -153,8 +159,8 @@ class MoELayer:
                         self.fwd_stage_combine(c - 1)
                     if c == n - 1:
                         self.fwd_stage_combine(c)
-        main.wait_stream(aux)
         main.wait_stream(comm)
+        main.wait_stream(self.post_stream)
         self._limits(False)
         self._fwd_schedule = "staged"
         return self.moe.out
@@ -173,7 +179,7 @@ class MoELayer:
         exchange stages).  Gating is chained chunk by chunk and the owners learn each stage's row layout just before
         its rows arrive; results are bit-identical to `forward` on the concatenated inputs."""
         n = len(self.stage_chunks)
-        main, aux, comm = self._streams()
+        main, comm = self._streams()
         moe, Sp = self.moe, self.moe.Sp
         if getattr(self, "x_in", None) is None:
             self.x_in = torch.empty((self.S, self.M), dtype=moe.dtype, device=self.device)
@@ -202,11 +208,8 @@ class MoELayer:
             if s == n - 1:
                 moe.zero_tail()          # the row totals are known with the last stage
             self.fwd_stage_experts_1(s)
-            half = main.record_event()
-            with torch.cuda.stream(aux):
-                aux.wait_event(half)
-                self.fwd_stage_experts_2(s)
-                done = aux.record_event()
+            self.fwd_stage_experts_2(s)
+            done = main.record_event()
             if s >= 1 or n == 1:
                 with torch.cuda.stream(comm):
                     comm.wait_event(done)
@@ -218,7 +221,6 @@ class MoELayer:
                             with torch.cuda.stream(self.post_stream):
                                 self.post_stream.wait_event(ev)
                                 post(*self.stage_chunks[t], rows)
-        main.wait_stream(aux)
         main.wait_stream(comm)
         main.wait_stream(self.post_stream)
         self._limits(False)
@@ -229,8 +231,9 @@ class MoELayer:
     def bwd_stage_combine(self, dout, c):
         self.moe.stage_combine_backward(dout, *self.stage_chunks[c])
 
-    def bwd_prepare(self):
-        self.moe.stage_prepare(self.moe.d_expert_out)
+    def bwd_prepare(self, zero=True):
+        if zero:
+            self.moe.stage_prepare(self.moe.d_expert_out)
         self.dy = self.moe.d_expert_out.view(self.G, self.C, self.M)
 
     def bwd_stage_experts_1(self, c):
@@ -262,7 +265,7 @@ class MoELayer:
             raise RuntimeError("backward_pipelined needs the row windows of forward_pipelined of the same step "
                                "(the last forward ran the %s schedule)" % self._fwd_schedule)
         n = len(self.stage_chunks)
-        main, aux, comm = self._streams()
+        main, comm = self._streams()
         self._limits(True)
         comm.wait_stream(main)
         arrived = []
@@ -272,15 +275,13 @@ class MoELayer:
                 self.moe.barrier()
                 arrived.append(comm.record_event())
         main.wait_event(arrived[0])
-        self.bwd_prepare()
+        self.bwd_prepare(zero=False)
+        self._zero_tail_aside(self.moe.d_expert_out)
         for c in range(n):
             main.wait_event(arrived[c])
             self.bwd_stage_experts_1(c)
-            half = main.record_event()
-            with torch.cuda.stream(aux):
-                aux.wait_event(half)
-                self.bwd_stage_experts_2(c)
-                done = aux.record_event()
+            self.bwd_stage_experts_2(c)
+            done = main.record_event()
             if c >= 1 or n == 1:
                 with torch.cuda.stream(comm):
                     comm.wait_event(done)
@@ -295,7 +296,6 @@ class MoELayer:
                                 post(c0, c1, rows, self.moe.dgates[c0:c1])
         # the weight gradients have no consumer before the optimizer: they run under the last gathers
         self.bwd_weights()
-        main.wait_stream(aux)
         main.wait_stream(comm)
         main.wait_stream(self.post_stream)
         self._limits(False)
@@ -304,6 +304,9 @@ class MoELayer:
 
     # ---- backward ----
     def bwd_combine(self, dout):
+        # Both halves of the backward combine in one pass.  Sending the rows first and gathering the gate gradients on a
+        # side stream beside the data-gradient GEMMs (lancet_moe_combine_bwd_part_p2p) shortens this step from 221 to
+        # 114 us at 2 GPUs but slows the GEMMs it runs beside by more: 6.0 against 5.7 ms per forward+backward.
         self.moe.combine_backward_send(dout)
 
     def bwd_experts(self):

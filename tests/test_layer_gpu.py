@@ -85,6 +85,46 @@ def test_layer_forward_backward(W, k, n, act):
     assert int(st.item()) == 0
 
 
+def test_combine_backward_halves_equal_the_joint_pass():
+    """lancet_moe_combine_bwd_part_p2p: rows only (part 1), then gate gradients only (part 2) == both in one pass."""
+    W, k, n, S, M, H, LE = 2, 2, 4, 1024, 256, 512, 2
+    shared = {}
+    layers = [LB.MoELayer(S, M, H, k, 1.25, n, torch.bfloat16, DEV, LE, fabric=LB.LocalFabric(W, r, shared), seed=3) for r in range(W)]
+    g = torch.Generator(device=DEV).manual_seed(77)
+    xs = [torch.randn((S, M), device=DEV, generator=g).bfloat16() for _ in range(W)]
+    gates = [torch.softmax(torch.randn((S, LE * W), device=DEV, generator=g), dim=1) for _ in range(W)]
+    douts = [torch.randn((S, M), device=DEV, generator=g).bfloat16() for _ in range(W)]
+    for r, l in enumerate(layers):
+        l.fwd_dispatch(xs[r], gates[r])
+    for l in layers:
+        l.fwd_experts()
+    for l in layers:
+        l.fwd_combine()
+
+    def poison():
+        for l in layers:
+            l.moe.d_expert_out.fill_(3.0)
+            l.moe.dgates.fill_(-7.0)
+
+    poison()
+    for r, l in enumerate(layers):
+        l.moe.combine_backward_send(douts[r])
+    want = [(l.moe.d_expert_out.clone(), l.moe.dgates.clone()) for l in layers]
+    poison()
+    for r, l in enumerate(layers):
+        l.moe.combine_backward_send(douts[r], part=1)
+    for l, (deo, _) in zip(layers, want):
+        assert torch.equal(l.moe.d_expert_out, deo) and bool((l.moe.dgates == -7.0).all())
+    for l in layers:
+        l.moe.d_expert_out.fill_(3.0)
+    for r, l in enumerate(layers):
+        l.moe.combine_backward_send(douts[r], part=2)
+    for l, (_, dg) in zip(layers, want):
+        assert torch.equal(l.moe.dgates, dg) and bool((l.moe.d_expert_out == 3.0).all())
+    with pytest.raises(LB.LancetError):
+        layers[0].moe.combine_backward_send(douts[0], part=3)
+
+
 def _run_plain(layers, xs, gates, douts):
     for r, l in enumerate(layers):
         l.fwd_dispatch(xs[r], gates[r])
@@ -172,12 +212,13 @@ def test_staged_pipeline_is_bit_identical(W, k, n, S, stages):
     # the windows equal the CPU restatement and cover the live rows of every block without gaps
     from oracle import moe_oracle as O
     for l in layers:
-        ob, oe, oc = O.stage_windows(l.moe.chain[l.moe.parity].cpu().numpy(), 128)
+        ob, oe, oc = O.stage_windows(l.moe.chain[l.moe.parity].cpu().numpy(), l.moe.ROW_ALIGN)
         assert (l.win_begin.cpu().numpy() == ob).all() and (l.win_end.cpu().numpy() == oe).all()
         assert (l.cnt.cpu().numpy() == oc).all()
         lo, hi, cnt = l.win_begin.cpu().numpy(), l.win_end.cpu().numpy(), l.cnt.cpu().numpy()
         assert (lo[0] == 0).all() and (hi[-1] == cnt).all()
-        assert (lo[1:] == hi[:-1] // 128 * 128).all() and (lo % 128 == 0).all()
+        A = l.moe.ROW_ALIGN
+        assert (lo[1:] == hi[:-1] // A * A).all() and (lo % A == 0).all()
     assert int(LB.gemm_status(torch.device(DEV)).item()) == 0
 
 
