@@ -1181,6 +1181,7 @@ def _main():
     ap.add_argument("--exchange-ctas", type=int, default=0, help="layer workload, staged schedule: CTA cap of the exchange kernels")
     ap.add_argument("--gemm-ctas", type=int, default=0, help="layer workload, staged schedule: CTA cap of the expert GEMMs")
     ap.add_argument("--gemm-single", action="store_true", help="expert GEMMs: single-CTA 128x256 tiles instead of CTA pairs (A/B timing)")
+    ap.add_argument("--plain-launches", action="store_true", help="dispatch path: plain kernel launches instead of programmatic stream serialization (A/B timing)")
     ap.add_argument("--no-pipeline", action="store_true", help="gpt workload: plain blocks (no chunked pipeline around the MoE layer)")
     ap.add_argument("--lans-layers", type=int, default=24, help="transformer layers in the LANS tensor list (24 = 196 tensors)")
     args = ap.parse_args()
@@ -1192,6 +1193,9 @@ def _main():
     if args.gemm_single:
         from lancet_b200 import _capi
         _capi.check(_capi.lib().lancet_set_gemm_paired(0))
+    if args.plain_launches:
+        from lancet_b200 import _capi
+        _capi.check(_capi.lib().lancet_set_chained_launch(0))
     if args.workload == "lans":
         run_single_leg(args, leg_lans)
     elif args.workload == "ffn":

@@ -448,6 +448,11 @@ int lancet_set_cta_limits(int exchange_ctas, int gemm_ctas);
  * Bit 1: 0 (default) = the tile walk visits all (source, expert) groups of one expert before the next expert's, so
  * that an expert's weights stay in L2; 1 = groups in index order. */
 int lancet_set_gemm_paired(int mode);
+/* The short dependent kernels of the dispatch path (gate selection, slot assignment, scatter, combine) are launched with
+ * programmatic stream serialization: the next kernel's CTAs become resident while the previous kernel drains and wait, as
+ * their first instruction, until it has completed.  Results do not change; 0 switches to plain launches (A/B timing).
+ * No counterpart in the reference (one TVM/CUDA launch per operator, src/op/dialect/cuda/moe.cc:364-395). */
+int lancet_set_chained_launch(int on);
 /* cudaMemcpyAsync(dst, src, bytes) with the kind inferred from the pointers; dst or src may be a peer
  * mapping from lancet_symm_open (copy-engine transfer over NVLink; the bandwidth yardstick of bench.py). */
 int lancet_peer_copy(void* dst, const void* src, size_t bytes, lancet_stream_t stream);

@@ -67,7 +67,8 @@ int sm_count() {
   return cached[dev];
 }
 
-static int g_exchange_ctas = 0, g_gemm_ctas = 0, g_gemm_paired = 1;
+static int g_exchange_ctas = 0, g_gemm_ctas = 0, g_gemm_paired = 1, g_chained = 1;
+bool chained_launch_enabled() { return __atomic_load_n(&g_chained, __ATOMIC_RELAXED) != 0; }
 bool gemm_paired_enabled() { return (__atomic_load_n(&g_gemm_paired, __ATOMIC_RELAXED) & 1) != 0; }
 int gemm_option(int bit) { return (__atomic_load_n(&g_gemm_paired, __ATOMIC_RELAXED) >> bit) & 1; }
 int exchange_cta_limit() { return __atomic_load_n(&g_exchange_ctas, __ATOMIC_RELAXED); }
@@ -80,6 +81,11 @@ int lancet_set_cta_limits(int exchange_ctas, int gemm_ctas) {
   if (exchange_ctas < 0 || gemm_ctas < 0) return lancet::fail(LANCET_ERR_INVALID, "lancet_set_cta_limits: negative limit");
   __atomic_store_n(&lancet::g_exchange_ctas, exchange_ctas, __ATOMIC_RELAXED);
   __atomic_store_n(&lancet::g_gemm_ctas, gemm_ctas, __ATOMIC_RELAXED);
+  return LANCET_OK;
+}
+
+int lancet_set_chained_launch(int on) {
+  __atomic_store_n(&lancet::g_chained, on ? 1 : 0, __ATOMIC_RELAXED);
   return LANCET_OK;
 }
 

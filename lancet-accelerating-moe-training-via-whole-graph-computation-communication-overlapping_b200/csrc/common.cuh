@@ -1,6 +1,7 @@
 // Shared host/device helpers of the C-ABI layer: status codes, the thread-local error text,
 // dtype dispatch and small device utilities.
 #pragma once
+#include <utility>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -54,6 +55,32 @@ inline int launch_status(const char* what) {
     return fail(LANCET_ERR_CUDA, "launch of %s failed: %s", what, cudaGetErrorString(e));
   }
   return LANCET_OK;
+}
+
+// Chains of short dependent kernels (gate -> slot assignment -> scatter -> combine) are launched with programmatic
+// stream serialization: the CTAs of the next kernel may become resident while the last CTAs of the previous one drain,
+// and wait in chain_enter() until that kernel has completed and its writes are visible.  Only the launch latency and the
+// drain overlap; nothing a chained kernel reads or writes is touched before the wait.  Every kernel launched this way
+// calls chain_enter() first, so completion is transitive along the chain; after a kernel that never releases its
+// dependents (any other kernel) the launch behaves like a plain one.  lancet_set_chained_launch(0) switches it off.
+bool chained_launch_enabled();
+__device__ __forceinline__ void chain_enter() {
+  asm volatile("griddepcontrol.launch_dependents;");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+template <typename... KArgs, typename... Args>
+inline void launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = chained_launch_enabled() ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 
 inline bool valid_dtype(int d) { return d == LANCET_F32 || d == LANCET_F16 || d == LANCET_BF16; }

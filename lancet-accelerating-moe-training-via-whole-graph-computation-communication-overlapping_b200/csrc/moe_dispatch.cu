@@ -49,6 +49,7 @@ dispatch_rows_kernel(const int32_t* __restrict__ idx_loc, const int32_t* __restr
                      const int32_t* __restrict__ rows_hi, const int32_t* __restrict__ rows_lo, const V* __restrict__ x,
                      V* __restrict__ out, int S, int Sp, int row_vecs, int C, int E, int global_loc, int zero_tail) {
   constexpr int U = 8;
+  chain_enter();
   const int lane = threadIdx.x & 31;
   const long long gw = (long long)blockIdx.x * kRowWarps + (threadIdx.x >> 5);
   const long long nwarps = (long long)gridDim.x * kRowWarps;
@@ -106,6 +107,7 @@ __global__ void __launch_bounds__(kRowThreads)
 combine_rows_kernel(const void* __restrict__ gates, int gates_dtype, const int32_t* __restrict__ idx_loc,
                     const T* __restrict__ src, T* __restrict__ out, int S, int Sp, int M, int C, int E) {
   using P = Pack<T, N>;
+  chain_enter();
   const int lane = threadIdx.x & 31;
   const int row_vecs = M / N;
   const long long gw = (long long)blockIdx.x * kRowWarps + (threadIdx.x >> 5);
@@ -302,13 +304,11 @@ static int dispatch_launch_v(const int32_t* idx_loc, int k, const int32_t* in_ca
   const int grid = row_grid(tasks);
   ProfScope prof("dispatch_rows_kernel", stream);
   if (k == 1)
-    dispatch_rows_kernel<V, 1><<<grid, kRowThreads, 0, stream>>>(idx_loc, in_cap, rows_hi, rows_lo,
-                                                                 static_cast<const V*>(x), static_cast<V*>(out), S,
-                                                                 Sp > 0 ? Sp : 1, row_vecs, C, E, global_loc, zero_tail);
+    launch_chained(dispatch_rows_kernel<V, 1>, grid, kRowThreads, 0, stream, idx_loc, in_cap, rows_hi, rows_lo,
+                   static_cast<const V*>(x), static_cast<V*>(out), S, Sp > 0 ? Sp : 1, row_vecs, C, E, global_loc, zero_tail);
   else
-    dispatch_rows_kernel<V, 2><<<grid, kRowThreads, 0, stream>>>(idx_loc, in_cap, rows_hi, rows_lo,
-                                                                 static_cast<const V*>(x), static_cast<V*>(out), S,
-                                                                 Sp > 0 ? Sp : 1, row_vecs, C, E, global_loc, zero_tail);
+    launch_chained(dispatch_rows_kernel<V, 2>, grid, kRowThreads, 0, stream, idx_loc, in_cap, rows_hi, rows_lo,
+                   static_cast<const V*>(x), static_cast<V*>(out), S, Sp > 0 ? Sp : 1, row_vecs, C, E, global_loc, zero_tail);
   return launch_status("dispatch_rows_kernel");
 }
 
@@ -348,14 +348,14 @@ static int combine_launch_t(const void* gates, int gates_dtype, const int32_t* i
   ProfScope prof("combine_rows_kernel", stream);
   if (vec) {
     if (k == 1)
-      combine_rows_kernel<T, N, 1><<<grid, kRowThreads, 0, stream>>>(gates, gates_dtype, idx_loc, s_, o_, S, Sp, M, C, E);
+      launch_chained(combine_rows_kernel<T, N, 1>, grid, kRowThreads, 0, stream, gates, gates_dtype, idx_loc, s_, o_, S, Sp, M, C, E);
     else
-      combine_rows_kernel<T, N, 2><<<grid, kRowThreads, 0, stream>>>(gates, gates_dtype, idx_loc, s_, o_, S, Sp, M, C, E);
+      launch_chained(combine_rows_kernel<T, N, 2>, grid, kRowThreads, 0, stream, gates, gates_dtype, idx_loc, s_, o_, S, Sp, M, C, E);
   } else {
     if (k == 1)
-      combine_rows_kernel<T, 1, 1><<<grid, kRowThreads, 0, stream>>>(gates, gates_dtype, idx_loc, s_, o_, S, Sp, M, C, E);
+      launch_chained(combine_rows_kernel<T, 1, 1>, grid, kRowThreads, 0, stream, gates, gates_dtype, idx_loc, s_, o_, S, Sp, M, C, E);
     else
-      combine_rows_kernel<T, 1, 2><<<grid, kRowThreads, 0, stream>>>(gates, gates_dtype, idx_loc, s_, o_, S, Sp, M, C, E);
+      launch_chained(combine_rows_kernel<T, 1, 2>, grid, kRowThreads, 0, stream, gates, gates_dtype, idx_loc, s_, o_, S, Sp, M, C, E);
   }
   return launch_status("combine_rows_kernel");
 }

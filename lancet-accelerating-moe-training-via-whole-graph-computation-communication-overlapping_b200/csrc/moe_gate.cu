@@ -40,6 +40,7 @@ __global__ void __launch_bounds__(kGateTile)
 gate_select_kernel(const void* __restrict__ gate, int gate_dtype, int Sp, int E, int tiles_per_chunk,
                    float* __restrict__ raw_gates, int32_t* __restrict__ idx_loc, int* __restrict__ hist) {
   extern __shared__ int warp_cnt[];  // [kGateWarps][K*E]
+  chain_enter();
   const int KE = K * E;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int chunk = blockIdx.x / tiles_per_chunk;
@@ -162,6 +163,7 @@ gate_assign_kernel(int Sp, int E, int C, int M, int n_chunks, int tiles_per_chun
                    int32_t* __restrict__ idx_loc, void* __restrict__ gates_out, int gates_dtype,
                    int32_t* __restrict__ out_capused, uint64_t* __restrict__ out_elems, int32_t* __restrict__ chain_row0) {
   extern __shared__ int sm[];  // pre[KE], used[E], tot[n_chunks][KE]
+  chain_enter();
   const int KE = K * E;
   int* pre = sm;
   int* used_s = sm + KE;
@@ -294,11 +296,11 @@ int gate_launch(const void* gate, int gate_dtype, int S, int E, int k, int n_chu
   const size_t smem2 = (size_t)(KE + E + (size_t)n_chunks * KE) * sizeof(int);
   // with S == 0 the select pass still runs (every thread is out of range) so that the histograms are zero
   if (k == 1)
-    gate_select_kernel<1><<<L.tiles, kGateTile, smem1, stream>>>(gate, gate_dtype, L.Sp, E, L.tiles_per_chunk, raw,
-                                                                 out_idx_loc, hist);
+    launch_chained(gate_select_kernel<1>, L.tiles, kGateTile, smem1, stream, gate, gate_dtype, L.Sp, E, L.tiles_per_chunk, raw,
+                   out_idx_loc, hist);
   else
-    gate_select_kernel<2><<<L.tiles, kGateTile, smem1, stream>>>(gate, gate_dtype, L.Sp, E, L.tiles_per_chunk, raw,
-                                                                 out_idx_loc, hist);
+    launch_chained(gate_select_kernel<2>, L.tiles, kGateTile, smem1, stream, gate, gate_dtype, L.Sp, E, L.tiles_per_chunk, raw,
+                   out_idx_loc, hist);
   if (int st = launch_status("gate_select_kernel")) return st;
   const int prescanned = L.tiles > kSelfScanMaxTiles ? 1 : 0;
   if (prescanned) {
@@ -306,13 +308,13 @@ int gate_launch(const void* gate, int gate_dtype, int S, int E, int k, int n_chu
     if (int st = launch_status("gate_scan_tiles_kernel")) return st;
   }
   if (k == 1)
-    gate_assign_kernel<1><<<L.tiles, kGateTile, smem2, stream>>>(L.Sp, E, C, M, n_chunks, L.tiles_per_chunk, prescanned,
-                                                                 global_loc, hist, total, in_capused, raw, out_idx_loc,
-                                                                 out_gates_s, gates_dtype, out_capused, out_elems, chain_row0);
+    launch_chained(gate_assign_kernel<1>, L.tiles, kGateTile, smem2, stream, L.Sp, E, C, M, n_chunks, L.tiles_per_chunk,
+                   prescanned, global_loc, hist, total, in_capused, raw, out_idx_loc, out_gates_s, gates_dtype, out_capused,
+                   out_elems, chain_row0);
   else
-    gate_assign_kernel<2><<<L.tiles, kGateTile, smem2, stream>>>(L.Sp, E, C, M, n_chunks, L.tiles_per_chunk, prescanned,
-                                                                 global_loc, hist, total, in_capused, raw, out_idx_loc,
-                                                                 out_gates_s, gates_dtype, out_capused, out_elems, chain_row0);
+    launch_chained(gate_assign_kernel<2>, L.tiles, kGateTile, smem2, stream, L.Sp, E, C, M, n_chunks, L.tiles_per_chunk,
+                   prescanned, global_loc, hist, total, in_capused, raw, out_idx_loc, out_gates_s, gates_dtype, out_capused,
+                   out_elems, chain_row0);
   return launch_status("gate_assign_kernel");
 }
 
