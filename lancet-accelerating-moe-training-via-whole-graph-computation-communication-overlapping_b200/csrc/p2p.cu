@@ -38,6 +38,7 @@ dispatch_rows_peer_kernel(const int32_t* __restrict__ idx_loc, const int32_t* __
                           const V* __restrict__ x, PeerTable recv, PeerTable counts, int S, int Sp, int row_vecs, int C,
                           int E, int LE, int my_rank, int zero_tail) {
   constexpr int U = 8;
+  chain_enter();
   const int lane = threadIdx.x & 31;
   if (!zero_tail && blockIdx.x == 0 && counts.ptr[0] != nullptr) {
     // tell every owner how many rows of my block it received; it zero-fills the rest locally
@@ -109,6 +110,7 @@ combine_rows_peer_kernel(const float* __restrict__ gates, const int32_t* __restr
                          T* __restrict__ out, int S, int Sp, int M, int C, int E, int LE, int my_rank) {
   using P = PackP<T, N>;
   constexpr int U = 4;
+  chain_enter();
   const int lane = threadIdx.x & 31;
   const int row_vecs = M / N;
   const long long gw = (long long)blockIdx.x * kP2PWarps + (threadIdx.x >> 5);
@@ -178,6 +180,7 @@ combine_bwd_peer_kernel(const float* __restrict__ gates, const int32_t* __restri
                         PeerTable d_eo, PeerTable eo, float* __restrict__ dgates, int S, int Sp, int M, int C, int E, int LE,
                         int my_rank) {
   using P = PackP<T, N>;
+  chain_enter();
   const int lane = threadIdx.x & 31;
   const int row_vecs = M / N;
   const long long gw = (long long)blockIdx.x * kP2PWarps + (threadIdx.x >> 5);
@@ -262,6 +265,7 @@ __device__ __forceinline__ unsigned long long globaltimer_ns() {
 // so that the same launch can be replayed from a CUDA graph.
 __global__ void p2p_barrier_kernel(PeerTable flags, int W, int my_rank, unsigned epoch, unsigned long long timeout_ns,
                                    int* __restrict__ status, unsigned* __restrict__ epoch_counter) {
+  chain_enter();   // the kernels before this one on the stream have completed: their peer stores are what the flag announces
   const int i = threadIdx.x;
   if (epoch_counter) epoch = *epoch_counter + 1;
   __syncwarp();
@@ -351,10 +355,10 @@ static int combine_p2p_t(const float* gates, const int32_t* idx_loc, const PeerT
   constexpr int N = 16 / sizeof(T);
   ProfScope prof("combine_rows_peer_kernel", st);
   if (k == 1)
-    combine_rows_peer_kernel<T, N, 1><<<p2p_grid(S), kP2PThreads, 0, st>>>(gates, idx_loc, t, static_cast<T*>(out), S, Sp,
+    launch_chained(combine_rows_peer_kernel<T, N, 1>, p2p_grid(S), kP2PThreads, 0, st, gates, idx_loc, t, static_cast<T*>(out), S, Sp,
                                                                          M, C, E, LE, rank);
   else
-    combine_rows_peer_kernel<T, N, 2><<<p2p_grid(S), kP2PThreads, 0, st>>>(gates, idx_loc, t, static_cast<T*>(out), S, Sp,
+    launch_chained(combine_rows_peer_kernel<T, N, 2>, p2p_grid(S), kP2PThreads, 0, st, gates, idx_loc, t, static_cast<T*>(out), S, Sp,
                                                                          M, C, E, LE, rank);
   return launch_status("combine_rows_peer_kernel");
 }
@@ -367,8 +371,8 @@ static int combine_bwd_p2p_t(const float* gates, const int32_t* idx_loc, const v
   constexpr int N = 16 / sizeof(T);
   ProfScope prof("combine_bwd_peer_kernel", st);
 #define LANCET_CB(KK, PP)                                                                                                      \
-  combine_bwd_peer_kernel<T, N, KK, PP><<<p2p_grid(S), kP2PThreads, 0, st>>>(gates, idx_loc, static_cast<const T*>(dout), td, \
-                                                                            te, dgates, S, Sp, M, C, E, LE, rank)
+  launch_chained(combine_bwd_peer_kernel<T, N, KK, PP>, p2p_grid(S), kP2PThreads, 0, st, gates, idx_loc,                      \
+                 static_cast<const T*>(dout), td, te, dgates, S, Sp, M, C, E, LE, rank)
   if (k == 1) {
     if (part == 0) LANCET_CB(1, 0);
     else if (part == 1) LANCET_CB(1, 1);
@@ -434,7 +438,8 @@ int lancet_p2p_barrier(void* const* peer_flags, int W, int rank, unsigned epoch,
   PeerTable t;
   for (int i = 0; i < kMaxPeers; ++i) t.ptr[i] = i < W ? peer_flags[i] : nullptr;
   for (int i = 0; i < W; ++i) LANCET_REQUIRE(t.ptr[i], LANCET_ERR_NULL, "lancet_p2p_barrier: flag pointer %d is null", i);
-  p2p_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(t, W, rank, epoch, timeout_ns, status, nullptr);
+  launch_chained(p2p_barrier_kernel, 1, 32, 0, static_cast<cudaStream_t>(stream), t, W, rank, epoch, timeout_ns, status,
+                 static_cast<unsigned*>(nullptr));
   return launch_status("p2p_barrier_kernel");
 }
 
@@ -448,7 +453,7 @@ int lancet_p2p_barrier_counted(void* const* peer_flags, int W, int rank, uint32_
   PeerTable t;
   for (int i = 0; i < kMaxPeers; ++i) t.ptr[i] = i < W ? peer_flags[i] : nullptr;
   for (int i = 0; i < W; ++i) LANCET_REQUIRE(t.ptr[i], LANCET_ERR_NULL, "lancet_p2p_barrier_counted: flag pointer %d is null", i);
-  p2p_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(t, W, rank, 0u, timeout_ns, status, epoch_counter);
+  launch_chained(p2p_barrier_kernel, 1, 32, 0, static_cast<cudaStream_t>(stream), t, W, rank, 0u, timeout_ns, status, epoch_counter);
   return launch_status("p2p_barrier_kernel");
 }
 
@@ -508,10 +513,10 @@ int lancet_moe_dispatch_chunked_p2p(const void* x, const void* gate, int gate_dt
   const int32_t* used = capused_chain + (size_t)n_chunks * E;
   ProfScope prof("dispatch_rows_peer_kernel", st);
   if (k == 1)
-    dispatch_rows_peer_kernel<uint4, 1><<<p2p_grid(tasks), kP2PThreads, 0, st>>>(
+    launch_chained(dispatch_rows_peer_kernel<uint4, 1>, p2p_grid(tasks), kP2PThreads, 0, st,
         idx_loc, used, static_cast<const uint4*>(x), t, tc, S, Sp > 0 ? Sp : 1, row_vecs, C, E, LE, rank, zero_tail);
   else
-    dispatch_rows_peer_kernel<uint4, 2><<<p2p_grid(tasks), kP2PThreads, 0, st>>>(
+    launch_chained(dispatch_rows_peer_kernel<uint4, 2>, p2p_grid(tasks), kP2PThreads, 0, st,
         idx_loc, used, static_cast<const uint4*>(x), t, tc, S, Sp > 0 ? Sp : 1, row_vecs, C, E, LE, rank, zero_tail);
   return launch_status("dispatch_rows_peer_kernel");
 }
@@ -637,10 +642,10 @@ int lancet_moe_dispatch_rows_p2p(const void* x, const int32_t* idx_loc, int S, i
   const int32_t* il = idx_loc + (size_t)chunk_begin * 2 * k * Sp;
   ProfScope prof("dispatch_rows_peer_kernel", st);
   if (k == 1)
-    dispatch_rows_peer_kernel<uint4, 1><<<p2p_grid(tokens), kP2PThreads, 0, st>>>(il, nullptr, xs, t, none, (int)tokens, Sp,
+    launch_chained(dispatch_rows_peer_kernel<uint4, 1>, p2p_grid(tokens), kP2PThreads, 0, st, il, nullptr, xs, t, none, (int)tokens, Sp,
                                                                                  row_vecs, C, E, LE, rank, 0);
   else
-    dispatch_rows_peer_kernel<uint4, 2><<<p2p_grid(tokens), kP2PThreads, 0, st>>>(il, nullptr, xs, t, none, (int)tokens, Sp,
+    launch_chained(dispatch_rows_peer_kernel<uint4, 2>, p2p_grid(tokens), kP2PThreads, 0, st, il, nullptr, xs, t, none, (int)tokens, Sp,
                                                                                  row_vecs, C, E, LE, rank, 0);
   return launch_status("dispatch_rows_peer_kernel");
 }
