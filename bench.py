@@ -779,7 +779,7 @@ def leg_lans(args, ctx, steps):
     launches = (L.lancet_launch_count() - l0) // steps
     ms, timing = timed_bursts(ctx, burst, steps)
     per_phase = {}
-    for ph, bpe in (("lans_phase1_kernel", 8.0), ("lans_phase2_kernel", 24.0), ("lans_phase3_kernel", 20.0)):
+    for ph, bpe in (("lans_phase1_kernel", 4.0), ("lans_phase2_kernel", 24.0), ("lans_phase3_kernel", 20.0)):
         L.lancet_profile_begin(ph.encode())
         burst()
         torch.cuda.synchronize()
@@ -813,8 +813,8 @@ def leg_lans(args, ctx, steps):
                      "traffic": 23.46 * n_el,
                      "bytes_per_launch": 24.0 * n_el, "avg_launch_us": p2["avg_launch_us"]},
         "phases": per_phase,
-        "step_hbm_frac": 52.0 * n_el / (ms / 1e3) / 1e9 / hbm_peak,
-        "step_bytes_per_element": 52.0,
+        "step_hbm_frac": 48.0 * n_el / (ms / 1e3) / 1e9 / hbm_peak,
+        "step_bytes_per_element": 48.0,
         "ms_per_step_device_step_counter": ms_dev,
     }
 

@@ -7,9 +7,11 @@
 // memory, and read `step` back from the device every call.
 //
 // Here the data dependence of the algorithm sets the passes:
-//   phase 1  reads g, p                -> ||g||, ||p||                    ( 8 B/element)
-//   phase 2  reads g, p, m, v          -> writes m, v; ||u_m||, ||u_g||   (24 B/element)
-//   phase 3  reads g, p, m, v          -> writes p                        (20 B/element)
+//   phase 1  reads g                   -> ||g||                                  ( 4 B/element)
+//   phase 2  reads g, p, m, v          -> writes m, v; ||p||, ||u_m||, ||u_g||   (24 B/element)
+//   phase 3  reads g, p, m, v          -> writes p                               (20 B/element)
+// ||g|| has to be known before anything else (the gradient is scaled by it); ||p|| is only needed by phase 3, so it is
+// summed in phase 2, which reads p anyway.
 // The update directions u_m, u_g are recomputed in phase 3 instead of being stored.  The tensor
 // table lives in device memory (no per-launch tensor limit).  Per-tensor norms are reduced in
 // a fixed order (per-chunk partial sums, then the last block to finish a tensor adds them up),
@@ -41,7 +43,7 @@ struct LansHyper {
 };
 
 struct LansLayout {
-  size_t tensors_off, part1_off, part2_off, norms_off, counters_off, bc_off, total;
+  size_t tensors_off, part1_off, part2_off, norms_off, counters_off, bc_off, map_off, total;
   long long nchunks;
 };
 
@@ -59,6 +61,7 @@ static LansLayout lans_layout(int n, const int64_t* numels) {
   L.norms_off = off;   off += up256((size_t)n * sizeof(float4));
   L.counters_off = off; off += up256((size_t)n * 2 * sizeof(int));
   L.bc_off = off;       off += 256;  // 1/bias_correction1, 1/bias_correction2 when the step counter lives on the device
+  L.map_off = off;      off += up256((size_t)(nch > 0 ? nch : 1) * sizeof(int));   // tensor of every chunk
   L.total = off;
   return L;
 }
@@ -70,6 +73,13 @@ __device__ __forceinline__ int find_tensor(const LansTensor* __restrict__ t, int
     if (t[mid].chunk_begin <= chunk) lo = mid; else hi = mid - 1;
   }
   return lo;
+}
+
+// Built with the tensor table: the tensor a chunk belongs to.  A block lives for one chunk, and a binary search through
+// the table in global memory (eight dependent loads for 200 tensors) was a quarter of the life of a phase-1 block.
+__global__ void lans_chunk_map_kernel(const LansTensor* __restrict__ tensors, int n, int nchunks, int* __restrict__ map) {
+  const int chunk = blockIdx.x * blockDim.x + threadIdx.x;
+  if (chunk < nchunks) map[chunk] = find_tensor(tensors, n, chunk);
 }
 
 __device__ __forceinline__ float2 block_sum2(float a, float b) {
@@ -97,10 +107,11 @@ __device__ __forceinline__ float2 block_sum2(float a, float b) {
 }
 
 // Publishes this block's partial and, in the last block of the tensor, adds all partials in
-// chunk order and writes sqrt of the two sums to out[0], out[1].
+// chunk order and writes sqrt of the sums to out[0] (and out[1] with n_out == 2).
 __device__ __forceinline__ void finish_tensor(float2 mine, float2* __restrict__ partials, int* __restrict__ counter,
-                                              const LansTensor& T, int chunk, float* __restrict__ out) {
+                                              const LansTensor& T, int chunk, float* __restrict__ out, int n_out = 2) {
   __shared__ int is_last;
+  __syncthreads();   // a second call in the same kernel must not overwrite is_last under a thread still reading it
   if (threadIdx.x == 0) {
     partials[chunk] = mine;
     __threadfence();
@@ -119,7 +130,7 @@ __device__ __forceinline__ void finish_tensor(float2 mine, float2* __restrict__ 
   const float2 tot = block_sum2(a, b);
   if (threadIdx.x == 0) {
     out[0] = sqrtf(tot.x);
-    out[1] = sqrtf(tot.y);
+    if (n_out == 2) out[1] = sqrtf(tot.y);
     *counter = 0;  // ready for the next step
   }
 }
@@ -184,36 +195,39 @@ __device__ __forceinline__ ChunkView chunk_view(const LansTensor& T, int chunk, 
 }
 
 __global__ void __launch_bounds__(kLansThreads)
-lans_phase1_kernel(const LansTensor* __restrict__ tensors, int n, float2* __restrict__ part1, float4* __restrict__ norms,
-                   int* __restrict__ counters) {
+lans_phase1_kernel(const LansTensor* __restrict__ tensors, const int* __restrict__ chunk_map, float2* __restrict__ part1,
+                   float4* __restrict__ norms, int* __restrict__ counters) {
   const int chunk = blockIdx.x;
-  const int t = find_tensor(tensors, n, chunk);
+  const int t = chunk_map[chunk];
   const LansTensor T = tensors[t];
   const ChunkView c = chunk_view(T, chunk, false);
   const float4* g4 = reinterpret_cast<const float4*>(T.g + c.off);
-  const float4* p4 = reinterpret_cast<const float4*>(T.p + c.off);
-  float sg = 0.f, sp = 0.f;
-  float sg2 = 0.f, sp2 = 0.f;
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
   int i = threadIdx.x;
-  for (; i + kLansThreads < c.nvec; i += 2 * kLansThreads) {
-    const float4 a = g4[i], b = p4[i], a2 = g4[i + kLansThreads], b2 = p4[i + kLansThreads];
-    sg += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
-    sp += b.x * b.x + b.y * b.y + b.z * b.z + b.w * b.w;
-    sg2 += a2.x * a2.x + a2.y * a2.y + a2.z * a2.z + a2.w * a2.w;
-    sp2 += b2.x * b2.x + b2.y * b2.y + b2.z * b2.z + b2.w * b2.w;
+  // a full chunk is eight vectors per thread: all eight loads are issued before the first sum (a block lives for one
+  // chunk only, so what it has in flight at once is what hides the memory latency)
+  for (; i + 7 * kLansThreads < c.nvec; i += 8 * kLansThreads) {
+    float4 a[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) a[u] = __ldcs(g4 + i + u * kLansThreads);
+#pragma unroll
+    for (int u = 0; u < 8; u += 4) {
+      s0 += a[u].x * a[u].x + a[u].y * a[u].y + a[u].z * a[u].z + a[u].w * a[u].w;
+      s1 += a[u + 1].x * a[u + 1].x + a[u + 1].y * a[u + 1].y + a[u + 1].z * a[u + 1].z + a[u + 1].w * a[u + 1].w;
+      s2 += a[u + 2].x * a[u + 2].x + a[u + 2].y * a[u + 2].y + a[u + 2].z * a[u + 2].z + a[u + 2].w * a[u + 2].w;
+      s3 += a[u + 3].x * a[u + 3].x + a[u + 3].y * a[u + 3].y + a[u + 3].z * a[u + 3].z + a[u + 3].w * a[u + 3].w;
+    }
   }
   for (; i < c.nvec; i += kLansThreads) {
-    const float4 a = g4[i], b = p4[i];
-    sg += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
-    sp += b.x * b.x + b.y * b.y + b.z * b.z + b.w * b.w;
+    const float4 a = g4[i];
+    s0 += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
   }
   for (int e = c.nvec * 4 + threadIdx.x; e < c.n; e += kLansThreads) {
-    const float a = T.g[c.off + e], b = T.p[c.off + e];
-    sg += a * a;
-    sp += b * b;
+    const float a = T.g[c.off + e];
+    s0 += a * a;
   }
-  const float2 mine = block_sum2(sg + sg2, sp + sp2);
-  finish_tensor(mine, part1, counters + 2 * t, T, chunk, reinterpret_cast<float*>(norms + t));
+  const float2 mine = block_sum2((s0 + s1) + (s2 + s3), 0.f);
+  finish_tensor(mine, part1, counters + 2 * t, T, chunk, reinterpret_cast<float*>(norms + t), 1);
 }
 
 // 1/bias_correction from a step counter that lives on the device (a float scalar, as the reference's op takes it:
@@ -250,10 +264,11 @@ __device__ __forceinline__ void phase2_vec(const float4& g, const float4& p, flo
 // cannot be moved below the next iteration's loads by the compiler (the arrays may alias as far as it knows), so
 // with one vector per array a thread had 64 bytes in flight and the kernel sat at 0.82 of the copy bandwidth.
 __global__ void __launch_bounds__(kLansThreads)
-lans_phase2_kernel(const LansTensor* __restrict__ tensors, int n, LansHyper h, const float* __restrict__ inv_bc_dev,
-                   float2* __restrict__ part2, float4* __restrict__ norms, int* __restrict__ counters) {
+lans_phase2_kernel(const LansTensor* __restrict__ tensors, const int* __restrict__ chunk_map, LansHyper h,
+                   const float* __restrict__ inv_bc_dev, float2* __restrict__ part1, float2* __restrict__ part2,
+                   float4* __restrict__ norms, int* __restrict__ counters) {
   const int chunk = blockIdx.x;
-  const int t = find_tensor(tensors, n, chunk);
+  const int t = chunk_map[chunk];
   const LansTensor T = tensors[t];
   const ChunkView c = chunk_view(T, chunk, true);
   load_bc(h, inv_bc_dev);
@@ -262,12 +277,14 @@ lans_phase2_kernel(const LansTensor* __restrict__ tensors, int n, LansHyper h, c
   const float4* p4 = reinterpret_cast<const float4*>(T.p + c.off);
   float4* m4 = reinterpret_cast<float4*>(T.m + c.off);
   float4* v4 = reinterpret_cast<float4*>(T.v + c.off);
-  float sm = 0.f, sq = 0.f, sm2 = 0.f, sq2 = 0.f;
+  float sm = 0.f, sq = 0.f, sm2 = 0.f, sq2 = 0.f, sp = 0.f, sp2 = 0.f;
   int i = threadIdx.x;
   for (; i + kLansThreads < c.nvec; i += 2 * kLansThreads) {
     const int j = i + kLansThreads;
     const float4 ga = __ldcs(g4 + i), pa = __ldcs(p4 + i), gb = __ldcs(g4 + j), pb = __ldcs(p4 + j);
     float4 ma = __ldcs(m4 + i), va = __ldcs(v4 + i), mb = __ldcs(m4 + j), vb = __ldcs(v4 + j);
+    sp += pa.x * pa.x + pa.y * pa.y + pa.z * pa.z + pa.w * pa.w;
+    sp2 += pb.x * pb.x + pb.y * pb.y + pb.z * pb.z + pb.w * pb.w;
     phase2_vec(ga, pa, ma, va, gnorm, h, sm, sq);
     phase2_vec(gb, pb, mb, vb, gnorm, h, sm2, sq2);
     m4[i] = ma;
@@ -278,20 +295,26 @@ lans_phase2_kernel(const LansTensor* __restrict__ tensors, int n, LansHyper h, c
   for (; i < c.nvec; i += kLansThreads) {
     const float4 g = g4[i], p = p4[i];
     float4 m = m4[i], v = v4[i];
+    sp += p.x * p.x + p.y * p.y + p.z * p.z + p.w * p.w;
     phase2_vec(g, p, m, v, gnorm, h, sm, sq);
     m4[i] = m;
     v4[i] = v;
   }
   for (int e = c.nvec * 4 + threadIdx.x; e < c.n; e += kLansThreads) {
     float m = T.m[c.off + e], v = T.v[c.off + e], um, ug;
-    lans_directions(T.g[c.off + e], T.p[c.off + e], m, v, gnorm, h, um, ug);
+    const float p = T.p[c.off + e];
+    sp += p * p;
+    lans_directions(T.g[c.off + e], p, m, v, gnorm, h, um, ug);
     sm += um * um;
     sq += ug * ug;
     T.m[c.off + e] = m;
     T.v[c.off + e] = v;
   }
   const float2 mine = block_sum2(sm + sm2, sq + sq2);
+  const float2 minep = block_sum2(sp + sp2, 0.f);
   finish_tensor(mine, part2, counters + 2 * t + 1, T, chunk, reinterpret_cast<float*>(norms + t) + 2);
+  // ||p||: the partial array and the ticket counter of phase 1 are free again (its last block reset the counter)
+  finish_tensor(minep, part1, counters + 2 * t, T, chunk, reinterpret_cast<float*>(norms + t) + 1, 1);
 }
 
 __device__ __forceinline__ void phase3_vec(const float4& g, float4& p, const float4& m, const float4& v, float inv_gn,
@@ -304,10 +327,10 @@ __device__ __forceinline__ void phase3_vec(const float4& g, float4& p, const flo
 }
 
 __global__ void __launch_bounds__(kLansThreads)
-lans_phase3_kernel(const LansTensor* __restrict__ tensors, int n, LansHyper h, const float* __restrict__ inv_bc_dev,
-                   const float4* __restrict__ norms) {
+lans_phase3_kernel(const LansTensor* __restrict__ tensors, const int* __restrict__ chunk_map, LansHyper h,
+                   const float* __restrict__ inv_bc_dev, const float4* __restrict__ norms) {
   const int chunk = blockIdx.x;
-  const int t = find_tensor(tensors, n, chunk);
+  const int t = chunk_map[chunk];
   const LansTensor T = tensors[t];
   const ChunkView c = chunk_view(T, chunk, true);
   load_bc(h, inv_bc_dev);
@@ -402,6 +425,11 @@ static int lans_impl(void* ws, size_t ws_bytes, int n_tensors, const int64_t* nu
     LANCET_CUDA(cudaMemsetAsync(base + L.counters_off, 0, (size_t)n_tensors * 2 * sizeof(int), stream));
     // tensors without elements never finish a block: their norms stay defined as zero
     LANCET_CUDA(cudaMemsetAsync(base + L.norms_off, 0, (size_t)n_tensors * sizeof(float4), stream));
+    if (L.nchunks > 0) {
+      lans_chunk_map_kernel<<<(int)((L.nchunks + 255) / 256), 256, 0, stream>>>(d_tensors, n_tensors, (int)L.nchunks,
+                                                                               reinterpret_cast<int*>(base + L.map_off));
+      if (int st = launch_status("lans_chunk_map_kernel")) return st;
+    }
   }
   if (L.nchunks == 0) return LANCET_OK;
   LansHyper h;
@@ -425,20 +453,21 @@ static int lans_impl(void* ws, size_t ws_bytes, int n_tensors, const int64_t* nu
   float2* part2 = reinterpret_cast<float2*>(base + L.part2_off);
   float4* norms = reinterpret_cast<float4*>(base + L.norms_off);
   int* counters = reinterpret_cast<int*>(base + L.counters_off);
+  const int* chunk_map = reinterpret_cast<const int*>(base + L.map_off);
   const int grid = (int)L.nchunks;
   {
     ProfScope prof("lans_phase1_kernel", stream);
-    lans_phase1_kernel<<<grid, kLansThreads, 0, stream>>>(d_tensors, n_tensors, part1, norms, counters);
+    lans_phase1_kernel<<<grid, kLansThreads, 0, stream>>>(d_tensors, chunk_map, part1, norms, counters);
   }
   if (int st = launch_status("lans_phase1_kernel")) return st;
   {
     ProfScope prof("lans_phase2_kernel", stream);
-    lans_phase2_kernel<<<grid, kLansThreads, 0, stream>>>(d_tensors, n_tensors, h, inv_bc_dev, part2, norms, counters);
+    lans_phase2_kernel<<<grid, kLansThreads, 0, stream>>>(d_tensors, chunk_map, h, inv_bc_dev, part1, part2, norms, counters);
   }
   if (int st = launch_status("lans_phase2_kernel")) return st;
   {
     ProfScope prof("lans_phase3_kernel", stream);
-    lans_phase3_kernel<<<grid, kLansThreads, 0, stream>>>(d_tensors, n_tensors, h, inv_bc_dev, norms);
+    lans_phase3_kernel<<<grid, kLansThreads, 0, stream>>>(d_tensors, chunk_map, h, inv_bc_dev, norms);
   }
   return launch_status("lans_phase3_kernel");
 }
