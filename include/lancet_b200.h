@@ -416,6 +416,20 @@ int lancet_moe_combine_bwd_part_p2p(const void* dout, const void* gates_s, const
                                     void* const* peer_d_expert_out, void* const* peer_expert_out, void* dgates_s, int S,
                                     int M, int C, int LE, int W, int rank, int k, int n_chunks, int dtype, int part,
                                     lancet_stream_t stream);
+/* Softmax cross-entropy of the language-model head over a padded vocabulary; replaces the log_softmax + nll_loss pair the
+ * reference's benchmark models end in (models/benchmark/raf/raf_bencher.py:84; raf.op.nll_loss and nll_loss_dpred,
+ * src/op/declare/loss.cc:55-92) without materialising float32 logits or log-probabilities.
+ * logits [rows][ld] (ld >= vocab elements between rows; columns >= vocab are padding and never read), target [rows] int64
+ * (negative = ignored row), loss_rows[r] = logsumexp(row r) - logits[r][target[r]] (0 for ignored rows), lse_rows[r] kept for
+ * the backward pass. */
+int lancet_softmax_xent_fwd(const void* logits, long long ld, const long long* target, int rows, int vocab, int dtype,
+                            float* loss_rows, float* lse_rows, lancet_stream_t stream);
+/* dlogits[r][j] = (softmax(row r)[j] - [j == target[r]]) * (*grad_out) * scale for j < vocab; 0 for vocab <= j < cols and in
+ * ignored rows.  grad_out is a float32 scalar in device memory (nullptr = 1): no host round trip; scale is the host-side
+ * reduction factor (1 / number of live rows for a mean).  dlogits [rows][ldd] has the logits' type. */
+int lancet_softmax_xent_bwd(const void* logits, long long ld, const long long* target, int rows, int vocab, int cols, int dtype,
+                            const float* lse_rows, const float* grad_out, float scale, void* dlogits, long long ldd,
+                            lancet_stream_t stream);
 /* Bias gradient of an expert layer: db[e][:] = sum over the groups of expert e and their live rows of
  * dY[g][r][:]  (dY [groups][C][N], db [LE][N]); the reference gets it from the autodiff of nn.Linear's
  * bias add (a `sum` over rows).  ws: lancet_grouped_bias_grad_workspace_bytes(LE, N) bytes. */

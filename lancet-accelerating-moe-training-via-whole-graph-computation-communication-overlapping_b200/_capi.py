@@ -156,6 +156,9 @@ SIGNATURES = {
     "lancet_set_cta_limits": (c_int, [c_int, c_int]),
     "lancet_set_gemm_paired": (c_int, [c_int]),
     "lancet_set_chained_launch": (c_int, [c_int]),
+    "lancet_softmax_xent_fwd": (c_int, [c_void_p, ctypes.c_longlong, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "lancet_softmax_xent_bwd": (c_int, [c_void_p, ctypes.c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                                        ctypes.c_float, c_void_p, ctypes.c_longlong, c_void_p]),
     "lancet_peer_copy": (c_int, [c_void_p, c_void_p, c_size_t, c_void_p]),
     "lancet_lans_dev_step": (c_int, [c_void_p, c_size_t, c_int, ctypes.POINTER(c_i64), ctypes.POINTER(c_void_p),
                                      ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p), c_int,

@@ -252,3 +252,29 @@ class MoE(torch.nn.Module):
         y = _MoEBlockFunction.apply(x.reshape(-1, shape[-1]), ln.weight, ln.bias, self.wg.weight, self.w1, self.b1, self.w2,
                                     self.b2, self)
         return y.reshape(shape)
+
+
+class _SoftmaxCrossEntropy(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, target, vocab):
+        loss_rows, lse = ops.softmax_xent_fwd(logits, target, vocab)
+        live = (target >= 0).sum()
+        ctx.save_for_backward(logits, target, lse, live)
+        ctx.vocab = vocab
+        return loss_rows.sum() / live.clamp(min=1)
+
+    @staticmethod
+    def backward(ctx, gout):
+        logits, target, lse, live = ctx.saved_tensors
+        # the mean's 1/live factor stays on the device with the upstream gradient: no host round trip
+        g = (gout.float() / live.clamp(min=1)).reshape(1).contiguous()
+        return ops.softmax_xent_bwd(logits, target, ctx.vocab, lse, g, 1.0), None, None
+
+
+def softmax_cross_entropy(logits, target, vocab=None):
+    """Mean cross-entropy of `logits` [rows, cols] (float32, float16 or bfloat16; columns from `vocab` on are padding) against
+    `target` [rows] int64 (negative = ignored), computed by the library's two kernels on the 16-bit logits themselves: the
+    language-model head of the reference's benchmark models (log_softmax + nll_loss, models/benchmark/raf/raf_bencher.py:84)
+    without float32 copies of the [tokens, vocabulary] matrix."""
+    return _SoftmaxCrossEntropy.apply(logits, target, logits.shape[1] if vocab is None else vocab)
+

@@ -7,7 +7,7 @@ import torch
 import torch.nn.functional as F
 
 from . import _capi
-from .autograd import DeferredGrads, DeferredLinear, MoE
+from .autograd import DeferredGrads, DeferredLinear, MoE, softmax_cross_entropy
 from .ops import LansState, gemm_status, lans
 
 
@@ -85,7 +85,11 @@ class GPTMoE(torch.nn.Module):
             for b in self.blocks:
                 x = b(x)
             logits = F.linear(self.ln(x), self.emb.weight)         # tied output embedding
-        return F.cross_entropy(logits[:, :-1, :self.vocab].float().reshape(-1, self.vocab), ids[:, 1:].reshape(-1))
+        # next-token loss on the padded 16-bit logits themselves: position t is scored against token t+1, the last
+        # position of every sequence is ignored, the padded vocabulary columns are never read
+        target = torch.full_like(ids, -1)
+        target[:, :-1] = ids[:, 1:]
+        return softmax_cross_entropy(logits.view(-1, logits.shape[-1]), target.view(-1), self.vocab)
 
     def close(self):
         for b in self.blocks:

@@ -280,6 +280,34 @@ def gate_softmax_bwd(probs, dprobs, wg, dtype):
     return dlogits, dh
 
 
+def softmax_xent_fwd(logits, target, vocab):
+    """Row losses and log-sum-exp of a [rows, cols >= vocab] logits matrix (columns past `vocab` are padding); target int64
+    [rows], negative = ignored.  Returns (loss_rows, lse_rows), float32."""
+    _require_cuda(logits, target)
+    if logits.dim() != 2 or logits.stride(1) != 1 or target.dtype != torch.int64 or not target.is_contiguous():
+        raise TypeError("softmax_xent_fwd: logits must be a row-major matrix and target a contiguous int64 vector")
+    rows = logits.shape[0]
+    loss = torch.empty((rows,), dtype=torch.float32, device=logits.device)
+    lse = torch.empty((rows,), dtype=torch.float32, device=logits.device)
+    check(_capi.lib().lancet_softmax_xent_fwd(_ptr(logits), logits.stride(0), _ptr(target), rows, vocab, _dt(logits), _ptr(loss),
+                                              _ptr(lse), _stream(logits)))
+    return loss, lse
+
+
+def softmax_xent_bwd(logits, target, vocab, lse, grad_out, scale):
+    """Gradient of sum(loss_rows) * grad_out * scale with respect to the logits, in the logits' type and shape; padded
+    columns and ignored rows are zero.  grad_out: float32 scalar tensor on the device (or None for 1)."""
+    _require_cuda(logits, target, lse)
+    rows, cols = logits.shape
+    dx = torch.empty((rows, cols), dtype=logits.dtype, device=logits.device)
+    if grad_out is not None and (grad_out.dtype != torch.float32 or grad_out.numel() != 1 or not grad_out.is_cuda):
+        raise TypeError("softmax_xent_bwd: grad_out must be a float32 scalar on the device")
+    check(_capi.lib().lancet_softmax_xent_bwd(_ptr(logits), logits.stride(0), _ptr(target), rows, vocab, cols, _dt(logits), _ptr(lse),
+                                              _ptr(grad_out) if grad_out is not None else None, float(scale), _ptr(dx),
+                                              dx.stride(0), _stream(logits)))
+    return dx
+
+
 ACT = {None: 0, "none": 0, "relu": 1, "gelu": 2, "gelu_tanh": 3}
 _gemm_status = {}
 
