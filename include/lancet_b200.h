@@ -416,6 +416,19 @@ int lancet_moe_combine_bwd_part_p2p(const void* dout, const void* gates_s, const
                                     void* const* peer_d_expert_out, void* const* peer_expert_out, void* dgates_s, int S,
                                     int M, int C, int LE, int W, int rank, int k, int n_chunks, int dtype, int part,
                                     lancet_stream_t stream);
+/* Layer normalisation over the last axis (raf.op.layer_norm / layer_norm_dx of the reference, src/op/declare/nn.cc; one of the
+ * non-MoE operators next to the MoE layer that the reference's forward partition splits into token chunks,
+ * src/pass/dist_optimization/partition_exprs.cc:1709-1795).  x [rows][M] float32, M a multiple of 128 up to 2048 in
+ * {128,256,512,768,1024,1536,2048}; y in out_dtype (float32, or the 16-bit type the next GEMM reads: no cast pass);
+ * mean, rstd [rows] float32 are kept for the backward pass.  A row's result depends on that row only. */
+int lancet_layer_norm_fwd(const float* x, const float* gamma, const float* beta, void* y, int out_dtype, float* mean, float* rstd,
+                          int rows, int M, float eps, lancet_stream_t stream);
+/* dx [rows][M] float32, dgamma, dbeta [M] float32 from dy [rows][M] in dy_dtype; ws: lancet_layer_norm_workspace_bytes(rows, M)
+ * bytes (partial column sums; they are added in a fixed order: reproducible). */
+size_t lancet_layer_norm_workspace_bytes(int rows, int M);
+int lancet_layer_norm_bwd(const float* x, const void* dy, int dy_dtype, const float* gamma, const float* mean, const float* rstd,
+                          float* dx, float* dgamma, float* dbeta, int rows, int M, void* ws, size_t ws_bytes,
+                          lancet_stream_t stream);
 /* Softmax cross-entropy of the language-model head over a padded vocabulary; replaces the log_softmax + nll_loss pair the
  * reference's benchmark models end in (models/benchmark/raf/raf_bencher.py:84; raf.op.nll_loss and nll_loss_dpred,
  * src/op/declare/loss.cc:55-92) without materialising float32 logits or log-probabilities.

@@ -156,6 +156,11 @@ SIGNATURES = {
     "lancet_set_cta_limits": (c_int, [c_int, c_int]),
     "lancet_set_gemm_paired": (c_int, [c_int]),
     "lancet_set_chained_launch": (c_int, [c_int]),
+    "lancet_layer_norm_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, ctypes.c_float,
+                                      c_void_p]),
+    "lancet_layer_norm_workspace_bytes": (ctypes.c_size_t, [c_int, c_int]),
+    "lancet_layer_norm_bwd": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                      c_int, c_void_p, ctypes.c_size_t, c_void_p]),
     "lancet_softmax_xent_fwd": (c_int, [c_void_p, ctypes.c_longlong, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "lancet_softmax_xent_bwd": (c_int, [c_void_p, ctypes.c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
                                         ctypes.c_float, c_void_p, ctypes.c_longlong, c_void_p]),

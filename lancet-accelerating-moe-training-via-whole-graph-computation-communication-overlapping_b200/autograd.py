@@ -278,3 +278,36 @@ def softmax_cross_entropy(logits, target, vocab=None):
     without float32 copies of the [tokens, vocabulary] matrix."""
     return _SoftmaxCrossEntropy.apply(logits, target, logits.shape[1] if vocab is None else vocab)
 
+
+class _LayerNormFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias, eps, out_dtype):
+        shape = x.shape
+        x2 = x.reshape(-1, shape[-1]).float()
+        y, mean, rstd = ops.layer_norm_fwd(x2, weight.float(), bias.float(), eps, out_dtype)
+        ctx.save_for_backward(x2, weight, mean, rstd)
+        ctx.shape, ctx.in_dtype = shape, x.dtype
+        return y.view(shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, weight, mean, rstd = ctx.saved_tensors
+        dx, dw, db = ops.layer_norm_bwd(x2, dy.reshape(x2.shape), weight.float(), mean, rstd)
+        return dx.view(ctx.shape).to(ctx.in_dtype), dw.to(weight.dtype), db.to(weight.dtype), None, None
+
+
+class LayerNorm(torch.nn.Module):
+    """Layer normalisation over the last axis on the library's kernels (parameters named as torch.nn.LayerNorm's).  Under
+    CUDA autocast the normalised rows come out in the autocast type, which is what the following GEMM reads: the separate
+    float32 -> 16-bit pass disappears, and the backward pass takes the 16-bit gradient as it is."""
+
+    def __init__(self, normalized_shape, eps=1e-5):
+        super().__init__()
+        self.weight = torch.nn.Parameter(torch.ones(normalized_shape))
+        self.bias = torch.nn.Parameter(torch.zeros(normalized_shape))
+        self.eps = eps
+
+    def forward(self, x):
+        out = torch.get_autocast_dtype("cuda") if torch.is_autocast_enabled("cuda") else torch.float32
+        return _LayerNormFunction.apply(x, self.weight, self.bias, self.eps, out)
+

@@ -1,14 +1,19 @@
 """GPT-2-style decoder with an expert-parallel MoE block in every other layer: the model family of the
 reference's benchmark (gpt2_moe_nl12_m1024_nh16_sl512, models/benchmark/pytorch/nlp.py:303-316,
-`moe_expert_interval=2`, `num_experts = 2 * world_size`, models/benchmark_raf.py:53).  Attention, layer norm,
-embeddings and the loss are plain torch modules (outside the hot path this library implements); the MoE
-blocks run on the library's fused layer, the optimizer step on its LANS op."""
+`moe_expert_interval=2`, `num_experts = 2 * world_size`, models/benchmark_raf.py:53).  Attention and the
+embeddings are plain torch modules (outside the hot path this library implements); the MoE blocks run on the
+library's fused layer, layer norm and the loss on its kernels, the optimizer step on its LANS op."""
 import torch
 import torch.nn.functional as F
 
 from . import _capi
-from .autograd import DeferredGrads, DeferredLinear, MoE, softmax_cross_entropy
+from .autograd import DeferredGrads, DeferredLinear, LayerNorm, MoE, softmax_cross_entropy
 from .ops import LansState, gemm_status, lans
+
+
+def _norm(m):
+    """The library's layer norm where its kernels take the width (a multiple of 128 up to 2048), torch's otherwise."""
+    return LayerNorm(m) if m in (128, 256, 512, 768, 1024, 1536, 2048) else torch.nn.LayerNorm(m)
 
 
 class Attention(torch.nn.Module):
@@ -28,7 +33,7 @@ class Attention(torch.nn.Module):
 class Block(torch.nn.Module):
     def __init__(self, m, nh, ffn, linear=torch.nn.Linear, fused_moe=False):
         super().__init__()
-        self.ln1, self.ln2 = torch.nn.LayerNorm(m), torch.nn.LayerNorm(m)
+        self.ln1, self.ln2 = _norm(m), _norm(m)
         self.attn = Attention(m, nh, linear)
         self.ffn = ffn
         self.fused_moe = fused_moe and isinstance(ffn, MoE)
@@ -67,7 +72,7 @@ class GPTMoE(torch.nn.Module):
                                           linear(ffn_dim, m))
             blocks.append(Block(m, nh, ffn, linear, fused_moe=pipeline))
         self.blocks = torch.nn.ModuleList(blocks)
-        self.ln = torch.nn.LayerNorm(m)
+        self.ln = _norm(m)
         torch.nn.init.normal_(self.emb.weight, std=0.02)
         torch.nn.init.normal_(self.pos.weight, std=0.01)
         self.to(device)

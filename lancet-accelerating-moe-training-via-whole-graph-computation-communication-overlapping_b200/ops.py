@@ -280,6 +280,36 @@ def gate_softmax_bwd(probs, dprobs, wg, dtype):
     return dlogits, dh
 
 
+def layer_norm_fwd(x, weight, bias, eps=1e-5, out_dtype=torch.float32):
+    """`raf.op.layer_norm` over the last axis of float32 rows [rows, M]; returns (y in out_dtype, mean, rstd)."""
+    _require_cuda(x, weight, bias)
+    if x.dtype != torch.float32 or weight.dtype != torch.float32 or bias.dtype != torch.float32:
+        raise TypeError("layer_norm_fwd: rows, weight and bias must be float32")
+    x = x.contiguous()
+    rows, M = x.shape
+    y = torch.empty((rows, M), dtype=out_dtype, device=x.device)
+    mean = torch.empty((rows,), dtype=torch.float32, device=x.device)
+    rstd = torch.empty((rows,), dtype=torch.float32, device=x.device)
+    check(_capi.lib().lancet_layer_norm_fwd(_ptr(x), _ptr(weight), _ptr(bias), _ptr(y), _DT[out_dtype], _ptr(mean), _ptr(rstd), rows, M,
+                                            float(eps), _stream(x)))
+    return y, mean, rstd
+
+
+def layer_norm_bwd(x, dy, weight, mean, rstd):
+    """Returns (dx float32 [rows, M], dweight [M], dbias [M]) of `layer_norm_fwd`; dy in float32 or a 16-bit type."""
+    _require_cuda(x, dy, weight, mean, rstd)
+    x, dy = x.contiguous(), dy.contiguous()
+    rows, M = x.shape
+    dx = torch.empty_like(x)
+    dw = torch.empty((M,), dtype=torch.float32, device=x.device)
+    db = torch.empty((M,), dtype=torch.float32, device=x.device)
+    L = _capi.lib()
+    ws = workspace(x.device, L.lancet_layer_norm_workspace_bytes(rows, M), "layer_norm")
+    check(L.lancet_layer_norm_bwd(_ptr(x), _ptr(dy), _dt(dy), _ptr(weight), _ptr(mean), _ptr(rstd), _ptr(dx), _ptr(dw), _ptr(db), rows,
+                                  M, _ptr(ws), ws.numel(), _stream(x)))
+    return dx, dw, db
+
+
 def softmax_xent_fwd(logits, target, vocab):
     """Row losses and log-sum-exp of a [rows, cols >= vocab] logits matrix (columns past `vocab` are padding); target int64
     [rows], negative = ignored.  Returns (loss_rows, lse_rows), float32."""
