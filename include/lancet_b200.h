@@ -433,7 +433,7 @@ int lancet_layer_norm_bwd(const float* x, const void* dy, int dy_dtype, const fl
  * reference's benchmark models end in (models/benchmark/raf/raf_bencher.py:84; raf.op.nll_loss and nll_loss_dpred,
  * src/op/declare/loss.cc:55-92) without materialising float32 logits or log-probabilities.
  * logits [rows][ld] (ld >= vocab elements between rows; columns >= vocab are padding and never read), target [rows] int64
- * (negative = ignored row), loss_rows[r] = logsumexp(row r) - logits[r][target[r]] (0 for ignored rows), lse_rows[r] kept for
+ * (negative or >= vocab = ignored row), loss_rows[r] = logsumexp(row r) - logits[r][target[r]] (0 for ignored rows), lse_rows[r] kept for
  * the backward pass. */
 int lancet_softmax_xent_fwd(const void* logits, long long ld, const long long* target, int rows, int vocab, int dtype,
                             float* loss_rows, float* lse_rows, lancet_stream_t stream);

@@ -15,7 +15,6 @@ namespace lancet {
 
 constexpr int kLnWarps = 8;
 constexpr int kLnThreads = kLnWarps * 32;
-constexpr int kLnMaxVpl = 16;   // float4 vectors per lane held in registers: rows of up to 2048 elements
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

@@ -364,3 +364,28 @@ def test_scatter_with_an_existing_routing_table():
     used = plan.capused.cpu().numpy()[-1]
     for e in range(E):
         assert (oh[e, used[e]:] == 0).all()
+
+
+def test_chained_and_plain_launches_give_the_same_bits():
+    """lancet_set_chained_launch: programmatic stream serialization only overlaps launch latency and drain."""
+    from lancet_b200 import _capi
+    rng = np.random.default_rng(5)
+    S, E, M = 4096, 8, 256
+    x = torch.from_numpy(rng.standard_normal((S, M)).astype(np.float32)).half().to(DEV)
+    gate = torch.softmax(torch.from_numpy(rng.standard_normal((S, E)).astype(np.float32)), dim=1).to(DEV)
+    used = torch.zeros(E, dtype=torch.int32, device=DEV)
+    outs = []
+    try:
+        for on in (1, 0, 1):
+            _capi.check(_capi.lib().lancet_set_chained_launch(on))
+            for _ in range(3):          # back-to-back steps: the next gate starts while the previous combine drains
+                enc = LB.moe_encode(x, gate, used, 1.25, k=2)
+                dec = LB.moe_decode(enc[4], enc[0], enc[1])
+            torch.cuda.synchronize()
+            outs.append([t.clone() for t in enc] + [dec.clone()])
+    finally:
+        _capi.check(_capi.lib().lancet_set_chained_launch(1))
+    for other in outs[1:]:
+        for a, b in zip(outs[0], other):
+            assert torch.equal(a, b)
+
