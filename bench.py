@@ -281,6 +281,25 @@ def cpu_vectorised_sample(world=1, repeats=3):
             "sample": "all %d tokens of one rank, vectorised NumPy encode+decode, median of %d" % (S_TOKENS, repeats)}
 
 
+def cpu_lans_sample():
+    """One LANS step of the NumPy float32 port on the eight tensors of one transformer layer of the bench's list
+    (12.6 M elements, a few seconds): the CPU figure next to the LANS leg, a reported baseline."""
+    from oracle import lans_oracle
+    shapes = lans_shapes(1)[2:10]
+    rng = np.random.default_rng(0)
+    p = [rng.normal(0, 0.02, s).astype(np.float32) for s in shapes]
+    g = [rng.normal(0, 1e-3, s).astype(np.float32) for s in shapes]
+    m = [rng.normal(0, 1e-4, s).astype(np.float32) for s in shapes]
+    v = [rng.uniform(0, 1e-6, s).astype(np.float32) for s in shapes]
+    n_el = sum(a.size for a in p)
+    t0 = time.perf_counter()
+    lans_oracle.lans_step(g, p, m, v, step=10)
+    dt = time.perf_counter() - t0
+    return {"value": n_el / dt, "unit": "elements/s", "cores": 1, "kind": "port",
+            "sample": "one step over the %d tensors of one transformer layer of the list, %.1f M elements, NumPy float32" % (
+                len(shapes), n_el / 1e6)}
+
+
 def run_reference_arm(args):
     """--impl reference: the reference's CPU implementation of the path (restated port; the reference
     itself has no CPU operator that builds without TVM) on the host cores.  One rank's work is timed, at any N."""
@@ -806,7 +825,9 @@ def leg_lans(args, ctx, steps):
     hbm_peak = float(peaks.get("hbm_gbs", FALLBACK_PEAKS["hbm_gbs"]))
     p2 = per_phase["lans_phase2_kernel"]
     del P, G, Mo, V, tl, state
+    cpu = None if getattr(args, "no_cpu", False) else cpu_lans_sample()
     return {
+        "cpu_baseline": cpu,
         "metric": "lans_elements_per_s", "value": n_el / (ms / 1e3), "unit": "elements/s", "ms_per_step": ms,
         "dtype": "f32", "timing": timing,
         "config": {"workload": "lans_step: %d fp32 tensors, %d elements" % (len(shapes), n_el),
