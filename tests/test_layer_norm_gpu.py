@@ -12,7 +12,8 @@ DEV = "cuda:0"
 
 
 @pytest.mark.parametrize("R,M,out_dt,dy_dt", [
-    (8192, 1024, torch.bfloat16, torch.bfloat16), (1000, 1024, torch.float32, torch.float32), (37, 128, torch.float32, torch.float32),
+    (8192, 1024, torch.bfloat16, torch.bfloat16), (65536, 1024, torch.bfloat16, torch.bfloat16),   # 268 MB of rows: larger than L2
+    (1000, 1024, torch.float32, torch.float32), (37, 128, torch.float32, torch.float32),
     (513, 768, torch.float16, torch.float16), (2048, 2048, torch.bfloat16, torch.float32), (5, 256, torch.float32, torch.bfloat16),
     (300, 1536, torch.bfloat16, torch.bfloat16), (64, 512, torch.float32, torch.float32),
 ])

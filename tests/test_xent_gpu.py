@@ -13,7 +13,8 @@ DEV = "cuda:0"
 
 
 @pytest.mark.parametrize("rows,vocab,cols,dt", [
-    (64, 1000, 1024, torch.bfloat16), (33, 50257, 50304, torch.bfloat16), (17, 777, 777, torch.float32),
+    (64, 1000, 1024, torch.bfloat16), (33, 50257, 50304, torch.bfloat16),
+    (2048, 50257, 50304, torch.bfloat16),                  # 206 MB of logits: larger than L2 (the case the profile captures) (17, 777, 777, torch.float32),
     (40, 4099, 4104, torch.float16), (8, 5, 8, torch.float32), (12, 1001, 1001, torch.bfloat16),   # odd stride: scalar path
 ])
 def test_loss_and_gradient_match_torch(rows, vocab, cols, dt):
