@@ -183,23 +183,36 @@ layer_norm_col_partial_kernel(const float* __restrict__ x, const TD* __restrict_
   }
 }
 
-// dgamma[c] = sum over the row splits of partial[split][0][c], dbeta[c] likewise, in split order.
-__global__ void __launch_bounds__(256)
-layer_norm_param_grad_kernel(const float* __restrict__ partial, int blocks, int M, float* __restrict__ dgamma,
+// dgamma[c] = sum over the row splits of partial[split][0][c], dbeta[c] likewise.  A block owns 128 of the 2 M columns (a lane
+// four of them); its eight warps take every eighth split and are added in warp order: a fixed order, and a short chain of loads.
+__global__ void __launch_bounds__(kLnThreads)
+layer_norm_param_grad_kernel(const float* __restrict__ partial, int splits, int M, float* __restrict__ dgamma,
                              float* __restrict__ dbeta) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= 2 * M) return;
-  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
-  int b = 0;
-  for (; b + 3 < blocks; b += 4) {
-    s0 += partial[(size_t)b * 2 * M + c];
-    s1 += partial[(size_t)(b + 1) * 2 * M + c];
-    s2 += partial[(size_t)(b + 2) * 2 * M + c];
-    s3 += partial[(size_t)(b + 3) * 2 * M + c];
+  __shared__ float4 red[kLnWarps][32];
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int c = blockIdx.x * 128 + lane * 4;       // column of the [2][M] pair
+  float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int b = w; b < splits; b += kLnWarps) {
+    const float4 t = *reinterpret_cast<const float4*>(partial + (size_t)b * 2 * M + c);
+    s.x += t.x;
+    s.y += t.y;
+    s.z += t.z;
+    s.w += t.w;
   }
-  for (; b < blocks; ++b) s0 += partial[(size_t)b * 2 * M + c];
-  const float s = (s0 + s1) + (s2 + s3);
-  if (c < M) dgamma[c] = s; else dbeta[c - M] = s;
+  red[w][lane] = s;
+  __syncthreads();
+  if (w == 0) {
+    float4 a = red[0][lane];
+    for (int k = 1; k < kLnWarps; ++k) {
+      const float4 t = red[k][lane];
+      a.x += t.x;
+      a.y += t.y;
+      a.z += t.z;
+      a.w += t.w;
+    }
+    float* out = c < M ? dgamma + c : dbeta + (c - M);
+    *reinterpret_cast<float4*>(out) = a;
+  }
 }
 
 static int ln_blocks(int R) {
@@ -288,6 +301,8 @@ int lancet_layer_norm_bwd(const float* x, const void* dy, int dy_dtype, const fl
   LANCET_REQUIRE(rows >= 0 && M > 0 && M % 128 == 0 && valid_dtype(dy_dtype), LANCET_ERR_INVALID,
                  "lancet_layer_norm_bwd: bad rows=%d, M=%d (a multiple of 128) or dtype", rows, M);
   LANCET_REQUIRE(dgamma && dbeta, LANCET_ERR_NULL, "lancet_layer_norm_bwd: null gradient pointer");
+  LANCET_REQUIRE(aligned(dgamma, 16) && aligned(dbeta, 16), LANCET_ERR_INVALID,
+                 "lancet_layer_norm_bwd: the gradient vectors must be 16-byte aligned");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (rows == 0) {
     LANCET_CUDA(cudaMemsetAsync(dgamma, 0, (size_t)M * sizeof(float), st));
@@ -319,7 +334,7 @@ int lancet_layer_norm_bwd(const float* x, const void* dy, int dy_dtype, const fl
     ln_col_launch<__nv_bfloat16>(x, dy, mean, rstd, partial, rows, M, splits, st);
   }
   if (int rc = launch_status("layer_norm_dx_kernel / layer_norm_col_partial_kernel")) return rc;
-  layer_norm_param_grad_kernel<<<(2 * M + 255) / 256, 256, 0, st>>>(partial, splits, M, dgamma, dbeta);
+  layer_norm_param_grad_kernel<<<2 * M / 128, kLnThreads, 0, st>>>(partial, splits, M, dgamma, dbeta);
   return launch_status("layer_norm_param_grad_kernel");
 }
 }
