@@ -25,7 +25,9 @@ class Attention(torch.nn.Module):
 
     def forward(self, x):
         B, T, M = x.shape
-        q, k, v = self.qkv(x).view(B, T, 3, self.nh, M // self.nh).permute(2, 0, 3, 1, 4)
+        # split along the last axis (the same columns as a [3, heads, head_dim] view): the backward pass then writes the three
+        # gradients straight into one [B, T, 3M] buffer instead of stacking them on a new leading axis and permuting a copy
+        q, k, v = (t.view(B, T, self.nh, M // self.nh).transpose(1, 2) for t in self.qkv(x).split(M, dim=2))
         y = F.scaled_dot_product_attention(q, k, v, is_causal=True)
         return self.proj(y.transpose(1, 2).reshape(B, T, M))
 
