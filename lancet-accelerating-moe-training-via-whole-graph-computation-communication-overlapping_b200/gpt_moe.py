@@ -117,45 +117,43 @@ class LansTrainer:
         self.shared = [p for p in self.params if id(p) not in expert_ids]
         self.m = [torch.zeros_like(p) for p in self.params]
         self.v = [torch.zeros_like(p) for p in self.params]
-        # gradients live in two flat buffers (replicated parameters, then this rank's experts): one all-reduce and one
-        # memset per step instead of a flatten / unflatten copy and a fill per tensor
-        def flat_views(ps):
-            sizes = [(p.numel() + 3) // 4 * 4 for p in ps]                 # keep every view 16-byte aligned
-            flat = torch.zeros(sum(sizes), dtype=torch.float32, device=self.device) if ps else None
-            views, off = [], 0
-            for p, n in zip(ps, sizes):
-                views.append(flat[off:off + p.numel()].view_as(p))
-                off += n
-            return flat, views
-        experts = [p for p in self.params if id(p) in expert_ids]
-        self.flat_shared, gs = flat_views(self.shared)
-        self.flat_expert, ge = flat_views(experts)
-        by_id = {id(p): g for p, g in zip(self.shared + experts, gs + ge)}
-        self.grads = [by_id[id(p)] for p in self.params]
-        for p, g in zip(self.params, self.grads):
-            p.grad = g
-        self.state = LansState(self.grads, [p.data for p in self.params], self.m, self.v)
+        # Gradients are taken from autograd as it produces them (`.grad` is cleared before every backward pass, so nothing is
+        # added into a preset buffer and no buffer has to be zeroed).  With several ranks the gradients of the replicated
+        # parameters are gathered into one flat buffer by a multi-tensor copy, averaged with one all-reduce, and the optimizer
+        # reads them from there; the experts' gradients are rank-local and are used where they are.
         self.lr = lr
         self.step_no = 0
         self.group = group
         self.world = torch.distributed.get_world_size(group) if torch.distributed.is_initialized() else 1
+        self.flat_shared, self.shared_views = None, None
+        if self.world > 1 and self.shared:
+            sizes = [(p.numel() + 3) // 4 * 4 for p in self.shared]                 # keep every view 16-byte aligned
+            self.flat_shared = torch.zeros(sum(sizes), dtype=torch.float32, device=self.device)
+            self.shared_views, off = [], 0
+            for p, n in zip(self.shared, sizes):
+                self.shared_views.append(self.flat_shared[off:off + p.numel()].view_as(p))
+                off += n
+        self._shared_ids = {id(p): i for i, p in enumerate(self.shared)}
 
     def step(self, ids):
         self.step_no += 1
+        for p in self.params:
+            p.grad = None
         loss = self.model(ids)
         loss.backward()
         # weight gradients still queued (dense blocks after the last MoE layer of the backward pass) and those running on
         # the side stream must be complete before they are averaged and applied
         DeferredGrads.join(self.device if self.device.type == "cuda" else None)
         self.check_status()
-        if self.world > 1 and self.flat_shared is not None:
+        grads = [p.grad for p in self.params]
+        if self.flat_shared is not None:
+            torch._foreach_copy_(self.shared_views, [p.grad for p in self.shared])
             torch.distributed.all_reduce(self.flat_shared, op=torch.distributed.ReduceOp.AVG, group=self.group)
+            grads = [self.shared_views[self._shared_ids[id(p)]] if id(p) in self._shared_ids else p.grad for p in self.params]
         with torch.no_grad():
-            lans(self.grads + [p.data for p in self.params] + self.m + self.v, self.step_no, learning_rate=self.lr,
-                 state=self.state)
-        for flat in (self.flat_shared, self.flat_expert):
-            if flat is not None:
-                flat.zero_()
+            # the pointer table is rebuilt when the gradient tensors moved (a few kilobytes and one small launch)
+            lans([g.contiguous() for g in grads] + [p.data for p in self.params] + self.m + self.v, self.step_no,
+                 learning_rate=self.lr)
         return loss.detach()
 
     def check_status(self):
