@@ -144,11 +144,19 @@ class _MoEBlockFunction(torch.autograd.Function):
         if getattr(layer, "x_in", None) is None:
             layer.x_in = torch.empty((moe.S, M), dtype=dt, device=x.device)
         lw, lb, wgf = ln_w.detach().float(), ln_b.detach().float(), wg.detach().float().contiguous()
+        # float32 rows of a width the library's layer norm takes: its kernels write the normalised rows straight into the
+        # layer's input buffer and keep mean and 1/std per row for the backward pass; otherwise torch's layer norm
+        native_ln = x.dtype == torch.float32 and M in ops.LAYER_NORM_WIDTHS
+        mean = torch.empty((moe.S,), dtype=torch.float32, device=x.device) if native_ln else None
+        rstd = torch.empty((moe.S,), dtype=torch.float32, device=x.device) if native_ln else None
 
         def pre(c0, c1):
             sl = slice(c0 * Sp, c1 * Sp)
-            with torch.autocast("cuda", enabled=False):
-                layer.x_in[sl] = F.layer_norm(x[sl].float(), (M,), lw, lb, eps)
+            if native_ln:
+                ops.layer_norm_fwd(x[sl], lw, lb, eps, out=layer.x_in[sl], mean=mean[sl], rstd=rstd[sl])
+            else:
+                with torch.autocast("cuda", enabled=False):
+                    layer.x_in[sl] = F.layer_norm(x[sl].float(), (M,), lw, lb, eps)
             ops.gate_softmax(layer.x_in[sl], wgf, out=probs[sl])
             return layer.x_in[sl], probs[sl]
 
@@ -162,7 +170,7 @@ class _MoEBlockFunction(torch.autograd.Function):
             h, g = pre(0, moe.n)
             post(0, moe.n, layer.forward(h, g))
         ctx.save_for_backward(x, ln_w, ln_b, wg, probs)
-        ctx.blk = blk
+        ctx.blk, ctx.ln_stats = blk, (mean, rstd)
         return y
 
     @staticmethod
@@ -178,6 +186,8 @@ class _MoEBlockFunction(torch.autograd.Function):
         dy = dy.contiguous()
         dx = torch.empty_like(x)
         wgf = wg.detach().float().contiguous()
+        lwf = ln_w.detach().float().contiguous()
+        mean, rstd = ctx.ln_stats
         acc = {"lw": torch.zeros_like(ln_w, dtype=torch.float32), "lb": torch.zeros_like(ln_b, dtype=torch.float32),
                "wg": torch.zeros_like(wgf)}
 
@@ -193,12 +203,15 @@ class _MoEBlockFunction(torch.autograd.Function):
             with torch.autocast("cuda", enabled=False):
                 acc["wg"].addmm_(dlogits.t(), layer.x_in[sl].float())
                 dh = dx_rows.float() + dh_gate.float()
-                xs = x[sl].detach().float().requires_grad_(True)
-                lw = ln_w.detach().float().requires_grad_(True)
-                lb = ln_b.detach().float().requires_grad_(True)
-                with torch.enable_grad():
-                    hh = F.layer_norm(xs, (M,), lw, lb, eps)
-                gx, gw, gb = torch.autograd.grad(hh, [xs, lw, lb], dh)
+                if mean is not None:
+                    gx, gw, gb = ops.layer_norm_bwd(x[sl], dh, lwf, mean[sl], rstd[sl])
+                else:
+                    xs = x[sl].detach().float().requires_grad_(True)
+                    lw = ln_w.detach().float().requires_grad_(True)
+                    lb = ln_b.detach().float().requires_grad_(True)
+                    with torch.enable_grad():
+                        hh = F.layer_norm(xs, (M,), lw, lb, eps)
+                    gx, gw, gb = torch.autograd.grad(hh, [xs, lw, lb], dh)
                 dx[sl] = dy[sl].float() + gx
                 acc["lw"] += gw
                 acc["lb"] += gb

@@ -280,17 +280,23 @@ def gate_softmax_bwd(probs, dprobs, wg, dtype):
     return dlogits, dh
 
 
-def layer_norm_fwd(x, weight, bias, eps=1e-5, out_dtype=torch.float32):
-    """`raf.op.layer_norm` over the last axis of float32 rows [rows, M]; returns (y in out_dtype, mean, rstd)."""
+LAYER_NORM_WIDTHS = (128, 256, 512, 768, 1024, 1536, 2048)
+
+
+def layer_norm_fwd(x, weight, bias, eps=1e-5, out_dtype=torch.float32, out=None, mean=None, rstd=None):
+    """`raf.op.layer_norm` over the last axis of float32 rows [rows, M]; returns (y in out_dtype, mean, rstd).  `out`, `mean`
+    and `rstd` may be given (contiguous, of the right shapes) to have the results written in place."""
     _require_cuda(x, weight, bias)
     if x.dtype != torch.float32 or weight.dtype != torch.float32 or bias.dtype != torch.float32:
         raise TypeError("layer_norm_fwd: rows, weight and bias must be float32")
     x = x.contiguous()
     rows, M = x.shape
-    y = torch.empty((rows, M), dtype=out_dtype, device=x.device)
-    mean = torch.empty((rows,), dtype=torch.float32, device=x.device)
-    rstd = torch.empty((rows,), dtype=torch.float32, device=x.device)
-    check(_capi.lib().lancet_layer_norm_fwd(_ptr(x), _ptr(weight), _ptr(bias), _ptr(y), _DT[out_dtype], _ptr(mean), _ptr(rstd), rows, M,
+    y = torch.empty((rows, M), dtype=out_dtype, device=x.device) if out is None else out
+    mean = torch.empty((rows,), dtype=torch.float32, device=x.device) if mean is None else mean
+    rstd = torch.empty((rows,), dtype=torch.float32, device=x.device) if rstd is None else rstd
+    if not (y.is_contiguous() and mean.is_contiguous() and rstd.is_contiguous()) or y.shape != x.shape:
+        raise ValueError("layer_norm_fwd: out, mean and rstd must be contiguous and shaped like the rows")
+    check(_capi.lib().lancet_layer_norm_fwd(_ptr(x), _ptr(weight), _ptr(bias), _ptr(y), _dt(y), _ptr(mean), _ptr(rstd), rows, M,
                                             float(eps), _stream(x)))
     return y, mean, rstd
 
