@@ -89,20 +89,19 @@ class _DeferredLinearFunction(torch.autograd.Function):
         xc, wc = x.to(cdt), weight.to(cdt)
         ctx.save_for_backward(xc, wc)
         ctx.owner = owner
-        with torch.autocast("cuda", enabled=False):
-            return F.linear(xc, wc, None if bias is None else bias.to(cdt))
+        # every operand already has the compute type, so an enclosing autocast region changes nothing here
+        return F.linear(xc, wc, None if bias is None else bias.to(cdt))
 
     @staticmethod
     def backward(ctx, dy):
         xc, wc = ctx.saved_tensors
         owner = ctx.owner
         dy = dy.contiguous()
-        with torch.autocast("cuda", enabled=False):
-            dx = dy.to(wc.dtype) @ wc
+        dx = dy.to(wc.dtype) @ wc          # (backward passes run outside autocast regions)
         x2, dy2 = xc.reshape(-1, xc.shape[-1]), dy.reshape(-1, dy.shape[-1]).to(xc.dtype)
 
         def weight_grads():
-            with torch.autocast("cuda", enabled=False), torch.no_grad():
+            with torch.no_grad():
                 dw = dy2.t() @ x2
                 owner.weight.grad = dw.to(owner.weight.dtype) if owner.weight.grad is None else owner.weight.grad.add_(dw)
                 if owner.bias is not None:
@@ -155,8 +154,7 @@ class _MoEBlockFunction(torch.autograd.Function):
             if native_ln:
                 ops.layer_norm_fwd(x[sl], lw, lb, eps, out=layer.x_in[sl], mean=mean[sl], rstd=rstd[sl])
             else:
-                with torch.autocast("cuda", enabled=False):
-                    layer.x_in[sl] = F.layer_norm(x[sl].float(), (M,), lw, lb, eps)
+                layer.x_in[sl] = F.layer_norm(x[sl].float(), (M,), lw, lb, eps)     # float32 under autocast as well
             ops.gate_softmax(layer.x_in[sl], wgf, out=probs[sl])
             return layer.x_in[sl], probs[sl]
 
@@ -200,21 +198,21 @@ class _MoEBlockFunction(torch.autograd.Function):
                 dg = dgates[c - c0] if k == 2 else dgates[c - c0, 0]
                 dprobs[cs] = ops.moe_encode_dg(dg.contiguous(), moe.idx_loc[c], E, gate=p[cs].contiguous() if k == 2 else None)
             dlogits, dh_gate = ops.gate_softmax_bwd(p.contiguous(), dprobs, wgf, dt)
-            with torch.autocast("cuda", enabled=False):
-                acc["wg"].addmm_(dlogits.t(), layer.x_in[sl].float())
-                dh = dx_rows.float() + dh_gate.float()
-                if mean is not None:
-                    gx, gw, gb = ops.layer_norm_bwd(x[sl], dh, lwf, mean[sl], rstd[sl])
-                else:
-                    xs = x[sl].detach().float().requires_grad_(True)
-                    lw = ln_w.detach().float().requires_grad_(True)
-                    lb = ln_b.detach().float().requires_grad_(True)
-                    with torch.enable_grad():
-                        hh = F.layer_norm(xs, (M,), lw, lb, eps)
-                    gx, gw, gb = torch.autograd.grad(hh, [xs, lw, lb], dh)
-                dx[sl] = dy[sl].float() + gx
-                acc["lw"] += gw
-                acc["lb"] += gb
+            # float32 arithmetic: backward passes run outside autocast regions
+            acc["wg"].addmm_(dlogits.t(), layer.x_in[sl].float())
+            dh = dx_rows.float() + dh_gate.float()
+            if mean is not None:
+                gx, gw, gb = ops.layer_norm_bwd(x[sl], dh, lwf, mean[sl], rstd[sl])
+            else:
+                xs = x[sl].detach().float().requires_grad_(True)
+                lw = ln_w.detach().float().requires_grad_(True)
+                lb = ln_b.detach().float().requires_grad_(True)
+                with torch.enable_grad():
+                    hh = F.layer_norm(xs, (M,), lw, lb, eps)
+                gx, gw, gb = torch.autograd.grad(hh, [xs, lw, lb], dh)
+            dx[sl] = dy[sl].float() + gx
+            acc["lw"] += gw
+            acc["lb"] += gb
 
         dyl = dy.to(dt).contiguous()
         if blk.pipeline:
