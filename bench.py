@@ -857,6 +857,96 @@ def as_line(leg, args, world=1):
 
 
 # ---------------------------------------------------------------------------------------------------------------
+# every form of the grouped GEMM alone (sustained, power-capped regime)
+# ---------------------------------------------------------------------------------------------------------------
+def leg_gemm_forms(args, ctx, steps):
+    """Each form of the expert GEMM by itself in bursts of about 0.25 s (the regime of a training step: clocks under the
+    power cap), on the shapes of the expert FFN configuration, paired and single-CTA form in turn, next to the library
+    GEMM on the forward shape.  The value of the line is the plain forward form."""
+    import lancet_b200 as LB
+    from lancet_b200 import _capi
+    dev = ctx.dev
+    L = _capi.lib()
+    G, LE, C, M, H = 8, 2, 2560, 2048, 8192
+    g = torch.Generator(device=dev).manual_seed(0)
+    x = torch.randn((G * LE, C, M), device=dev, generator=g).bfloat16()
+    w1 = (torch.randn((LE, H, M), device=dev, generator=g) * 0.02).bfloat16()
+    w2 = (torch.randn((LE, M, H), device=dev, generator=g) * 0.02).bfloat16()
+    b1, b2 = torch.zeros((LE, H), device=dev).bfloat16(), torch.zeros((LE, M), device=dev).bfloat16()
+    h = torch.empty((G * LE, C, H), device=dev, dtype=torch.bfloat16)
+    hpre, dh = torch.empty_like(h), torch.empty_like(h)
+    y = torch.empty((G * LE, C, M), device=dev, dtype=torch.bfloat16)
+    dy = torch.randn((G * LE, C, M), device=dev, generator=g).bfloat16()
+    dx, dw1, dw2 = torch.empty_like(x), torch.empty_like(w1), torch.empty_like(w2)
+    flop = 2.0 * G * LE * C * M * H
+    forms = {
+        "nt_plain_K2048": lambda: LB.grouped_gemm_nt(x, w1, out=h),
+        "nt_bias_gelu_pre_K2048": lambda: LB.grouped_gemm_nt(x, w1, bias=b1, act="gelu", out=h, preact=hpre),
+        "nt_bias_gelu_K2048": lambda: LB.grouped_gemm_nt(x, w1, bias=b1, act="gelu", out=h),
+        "nt_bias_gelu_tanh_pre_K2048": lambda: LB.grouped_gemm_nt(x, w1, bias=b1, act="gelu_tanh", out=h, preact=hpre),
+        "nt_bias_relu_K2048": lambda: LB.grouped_gemm_nt(x, w1, bias=b1, act="relu", out=h),
+        "nt_bias_K8192": lambda: LB.grouped_gemm_nt(h, w2, bias=b2, out=y),
+        "nn_dgelu_K2048": lambda: LB.grouped_gemm_nn(dy, w2, act="gelu", preact=hpre, out=dh),
+        "nn_dgelu_tanh_K2048": lambda: LB.grouped_gemm_nn(dy, w2, act="gelu_tanh", preact=hpre, out=dh),
+        "nn_plain_K8192": lambda: LB.grouped_gemm_nn(dh, w1, out=dx),
+        "tn_dw2": lambda: LB.grouped_gemm_tn(dy, h, LE, out=dw2),
+        "tn_dw1": lambda: LB.grouped_gemm_tn(dh, x, LE, out=dw1),
+    }
+    xa = x.view(G, LE, C, M)[:, 0].reshape(G * C, M).contiguous()
+    ha = torch.empty((G * C, H), device=dev, dtype=torch.bfloat16)
+
+    def library():
+        torch.matmul(xa, w1[0].t(), out=ha)
+        torch.matmul(xa, w1[1].t(), out=ha)
+
+    def timed(fn, target_s=0.25):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        n = max(5, int(target_s * 1e3 / max(e0.elapsed_time(e1), 1e-3)))
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    sampler = ClockSampler(dev.index)
+    out = {}
+    try:
+        for name, fn in forms.items():
+            row = {}
+            for rep in range(2):                           # the two forms take turns twice: best of two per form
+                for mode, flag in (("paired", 1), ("single_cta", 0)):
+                    _capi.check(L.lancet_set_gemm_paired(flag))
+                    ms = timed(fn)
+                    row[mode] = min(ms, row.get(mode, ms))
+            out[name] = {m: {"ms": v, "tflops": flop / v / 1e9} for m, v in row.items()}
+    finally:
+        _capi.check(L.lancet_set_gemm_paired(1))
+    ms_lib = min(timed(library), timed(library))
+    out["library_matmul_20480x8192x2048"] = {"ms": ms_lib, "tflops": flop / ms_lib / 1e9}
+    clocks = ClockSampler.summarise(sampler.stop())
+    st = LB.gemm_status(dev)
+    _capi.check(L.lancet_p2p_status(ctypes.c_void_p(st.data_ptr()), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+    peaks, peak_kind = load_peaks()
+    sustained = float(peaks.get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops"]))
+    best = out["nt_plain_K2048"]["paired"]
+    return {"metric": "grouped_gemm_tflops", "value": best["tflops"], "unit": "TFLOP/s", "ms_per_step": best["ms"], "dtype": "bf16",
+            "config": {"workload": "every form of the grouped GEMM alone: 16 groups x 2560 rows, M=2048, H=8192, bursts of 0.25 s",
+                       "l2": "operands of 1.2 GB per launch exceed the 126 MB L2"},
+            "clocks": clocks, "forms": out,
+            "roofline": {"bound": "tensor", "kernel": "grouped_gemm_kernel (NT, plain, paired)", "achieved": best["tflops"],
+                         "peak": sustained, "unit": "TFLOP/s", "frac": best["tflops"] / sustained,
+                         "peak_kind": peak_kind + " (sustained cuBLAS bf16)", "traffic": None}}
+
+
+# ---------------------------------------------------------------------------------------------------------------
 # expert FFN
 # ---------------------------------------------------------------------------------------------------------------
 def leg_ffn(args, ctx, steps):
@@ -1198,7 +1288,7 @@ def _main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="moe", choices=["moe", "lans", "ffn", "layer", "a2a", "peerbw", "gpt"])
+    ap.add_argument("--workload", default="moe", choices=["moe", "lans", "ffn", "gemm-forms", "layer", "a2a", "peerbw", "gpt"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-legs", action="store_true", help="moe workload: skip the lans / ffn / layer / peerbw legs")
     ap.add_argument("--no-graph", action="store_true", help="launch every step eagerly instead of replaying a CUDA graph")
@@ -1227,6 +1317,8 @@ def _main():
         run_single_leg(args, leg_lans)
     elif args.workload == "ffn":
         run_single_leg(args, leg_ffn)
+    elif args.workload == "gemm-forms":
+        run_single_leg(args, leg_gemm_forms)
     elif args.workload == "layer":
         run_single_leg(args, leg_layer)
     elif args.workload == "a2a":
