@@ -56,6 +56,27 @@ def test_invalid_arguments_launch_nothing(L):
                          0, None) == 1  # workspace too small
 
 
+def test_invalid_arguments_of_the_layer_norm_loss_and_split_combine_entries(L):
+    one = ctypes.c_void_p(16)
+    # layer norm: the width must be a multiple of 128 the kernels are built for; null operands
+    assert L.lancet_layer_norm_fwd(one, one, one, one, 0, one, one, 4, 100, 1e-5, None) == 1
+    assert L.lancet_layer_norm_fwd(one, one, one, one, 0, one, one, 4, 384, 1e-5, None) == 6     # 128 x 3: not instantiated
+    assert L.lancet_layer_norm_fwd(None, one, one, one, 0, one, one, 4, 256, 1e-5, None) == 2
+    assert L.lancet_layer_norm_fwd(one, one, one, one, 0, one, one, 0, 256, 1e-5, None) == 0    # no rows: nothing to do
+    assert L.lancet_layer_norm_bwd(one, one, 0, one, one, one, one, one, one, 4, 256, one, 8, None) == 1   # workspace too small
+    assert L.lancet_layer_norm_workspace_bytes(8192, 1024) > 0 and L.lancet_layer_norm_workspace_bytes(8192, 100) == 0
+    # loss: the vocabulary cannot be wider than a row; null operands
+    assert L.lancet_softmax_xent_fwd(one, 16, one, 4, 17, 2, one, one, None) == 1
+    assert L.lancet_softmax_xent_fwd(None, 16, one, 4, 10, 2, one, one, None) == 2
+    assert L.lancet_softmax_xent_bwd(one, 16, one, 4, 10, 8, 2, one, None, 1.0, one, 16, None) == 1   # fewer columns than classes
+    assert L.lancet_softmax_xent_fwd(one, 16, one, 0, 10, 2, one, one, None) == 0
+    # the two halves of the backward combine: part is 0, 1 or 2
+    ptrs = (ctypes.c_void_p * 2)(16, 16)
+    assert L.lancet_moe_combine_bwd_part_p2p(one, one, one, ptrs, ptrs, one, 8, 8, 4, 1, 2, 0, 2, 1, 0, 3, None) == 1
+    assert b"part" in L.lancet_last_error()
+    assert L.lancet_set_chained_launch(1) == 0
+
+
 def test_workspace_queries(L):
     assert L.lancet_moe_gate_workspace_bytes(16384, 16, 2) >= 2 * 16384 * 4 + 64 * 32 * 4
     assert L.lancet_moe_gate_workspace_bytes(0, 8, 1) > 0
