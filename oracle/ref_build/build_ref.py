@@ -21,12 +21,13 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(os.path.dirname(HERE), "_ref")
 LIB = os.path.join(OUT, "libraf_ref_kernels.so")
 KERNELS = "src/op/dialect/cuda/kernels"
+DEFAULT_ROOT = os.environ.get("LANCET_REFERENCE_ROOT", "/root/reference")   # where the reference tree is mounted, if at all
 SOURCES = ("tutel_moe_dispatch.cu", "multi_tensor_lans.cu")
 
 
-def build(ref_root="/root/reference", verbose=False):
+def build(ref_root=None, verbose=False):
     """Returns the library path, or None when the reference tree or nvcc is not available."""
-    kdir = os.path.join(ref_root, KERNELS)
+    kdir = os.path.join(ref_root or DEFAULT_ROOT, KERNELS)
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     if not all(os.path.exists(os.path.join(kdir, s)) for s in SOURCES) or not os.path.exists(nvcc):
         return None

@@ -9,7 +9,7 @@ from oracle.ref_build import build_ref
 from tests import ref_kernels
 
 
-@pytest.mark.skipif(not os.path.isdir("/root/reference/src/op/dialect/cuda/kernels"), reason="reference tree not present")
+@pytest.mark.skipif(not os.path.isdir(os.path.join(build_ref.DEFAULT_ROOT, build_ref.KERNELS)), reason="reference tree not present")
 def test_reference_kernels_build_and_export():
     path = build_ref.build()
     assert path and os.path.exists(path) and path == ref_kernels.PATH
