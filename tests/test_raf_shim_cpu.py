@@ -17,11 +17,19 @@ def built():
     LB.build.build()
 
 
-def test_registry_cpp(tmp_path):
+@pytest.mark.parametrize("flags", [[], ["-g", "-fsanitize=address,undefined", "-fno-omit-frame-pointer"]],
+                         ids=["plain", "asan_ubsan"])
+def test_registry_cpp(tmp_path, flags):
+    """The registry's host code, also under the address and undefined-behaviour sanitizers (the reference offers them for
+    its host code through RAF_USE_SANITIZER, cmake/modules/Sanitizer.cmake:77-93)."""
     shim = os.path.join(LB.build.CSRC, "raf_shim")
     exe = str(tmp_path / "test_raf_shim")
-    subprocess.run(["g++", "-std=c++17", "-O1", "-I", shim, os.path.join(ROOT, "tests", "cpp", "test_raf_shim.cc"),
-                    os.path.join(shim, "registry.cc"), "-o", exe], check=True)
+    cmd = ["g++", "-std=c++17", "-O1"] + flags + ["-I", shim, os.path.join(ROOT, "tests", "cpp", "test_raf_shim.cc"),
+                                                   os.path.join(shim, "registry.cc"), "-o", exe]
+    built = subprocess.run(cmd, capture_output=True, text=True)
+    if built.returncode != 0 and flags:
+        pytest.skip("sanitizer runtime not available: " + built.stderr[-200:])
+    assert built.returncode == 0, built.stderr
     r = subprocess.run([exe], capture_output=True, text=True)
     assert r.returncode == 0 and "raf shim ok" in r.stdout, r.stdout + r.stderr
 
