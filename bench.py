@@ -334,7 +334,7 @@ def run_reference_arm(args):
 def moe_config(world):
     return {"workload": "moe_dispatch_a2a_combine: S=%d tokens/GPU, M=%d fp16, E=%d, top-%d, cf=%.2f, %d chunks" % (
         S_TOKENS, M_DIM, 2 * world, TOP_K, CAP_FACTOR, N_CHUNKS),
-        "tokens_per_gpu": S_TOKENS, "model_dim": M_DIM, "experts": 2 * world, "top_k": TOP_K,
+        "tokens_per_gpu": S_TOKENS, "row_width": M_DIM, "experts": 2 * world, "top_k": TOP_K,
         "capacity_factor": CAP_FACTOR, "chunks": N_CHUNKS,
         "l2": "inputs rotate over 2 sets; 288 MiB touched per step exceeds the 126 MB L2"}
 
